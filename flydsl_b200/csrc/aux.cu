@@ -1,0 +1,241 @@
+// Bandwidth-bound helpers around the GEMM stages: row gather into sorted order,
+// top-k reduce, 1x128 activation quantiser, weight (un)shuffle.
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace flymoe {
+
+// ---------------------------------------------------------------------------- gather
+// One warp per sorted row, 16 bytes per lane per step.
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
+                   const int* __restrict__ sorted_ids, const int* __restrict__ num_valid_ids,
+                   int num_tokens, int topk, int row_vec, int src_layout, int max_rows) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  const int valid = min(__ldg(num_valid_ids), max_rows);
+  for (int r = blockIdx.x * warps_per_block + (threadIdx.x >> 5); r < valid;
+       r += gridDim.x * warps_per_block) {
+    const int id = __ldg(sorted_ids + r);
+    const int t = id_token(id), s = id_slot(id);
+    uint4* d = dst + size_t(r) * row_vec;
+    if (t < num_tokens && s < topk) {
+      const size_t srow = (src_layout == FLYMOE_ROWS_BY_TOKEN) ? size_t(t) : size_t(t) * topk + s;
+      const uint4* p = src + srow * row_vec;
+      for (int i = lane; i < row_vec; i += 32) d[i] = __ldg(p + i);
+    } else {
+      for (int i = lane; i < row_vec; i += 32) d[i] = make_uint4(0, 0, 0, 0);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------- reduce
+template <typename T> struct Vec8;
+template <> struct Vec8<__half> {
+  static __device__ __forceinline__ void load(const __half* p, float* f) {
+    uint4 v = __ldg(reinterpret_cast<const uint4*>(p));
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { float2 x = __half22float2(h[i]); f[2 * i] = x.x; f[2 * i + 1] = x.y; }
+  }
+  static __device__ __forceinline__ void store(__half* p, const float* f) {
+    uint4 v;
+    v.x = pack_f16x2(f[0], f[1]); v.y = pack_f16x2(f[2], f[3]);
+    v.z = pack_f16x2(f[4], f[5]); v.w = pack_f16x2(f[6], f[7]);
+    *reinterpret_cast<uint4*>(p) = v;
+  }
+};
+template <> struct Vec8<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* f) {
+    uint4 v = __ldg(reinterpret_cast<const uint4*>(p));
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { float2 x = __bfloat1622float2(h[i]); f[2 * i] = x.x; f[2 * i + 1] = x.y; }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* f) {
+    uint4 v;
+    v.x = pack_bf16x2(f[0], f[1]); v.y = pack_bf16x2(f[2], f[3]);
+    v.z = pack_bf16x2(f[4], f[5]); v.w = pack_bf16x2(f[6], f[7]);
+    *reinterpret_cast<uint4*>(p) = v;
+  }
+};
+template <> struct Vec8<float> {
+  static __device__ __forceinline__ void load(const float* p, float* f) {
+    float4 a = __ldg(reinterpret_cast<const float4*>(p));
+    float4 b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float* f) {
+    reinterpret_cast<float4*>(p)[0] = make_float4(f[0], f[1], f[2], f[3]);
+    reinterpret_cast<float4*>(p)[1] = make_float4(f[4], f[5], f[6], f[7]);
+  }
+};
+
+// grid (T, ceil(D / 2048)), 256 threads x 8 elements.
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_reduce_kernel(const T* __restrict__ x, T* __restrict__ y, const uint8_t* __restrict__ mask,
+                  const float* __restrict__ weights, int topk, int model_dim) {
+  const int t = blockIdx.x;
+  const int col = (blockIdx.y * 256 + threadIdx.x) * 8;
+  if (col >= model_dim) return;
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (int s = 0; s < topk; ++s) {
+    if (mask != nullptr && mask[size_t(t) * topk + s] == 0) continue;
+    float f[8];
+    Vec8<T>::load(x + (size_t(t) * topk + s) * model_dim + col, f);
+    const float w = weights != nullptr ? __ldg(weights + size_t(t) * topk + s) : 1.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = weights != nullptr ? fmaf(f[i], w, acc[i]) : acc[i] + f[i];
+  }
+  Vec8<T>::store(y + size_t(t) * model_dim + col, acc);
+}
+
+// ---------------------------------------------------------------------------- quantiser
+// One warp per (row, 128-column group): 4 elements per lane.
+template <typename T>
+__global__ void __launch_bounds__(256)
+quant_act_1x128_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scale,
+                       long long scale_stride, int rows, int groups) {
+  const int lane = threadIdx.x & 31;
+  const long long total = (long long)rows * groups;
+  const int warps_per_block = blockDim.x >> 5;
+  for (long long g = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5); g < total;
+       g += (long long)gridDim.x * warps_per_block) {
+    const int r = int(g / groups), gb = int(g - (long long)r * groups);
+    const T* p = x + (size_t(r) * groups + gb) * 128 + lane * 4;
+    float f[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) f[i] = float(p[i]);
+    float amax = fmaxf(fmaxf(fabsf(f[0]), fabsf(f[1])), fmaxf(fabsf(f[2]), fabsf(f[3])));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    float sc = __fdiv_rn(amax, 448.0f);
+    if (sc == 0.f) sc = 1.f;
+    const uint32_t packed = float4_to_e4m3x4(__fdiv_rn(f[0], sc), __fdiv_rn(f[1], sc),
+                                             __fdiv_rn(f[2], sc), __fdiv_rn(f[3], sc));
+    *reinterpret_cast<uint32_t*>(q + (size_t(r) * groups + gb) * 128 + lane * 4) = packed;
+    if (lane == 0) scale[(long long)gb * scale_stride + r] = sc;
+  }
+}
+
+// ---------------------------------------------------------------------------- shuffle
+// Preshuffle order of a [rows, cols] byte matrix: element (n, k) lives at
+// (((n/16) * (cols/32) + k/32) * 2 + (k%32)/16) * 256 + (n%16) * 16 + k%16.
+// One thread moves 16 bytes.
+__global__ void __launch_bounds__(256)
+shuffle_weight_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long long rows, int cols,
+                      int to_plain) {
+  const long long nvec = rows * (cols / 16);
+  const int kv = cols / 16;  // 16-byte vectors per row
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long n = i / kv;
+    const int kc = int(i - n * kv);              // 16-byte chunk index along k
+    const long long shuf = (((n / 16) * (cols / 32) + kc / 2) * 2 + (kc & 1)) * 16 + (n % 16);
+    if (to_plain) dst[i] = __ldg(src + shuf);
+    else dst[shuf] = __ldg(src + i);
+  }
+}
+
+}  // namespace flymoe
+
+extern "C" int flymoe_gather_rows(const void* src, void* dst, const int32_t* sorted_ids,
+                                  const int32_t* num_valid_ids, int num_tokens, int topk,
+                                  int row_bytes, int src_layout, int max_rows, void* stream) {
+  using namespace flymoe;
+  FLYMOE_REQUIRE(src && dst && sorted_ids && num_valid_ids, "gather_rows: null pointer");
+  FLYMOE_REQUIRE(row_bytes > 0 && row_bytes % 16 == 0, "gather_rows: row_bytes must be a multiple of 16");
+  FLYMOE_REQUIRE(aligned16(src) && aligned16(dst), "gather_rows: pointers must be 16-byte aligned");
+  FLYMOE_REQUIRE(src_layout == FLYMOE_ROWS_BY_TOKEN || src_layout == FLYMOE_ROWS_BY_PAIR,
+                 "gather_rows: src_layout must be BY_TOKEN or BY_PAIR");
+  if (max_rows <= 0) return FLYMOE_OK;
+  const int blocks = std::min(ceil_div(max_rows, 8), sm_count() * 8);
+  gather_rows_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(src), static_cast<uint4*>(dst), sorted_ids, num_valid_ids, num_tokens,
+      topk, row_bytes / 16, src_layout, max_rows);
+  FLYMOE_CUDA_CHECK(cudaGetLastError());
+  return FLYMOE_OK;
+}
+
+extern "C" int flymoe_moe_reduce(const void* x, void* y, const uint8_t* valid_mask,
+                                 const float* weights, int num_tokens, int topk, int model_dim,
+                                 int dtype, void* stream) {
+  using namespace flymoe;
+  FLYMOE_REQUIRE(num_tokens >= 0 && topk >= 1 && model_dim >= 8 && model_dim % 8 == 0,
+                 "moe_reduce: model_dim must be a positive multiple of 8");
+  if (num_tokens == 0) return FLYMOE_OK;
+  FLYMOE_REQUIRE(x && y, "moe_reduce: null pointer");
+  FLYMOE_REQUIRE(aligned16(x) && aligned16(y), "moe_reduce: pointers must be 16-byte aligned");
+  dim3 grid(num_tokens, ceil_div(model_dim, 2048));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case FLYMOE_F16:
+      moe_reduce_kernel<__half><<<grid, 256, 0, s>>>(static_cast<const __half*>(x), static_cast<__half*>(y),
+                                                     valid_mask, weights, topk, model_dim);
+      break;
+    case FLYMOE_BF16:
+      moe_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x),
+                                                            static_cast<__nv_bfloat16*>(y), valid_mask,
+                                                            weights, topk, model_dim);
+      break;
+    case FLYMOE_F32:
+      moe_reduce_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(x), static_cast<float*>(y),
+                                                    valid_mask, weights, topk, model_dim);
+      break;
+    default:
+      set_last_error_msg("moe_reduce: dtype must be F16, BF16 or F32");
+      return FLYMOE_ERR_INVALID_ARGUMENT;
+  }
+  FLYMOE_CUDA_CHECK(cudaGetLastError());
+  return FLYMOE_OK;
+}
+
+extern "C" int flymoe_quant_act_1x128(const void* x, int x_dtype, void* q, float* scale,
+                                      int64_t scale_stride, int rows, int cols, void* stream) {
+  using namespace flymoe;
+  FLYMOE_REQUIRE(rows >= 0 && cols > 0 && cols % 128 == 0, "quant_act_1x128: cols must be a multiple of 128");
+  if (rows == 0) return FLYMOE_OK;
+  FLYMOE_REQUIRE(x && q && scale, "quant_act_1x128: null pointer");
+  FLYMOE_REQUIRE(scale_stride >= rows, "quant_act_1x128: scale_stride < rows");
+  const int groups = cols / 128;
+  const long long total = (long long)rows * groups;
+  const int blocks = int(std::min<long long>((total + 7) / 8, (long long)sm_count() * 16));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  uint8_t* qq = static_cast<uint8_t*>(q);
+  switch (x_dtype) {
+    case FLYMOE_F16:
+      quant_act_1x128_kernel<__half><<<blocks, 256, 0, s>>>(static_cast<const __half*>(x), qq, scale,
+                                                            scale_stride, rows, groups);
+      break;
+    case FLYMOE_BF16:
+      quant_act_1x128_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), qq,
+                                                                   scale, scale_stride, rows, groups);
+      break;
+    case FLYMOE_F32:
+      quant_act_1x128_kernel<float><<<blocks, 256, 0, s>>>(static_cast<const float*>(x), qq, scale,
+                                                           scale_stride, rows, groups);
+      break;
+    default:
+      set_last_error_msg("quant_act_1x128: dtype must be F16, BF16 or F32");
+      return FLYMOE_ERR_INVALID_ARGUMENT;
+  }
+  FLYMOE_CUDA_CHECK(cudaGetLastError());
+  return FLYMOE_OK;
+}
+
+extern "C" int flymoe_shuffle_weight(const void* src, void* dst, int64_t rows, int cols, int to_plain,
+                                     void* stream) {
+  using namespace flymoe;
+  FLYMOE_REQUIRE(src && dst && src != dst, "shuffle_weight: src and dst must be distinct non-null pointers");
+  FLYMOE_REQUIRE(rows > 0 && rows % 16 == 0 && cols > 0 && cols % 32 == 0,
+                 "shuffle_weight: rows must be a multiple of 16 and cols of 32");
+  FLYMOE_REQUIRE(aligned16(src) && aligned16(dst), "shuffle_weight: pointers must be 16-byte aligned");
+  const long long nvec = rows * (cols / 16);
+  const int blocks = int(std::min<long long>((nvec + 255) / 256, (long long)sm_count() * 32));
+  shuffle_weight_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(src), static_cast<uint4*>(dst), rows, cols, to_plain);
+  FLYMOE_CUDA_CHECK(cudaGetLastError());
+  return FLYMOE_OK;
+}

@@ -1,0 +1,141 @@
+// C entry points of the two grouped-GEMM stages: argument validation and dispatch.
+#include "common.cuh"
+#include "gemm_args.cuh"
+
+using namespace flymoe;
+
+static bool layout_ok(int l) {
+  return l == FLYMOE_ROWS_BY_TOKEN || l == FLYMOE_ROWS_BY_PAIR || l == FLYMOE_ROWS_SORTED;
+}
+
+static long long layout_rows(int layout, int num_tokens, int topk, int size_expert_ids, int tile_m) {
+  if (layout == FLYMOE_ROWS_BY_TOKEN) return num_tokens;
+  if (layout == FLYMOE_ROWS_BY_PAIR) return (long long)num_tokens * topk;
+  return (long long)size_expert_ids * tile_m;
+}
+
+extern "C" int flymoe_moe_gemm1(void* out, float* out_scale, int64_t out_scale_stride, const void* x,
+                                const float* scale_x, int64_t sx_stride, const void* w,
+                                const float* scale_w, const int32_t* sorted_ids,
+                                const int32_t* sorted_expert_ids, const float* sorted_weights,
+                                const int32_t* num_valid_ids, int num_tokens, int inter_dim,
+                                int model_dim, int size_expert_ids, int experts, int topk, int tile_m,
+                                int doweight, int out_dtype, int x_layout, int x_scale_layout,
+                                int out_layout, int impl, void* stream) {
+  FLYMOE_REQUIRE(num_tokens >= 0 && num_tokens < (1 << 24), "gemm1: num_tokens out of range");
+  FLYMOE_REQUIRE(inter_dim > 0 && inter_dim % 128 == 0, "gemm1: inter_dim must be a positive multiple of 128");
+  FLYMOE_REQUIRE(model_dim > 0 && model_dim % 128 == 0, "gemm1: model_dim must be a positive multiple of 128");
+  FLYMOE_REQUIRE(experts >= 1 && topk >= 1 && topk <= 255, "gemm1: experts/topk out of range");
+  FLYMOE_REQUIRE(tile_m >= 1 && size_expert_ids >= 0, "gemm1: tile_m/size_expert_ids out of range");
+  FLYMOE_REQUIRE(out_dtype == FLYMOE_F16 || out_dtype == FLYMOE_BF16 || out_dtype == FLYMOE_E4M3,
+                 "gemm1: out_dtype must be F16, BF16 or E4M3");
+  FLYMOE_REQUIRE(layout_ok(x_layout) && x_layout != FLYMOE_ROWS_BY_PAIR, "gemm1: x_layout must be BY_TOKEN or SORTED");
+  FLYMOE_REQUIRE(layout_ok(x_scale_layout) && x_scale_layout != FLYMOE_ROWS_BY_PAIR,
+                 "gemm1: x_scale_layout must be BY_TOKEN or SORTED");
+  FLYMOE_REQUIRE(out_layout == FLYMOE_ROWS_BY_PAIR || out_layout == FLYMOE_ROWS_SORTED,
+                 "gemm1: out_layout must be BY_PAIR or SORTED");
+  if (num_tokens == 0 || size_expert_ids == 0) return FLYMOE_OK;
+  FLYMOE_REQUIRE(out && x && scale_x && w && scale_w && sorted_ids && sorted_expert_ids && num_valid_ids,
+                 "gemm1: null pointer");
+  FLYMOE_REQUIRE(!doweight || sorted_weights, "gemm1: doweight needs sorted_weights");
+  FLYMOE_REQUIRE(out_dtype != FLYMOE_E4M3 || out_scale, "gemm1: e4m3 output needs out_scale");
+  FLYMOE_REQUIRE(aligned16(out) && aligned16(x) && aligned16(w), "gemm1: out/x/w must be 16-byte aligned");
+  const long long srows = layout_rows(x_scale_layout, num_tokens, topk, size_expert_ids, tile_m);
+  FLYMOE_REQUIRE(sx_stride >= srows || x_scale_layout == FLYMOE_ROWS_SORTED, "gemm1: sx_stride smaller than row count");
+  int* status = device_status_ptr();
+  FLYMOE_REQUIRE(status != nullptr, "gemm1: no CUDA device");
+
+  GemmArgs a;
+  a.a = static_cast<const uint8_t*>(x);
+  a.scale_a = scale_x;
+  a.sa_stride = sx_stride;
+  a.a_layout = x_layout;
+  a.a_scale_layout = x_scale_layout;
+  a.a_rows = layout_rows(x_layout, num_tokens, topk, size_expert_ids, tile_m);
+  a.w = static_cast<const uint8_t*>(w);
+  a.scale_w = scale_w;
+  a.sorted_ids = sorted_ids;
+  a.sorted_expert_ids = sorted_expert_ids;
+  a.sorted_weights = sorted_weights;
+  a.num_valid_ids = num_valid_ids;
+  a.out = out;
+  a.out_scale = out_scale;
+  a.out_scale_stride = out_scale_stride;
+  a.out_dtype = out_dtype;
+  a.out_layout = out_layout;
+  a.accumulate = 0;
+  a.doweight = doweight;
+  a.num_tokens = num_tokens;
+  a.topk = topk;
+  a.experts = experts;
+  a.n_dim = inter_dim;
+  a.k_dim = model_dim;
+  a.size_expert_ids = size_expert_ids;
+  a.tile_m = tile_m;
+  a.status = status;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (impl == FLYMOE_IMPL_SIMT) return launch_gemm_simt(1, a, s);
+  if (impl == FLYMOE_IMPL_TCGEN05) return launch_gemm_sm100(1, a, s);
+  set_last_error_msg("gemm1: unknown impl");
+  return FLYMOE_ERR_INVALID_ARGUMENT;
+}
+
+extern "C" int flymoe_moe_gemm2(void* out, const void* a2, const float* scale_a, int64_t sa_stride,
+                                const void* w, const float* scale_w, const int32_t* sorted_ids,
+                                const int32_t* sorted_expert_ids, const float* sorted_weights,
+                                const int32_t* num_valid_ids, int num_tokens, int model_dim,
+                                int inter_dim, int size_expert_ids, int experts, int topk, int tile_m,
+                                int doweight, int out_dtype, int accumulate, int a_layout,
+                                int a_scale_layout, int impl, void* stream) {
+  FLYMOE_REQUIRE(num_tokens >= 0 && num_tokens < (1 << 24), "gemm2: num_tokens out of range");
+  FLYMOE_REQUIRE(inter_dim > 0 && inter_dim % 128 == 0, "gemm2: inter_dim must be a positive multiple of 128");
+  FLYMOE_REQUIRE(model_dim > 0 && model_dim % 128 == 0, "gemm2: model_dim must be a positive multiple of 128");
+  FLYMOE_REQUIRE(experts >= 1 && topk >= 1 && topk <= 255, "gemm2: experts/topk out of range");
+  FLYMOE_REQUIRE(tile_m >= 1 && size_expert_ids >= 0, "gemm2: tile_m/size_expert_ids out of range");
+  FLYMOE_REQUIRE(out_dtype == FLYMOE_F16 || out_dtype == FLYMOE_BF16 || (out_dtype == FLYMOE_F32 && accumulate),
+                 "gemm2: out_dtype must be F16 or BF16 (F32 only with accumulate)");
+  FLYMOE_REQUIRE((a_layout == FLYMOE_ROWS_BY_PAIR || a_layout == FLYMOE_ROWS_SORTED) &&
+                     (a_scale_layout == FLYMOE_ROWS_BY_PAIR || a_scale_layout == FLYMOE_ROWS_SORTED),
+                 "gemm2: a_layout/a_scale_layout must be BY_PAIR or SORTED");
+  if (num_tokens == 0 || size_expert_ids == 0) return FLYMOE_OK;
+  FLYMOE_REQUIRE(out && a2 && scale_a && w && scale_w && sorted_ids && sorted_expert_ids && num_valid_ids,
+                 "gemm2: null pointer");
+  FLYMOE_REQUIRE(!doweight || sorted_weights, "gemm2: doweight needs sorted_weights");
+  FLYMOE_REQUIRE(aligned16(out) && aligned16(a2) && aligned16(w), "gemm2: out/a2/w must be 16-byte aligned");
+  int* status = device_status_ptr();
+  FLYMOE_REQUIRE(status != nullptr, "gemm2: no CUDA device");
+
+  GemmArgs a;
+  a.a = static_cast<const uint8_t*>(a2);
+  a.scale_a = scale_a;
+  a.sa_stride = sa_stride;
+  a.a_layout = a_layout;
+  a.a_scale_layout = a_scale_layout;
+  a.a_rows = layout_rows(a_layout, num_tokens, topk, size_expert_ids, tile_m);
+  a.w = static_cast<const uint8_t*>(w);
+  a.scale_w = scale_w;
+  a.sorted_ids = sorted_ids;
+  a.sorted_expert_ids = sorted_expert_ids;
+  a.sorted_weights = sorted_weights;
+  a.num_valid_ids = num_valid_ids;
+  a.out = out;
+  a.out_scale = nullptr;
+  a.out_scale_stride = 0;
+  a.out_dtype = out_dtype;
+  a.out_layout = FLYMOE_ROWS_BY_PAIR;
+  a.accumulate = accumulate ? 1 : 0;
+  a.doweight = doweight;
+  a.num_tokens = num_tokens;
+  a.topk = topk;
+  a.experts = experts;
+  a.n_dim = model_dim;
+  a.k_dim = inter_dim;
+  a.size_expert_ids = size_expert_ids;
+  a.tile_m = tile_m;
+  a.status = status;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (impl == FLYMOE_IMPL_SIMT) return launch_gemm_simt(2, a, s);
+  if (impl == FLYMOE_IMPL_TCGEN05) return launch_gemm_sm100(2, a, s);
+  set_last_error_msg("gemm2: unknown impl");
+  return FLYMOE_ERR_INVALID_ARGUMENT;
+}

@@ -1,0 +1,557 @@
+// Grouped FP8 (e4m3) block-scaled GEMM for both MoE stages on sm_100a.
+//
+// One persistent CTA per SM walks a static sequence of (sorted row block, N tile)
+// tiles.  Warp roles (384 threads):
+//   warp 0      TMA producer: per 128-wide K block one A box (tile_m sorted rows x 128 B)
+//               and 256 weight rows x 128 B into a 4-deep shared-memory ring
+//               (128-byte swizzle, K-major).
+//   warp 1      MMA issuer: four tcgen05.mma (kind::f8f6f4, M=128, N=256, K=32) per K
+//               block into one of two 256-column TMEM accumulator stages, started from
+//               zero for every K block; tcgen05.commit releases the smem stage and
+//               publishes the TMEM stage.
+//   warps 4-11  epilogue, two warpgroups: tcgen05.ld the fp32 partial sums of the K
+//               block and fold them into register accumulators with the product of the
+//               row's activation scale and the weight block's scale (the scales are
+//               arbitrary fp32 per 128 K, so they cannot ride inside the MMA).
+//               Each thread owns one sorted row.
+// Stage 1 tile: 128 gate rows + 128 up rows of W1 (one quantisation group of the
+// output); each warpgroup takes 64 gate + 64 up columns, computes silu(gate)*up and
+// either stores f16/bf16 or requantises to e4m3 with the per-row 1x128 scale (row amax
+// exchanged between the two warpgroups through shared memory).
+// Stage 2 tile: 256 rows of W2; each warpgroup takes 128 columns, multiplies by the
+// routing weight and adds into out[token] with vector reductions (or stores per-pair
+// rows for a later top-k reduce).
+//
+// Every wait is bounded: when one gives up it raises the CTA's abort flag and the
+// device status word, every role drains out, TMEM is released and the kernel returns.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <stdio.h>
+
+#include "common.cuh"
+#include "gemm_args.cuh"
+
+namespace flymoe {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 128;
+constexpr int kStages = 4;
+constexpr int kATileBytes = BM * BK;            // 16 KB
+constexpr int kBTileBytes = BN * BK;            // 32 KB
+constexpr int kStageBytes = kATileBytes + kBTileBytes;
+constexpr int kAccStages = 2;
+constexpr int kTmemCols = 512;
+constexpr int kNumThreads = 384;
+constexpr int kEpilogueWarps = 8;
+constexpr unsigned long long kWaitLimitNs = 4000000000ull;   // 4 s
+
+struct __align__(16) SmemCtrl {
+  unsigned long long full[kStages];
+  unsigned long long empty[kStages];
+  unsigned long long tmem_full[kAccStages];
+  unsigned long long tmem_empty[kAccStages];
+  unsigned long long amax_bar[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  float amax[2][2][BM];
+};
+constexpr size_t kSmemBytes = size_t(kStages) * kStageBytes + sizeof(SmemCtrl) + 1024;
+
+// ------------------------------------------------------------------------------ PTX
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+  return done;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait.  Returns false when the CTA is aborting or the time limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+#pragma unroll 1
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 0xFF) == 0) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1,
+                                            int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major, 128-byte-swizzled operand tile: 8-row groups 1024 B apart.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= uint64_t((smem_addr >> 4) & 0x3FFF);          // start address
+  d |= uint64_t(1) << 16;                            // leading byte offset (unused with swizzle)
+  d |= uint64_t((1024 >> 4) & 0x3FFF) << 32;         // stride byte offset
+  d |= uint64_t(1) << 46;                            // descriptor version (sm_100)
+  d |= uint64_t(2) << 61;                            // SWIZZLE_128B
+  return d;
+}
+// kind::f8f6f4, A=B=e4m3, D=f32, both K-major, M=128, N=256.
+constexpr uint32_t kInstrDesc = (1u << 4) | (0u << 7) | (0u << 10) | (uint32_t(BN >> 3) << 17) |
+                                (uint32_t(BM >> 4) << 24);
+
+__device__ __forceinline__ void red_add_v4_f32(float* p, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+__device__ __forceinline__ void red_add_v4_bf16x2(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d)
+               : "memory");
+}
+__device__ __forceinline__ void red_add_v4_f16x2(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("red.global.add.noftz.v4.f16x2 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d)
+               : "memory");
+}
+
+// ------------------------------------------------------------------------------ tiles
+struct TileSched {
+  int num_mblocks, num_ntiles, total, group_m;
+  __device__ __forceinline__ void decode(int t, int& mb, int& n) const {
+    const int per_group = group_m * num_ntiles;
+    const int bg = t / per_group;
+    const int rem = t - bg * per_group;
+    const int gs = min(group_m, num_mblocks - bg * group_m);
+    n = rem / gs;
+    mb = bg * group_m + (rem - n * gs);
+  }
+};
+
+template <int STAGE>
+__global__ void __launch_bounds__(kNumThreads, 1)
+moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                      const GemmArgs a, const int group_m) {
+  extern __shared__ uint8_t smem_dyn[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+  SmemCtrl* ctrl = reinterpret_cast<SmemCtrl*>(smem + size_t(kStages) * kStageBytes);
+  volatile int* abort_flag = &ctrl->abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int KB = a.k_dim / BK;
+
+  const int valid_rows = min(__ldg(a.num_valid_ids), a.size_expert_ids * a.tile_m);
+  TileSched sched;
+  sched.num_mblocks = (valid_rows + a.tile_m - 1) / a.tile_m;
+  sched.num_ntiles = STAGE == 1 ? a.n_dim / 128 : (a.n_dim + BN - 1) / BN;
+  sched.total = sched.num_mblocks * sched.num_ntiles;
+  sched.group_m = group_m;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(smem_u32(&ctrl->full[i]), 1);
+      mbar_init(smem_u32(&ctrl->empty[i]), 1);
+    }
+    for (int i = 0; i < kAccStages; ++i) {
+      mbar_init(smem_u32(&ctrl->tmem_full[i]), 1);
+      mbar_init(smem_u32(&ctrl->tmem_empty[i]), kEpilogueWarps);
+    }
+    mbar_init(smem_u32(&ctrl->amax_bar[0]), kEpilogueWarps);
+    mbar_init(smem_u32(&ctrl->amax_bar[1]), kEpilogueWarps);
+    ctrl->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&ctrl->tmem_base)), "r"(uint32_t(kTmemCols)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = ctrl->tmem_base;
+
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    if (warp == 0 && lane == 0) {
+      // ---------------------------------------------------------------- TMA producer
+      int stage = 0;
+      uint32_t phase = 0;
+      const uint32_t tx_bytes = uint32_t(a.tile_m) * BK + kBTileBytes;
+      bool ok = true;
+      for (int t = blockIdx.x; t < sched.total && ok; t += gridDim.x) {
+        int mb, n;
+        sched.decode(t, mb, n);
+        const int e = __ldg(a.sorted_expert_ids + mb);
+        if (e < 0 || e >= a.experts) continue;
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, a.status, 1)) { ok = false; break; }
+          const uint32_t full = smem_u32(&ctrl->full[stage]);
+          const uint32_t sa = smem_u32(smem + size_t(stage) * kStageBytes);
+          const uint32_t sb = sa + kATileBytes;
+          mbar_expect_tx(full, tx_bytes);
+          tma_load_2d(sa, &tmap_a, full, kb * BK, mb * a.tile_m);
+          if (STAGE == 1) {
+            tma_load_3d(sb, &tmap_b, full, kb * BK, n * 128, e);
+            tma_load_3d(sb + 128 * BK, &tmap_b, full, kb * BK, a.n_dim + n * 128, e);
+          } else {
+            tma_load_3d(sb, &tmap_b, full, kb * BK, n * BN, e);
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    } else if (warp == 1 && lane == 0) {
+      // ---------------------------------------------------------------- MMA issuer
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < sched.total && ok; t += gridDim.x) {
+        int mb, n;
+        sched.decode(t, mb, n);
+        const int e = __ldg(a.sorted_expert_ids + mb);
+        if (e < 0 || e >= a.experts) continue;
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!mbar_wait(smem_u32(&ctrl->tmem_empty[acc]), acc_phase ^ 1, abort_flag, a.status, 2)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag, a.status, 3)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t sa = smem_u32(smem + size_t(stage) * kStageBytes);
+          const uint64_t adesc = make_smem_desc(sa);
+          const uint64_t bdesc = make_smem_desc(sa + kATileBytes);
+          const uint32_t d_tmem = tmem_base + uint32_t(acc) * BN;
+#pragma unroll
+          for (int k = 0; k < BK / 32; ++k)
+            umma_f8(d_tmem, adesc + uint64_t(k * 2), bdesc + uint64_t(k * 2), kInstrDesc, k > 0 ? 1u : 0u);
+          umma_commit(smem_u32(&ctrl->empty[stage]));
+          umma_commit(smem_u32(&ctrl->tmem_full[acc]));
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+          if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
+        }
+      }
+    }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    // ------------------------------------------------------------------ epilogue
+    const int wg = (warp - 4) >> 2;          // 0 or 1
+    const int q = warp & 3;                  // TMEM lane quadrant of this warp
+    const int row_in_tile = q * 32 + lane;
+    const bool warp_active = q * 32 < a.tile_m;
+    const uint32_t lane_base = uint32_t(q * 32) << 16;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    uint32_t tile_iter = 0;
+    bool ok = true;
+    constexpr int NACC = 128;                // fp32 accumulators per thread
+    for (int t = blockIdx.x; t < sched.total && ok; t += gridDim.x) {
+      int mb, n;
+      sched.decode(t, mb, n);
+      const int e = __ldg(a.sorted_expert_ids + mb);
+      if (e < 0 || e >= a.experts) continue;
+
+      const int r = mb * a.tile_m + row_in_tile;
+      const bool in_tile = row_in_tile < a.tile_m && r < valid_rows;
+      int tok = 0, slot = 0;
+      bool valid = false;
+      if (in_tile) {
+        const int id = __ldg(a.sorted_ids + r);
+        tok = id_token(id);
+        slot = id_slot(id);
+        valid = tok < a.num_tokens && slot < a.topk;
+      }
+      long long sidx = 0;
+      if (valid) {
+        sidx = a.a_scale_layout == FLYMOE_ROWS_BY_TOKEN ? (long long)tok
+             : a.a_scale_layout == FLYMOE_ROWS_BY_PAIR ? (long long)tok * a.topk + slot : (long long)r;
+      }
+      const float* sa_ptr = a.scale_a + sidx;
+      // weight block scales of this tile
+      const int wblk_per_expert = (STAGE == 1 ? 2 * a.n_dim : a.n_dim) / 128;
+      const int blk0 = STAGE == 1 ? n : n * 2 + wg;
+      const int blk1 = STAGE == 1 ? a.n_dim / 128 + n : blk0;
+      const bool half_ok = STAGE == 1 ? true : (n * BN + wg * 128 < a.n_dim);
+      const float* sw0_ptr = a.scale_w + ((long long)e * wblk_per_expert + (half_ok ? blk0 : 0)) * KB;
+      const float* sw1_ptr = a.scale_w + ((long long)e * wblk_per_expert + blk1) * KB;
+
+      float accv[NACC];
+#pragma unroll
+      for (int j = 0; j < NACC; ++j) accv[j] = 0.f;
+
+      float sa_next = valid ? __ldg(sa_ptr) : 0.f;
+      float s0_next = __ldg(sw0_ptr);
+      float s1_next = STAGE == 1 ? __ldg(sw1_ptr) : 0.f;
+      for (int kb = 0; kb < KB; ++kb) {
+        const float c0 = sa_next * s0_next;
+        const float c1 = sa_next * s1_next;
+        if (kb + 1 < KB) {
+          sa_next = valid ? __ldg(sa_ptr + (long long)(kb + 1) * a.sa_stride) : 0.f;
+          s0_next = __ldg(sw0_ptr + kb + 1);
+          if (STAGE == 1) s1_next = __ldg(sw1_ptr + kb + 1);
+        }
+        if (!mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, abort_flag, a.status, 4)) { ok = false; break; }
+        tcgen05_fence_after();
+        if (warp_active && half_ok) {
+          const uint32_t tbase = tmem_base + lane_base + uint32_t(acc) * BN;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            // stage 1: h=0 gate columns, h=1 up columns; stage 2: two halves of 128 columns
+            const uint32_t col = STAGE == 1 ? uint32_t(h * 128 + wg * 64) : uint32_t(wg * 128 + h * 64);
+            const float c = (STAGE == 1 && h == 1) ? c1 : c0;
+            uint32_t v[64];
+            tmem_ld_x32(tbase + col, v);
+            tmem_ld_x32(tbase + col + 32, v + 32);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 64; ++j) accv[h * 64 + j] = fmaf(__uint_as_float(v[j]), c, accv[h * 64 + j]);
+          }
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&ctrl->tmem_empty[acc]));
+        if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
+      }
+      if (!ok) break;
+
+      // ---- tile epilogue -----------------------------------------------------------
+      const float wgt = (a.doweight && valid) ? __ldg(a.sorted_weights + r) : 1.f;
+      if (STAGE == 1) {
+        // accv[0..63] = gate, accv[64..127] = up, columns n*128 + wg*64 + j
+        float amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 64; ++j) {
+          const float hval = valid ? silu_f32(accv[j]) * accv[64 + j] * wgt : 0.f;
+          accv[j] = hval;
+          amax = fmaxf(amax, fabsf(hval));
+        }
+        const long long orow = a.out_layout == FLYMOE_ROWS_SORTED ? (long long)r : (long long)tok * a.topk + slot;
+        const long long ocol = (long long)n * 128 + wg * 64;
+        if (a.out_dtype == FLYMOE_E4M3) {
+          const int buf = tile_iter & 1;
+          const uint32_t bar = smem_u32(&ctrl->amax_bar[buf]);
+          if (warp_active) ctrl->amax[buf][wg][row_in_tile] = amax;
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar);
+          if (!mbar_wait(bar, (tile_iter >> 1) & 1, abort_flag, a.status, 5)) { ok = false; break; }
+          const bool wr = warp_active && (valid || (in_tile && a.out_layout == FLYMOE_ROWS_SORTED));
+          if (wr) {
+            const float m = fmaxf(ctrl->amax[buf][0][row_in_tile], ctrl->amax[buf][1][row_in_tile]);
+            float sc = __fdiv_rn(m, 448.0f);
+            if (sc == 0.f) sc = 1.f;
+            uint8_t* op = static_cast<uint8_t*>(a.out) + orow * a.n_dim + ocol;
+#pragma unroll
+            for (int j = 0; j < 64; j += 16) {
+              uint4 pk;
+              pk.x = float4_to_e4m3x4(__fdiv_rn(accv[j + 0], sc), __fdiv_rn(accv[j + 1], sc),
+                                      __fdiv_rn(accv[j + 2], sc), __fdiv_rn(accv[j + 3], sc));
+              pk.y = float4_to_e4m3x4(__fdiv_rn(accv[j + 4], sc), __fdiv_rn(accv[j + 5], sc),
+                                      __fdiv_rn(accv[j + 6], sc), __fdiv_rn(accv[j + 7], sc));
+              pk.z = float4_to_e4m3x4(__fdiv_rn(accv[j + 8], sc), __fdiv_rn(accv[j + 9], sc),
+                                      __fdiv_rn(accv[j + 10], sc), __fdiv_rn(accv[j + 11], sc));
+              pk.w = float4_to_e4m3x4(__fdiv_rn(accv[j + 12], sc), __fdiv_rn(accv[j + 13], sc),
+                                      __fdiv_rn(accv[j + 14], sc), __fdiv_rn(accv[j + 15], sc));
+              *reinterpret_cast<uint4*>(op + j) = pk;
+            }
+            if (wg == 0) a.out_scale[(long long)n * a.out_scale_stride + orow] = sc;
+          }
+        } else if (warp_active && valid) {
+          uint8_t* op = static_cast<uint8_t*>(a.out) + (orow * a.n_dim + ocol) * 2;
+          const bool bf = a.out_dtype == FLYMOE_BF16;
+#pragma unroll
+          for (int j = 0; j < 64; j += 8) {
+            uint4 pk;
+            pk.x = bf ? pack_bf16x2(accv[j + 0], accv[j + 1]) : pack_f16x2(accv[j + 0], accv[j + 1]);
+            pk.y = bf ? pack_bf16x2(accv[j + 2], accv[j + 3]) : pack_f16x2(accv[j + 2], accv[j + 3]);
+            pk.z = bf ? pack_bf16x2(accv[j + 4], accv[j + 5]) : pack_f16x2(accv[j + 4], accv[j + 5]);
+            pk.w = bf ? pack_bf16x2(accv[j + 6], accv[j + 7]) : pack_f16x2(accv[j + 6], accv[j + 7]);
+            *reinterpret_cast<uint4*>(op + j * 2) = pk;
+          }
+        }
+      } else if (warp_active && valid && half_ok) {
+        // accv[0..127]: columns n*256 + wg*128 + j
+        const long long ocol = (long long)n * BN + wg * 128;
+        if (a.accumulate) {
+          const long long o = (long long)tok * a.n_dim + ocol;
+          if (a.out_dtype == FLYMOE_F32) {
+            float* op = static_cast<float*>(a.out) + o;
+#pragma unroll
+            for (int j = 0; j < 128; j += 4)
+              red_add_v4_f32(op + j, accv[j] * wgt, accv[j + 1] * wgt, accv[j + 2] * wgt, accv[j + 3] * wgt);
+          } else {
+            uint8_t* op = static_cast<uint8_t*>(a.out) + o * 2;
+            const bool bf = a.out_dtype == FLYMOE_BF16;
+#pragma unroll
+            for (int j = 0; j < 128; j += 8) {
+              if (bf)
+                red_add_v4_bf16x2(op + j * 2, pack_bf16x2(accv[j] * wgt, accv[j + 1] * wgt),
+                                  pack_bf16x2(accv[j + 2] * wgt, accv[j + 3] * wgt),
+                                  pack_bf16x2(accv[j + 4] * wgt, accv[j + 5] * wgt),
+                                  pack_bf16x2(accv[j + 6] * wgt, accv[j + 7] * wgt));
+              else
+                red_add_v4_f16x2(op + j * 2, pack_f16x2(accv[j] * wgt, accv[j + 1] * wgt),
+                                 pack_f16x2(accv[j + 2] * wgt, accv[j + 3] * wgt),
+                                 pack_f16x2(accv[j + 4] * wgt, accv[j + 5] * wgt),
+                                 pack_f16x2(accv[j + 6] * wgt, accv[j + 7] * wgt));
+            }
+          }
+        } else {
+          const long long o = ((long long)tok * a.topk + slot) * a.n_dim + ocol;
+          uint8_t* op = static_cast<uint8_t*>(a.out) + o * 2;
+          const bool bf = a.out_dtype == FLYMOE_BF16;
+#pragma unroll
+          for (int j = 0; j < 128; j += 8) {
+            uint4 pk;
+            pk.x = bf ? pack_bf16x2(accv[j] * wgt, accv[j + 1] * wgt) : pack_f16x2(accv[j] * wgt, accv[j + 1] * wgt);
+            pk.y = bf ? pack_bf16x2(accv[j + 2] * wgt, accv[j + 3] * wgt) : pack_f16x2(accv[j + 2] * wgt, accv[j + 3] * wgt);
+            pk.z = bf ? pack_bf16x2(accv[j + 4] * wgt, accv[j + 5] * wgt) : pack_f16x2(accv[j + 4] * wgt, accv[j + 5] * wgt);
+            pk.w = bf ? pack_bf16x2(accv[j + 6] * wgt, accv[j + 7] * wgt) : pack_f16x2(accv[j + 6] * wgt, accv[j + 7] * wgt);
+            *reinterpret_cast<uint4*>(op + j * 2) = pk;
+          }
+        }
+      }
+      ++tile_iter;
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(uint32_t(kTmemCols))
+                 : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------ host
+static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &p, 12000, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+  }
+  return fn;
+}
+
+static int make_map(CUtensorMap* map, const void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides,
+                    const cuuint32_t* box) {
+  PFN_cuTensorMapEncodeTiled_v12000 fn = encode_fn();
+  if (fn == nullptr) {
+    set_last_error_msg("cuTensorMapEncodeTiled is not available from this driver");
+    return FLYMOE_ERR_CUDA;
+  }
+  cuuint32_t elem_strides[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, rank, const_cast<void*>(base), dims, strides, box, elem_strides,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[128];
+    snprintf(buf, sizeof(buf), "cuTensorMapEncodeTiled failed with CUresult %d", int(r));
+    set_last_error_msg(buf);
+    return FLYMOE_ERR_CUDA;
+  }
+  return FLYMOE_OK;
+}
+
+int launch_gemm_sm100(int stage, const GemmArgs& a, cudaStream_t stream) {
+  if (a.tile_m != 16 && a.tile_m != 32 && a.tile_m != 64 && a.tile_m != 128) {
+    set_last_error_msg("tcgen05 GEMM: tile_m must be 16, 32, 64 or 128");
+    return FLYMOE_ERR_UNSUPPORTED;
+  }
+  if (a.a_layout != FLYMOE_ROWS_SORTED) {
+    set_last_error_msg("tcgen05 GEMM: activations must be in sorted-row order (use flymoe_gather_rows)");
+    return FLYMOE_ERR_UNSUPPORTED;
+  }
+  const long long wrows = stage == 1 ? 2LL * a.n_dim : a.n_dim;
+  CUtensorMap map_a, map_b;
+  {
+    cuuint64_t dims[2] = {cuuint64_t(a.k_dim), cuuint64_t(a.a_rows)};
+    cuuint64_t strides[1] = {cuuint64_t(a.k_dim)};
+    cuuint32_t box[2] = {cuuint32_t(BK), cuuint32_t(a.tile_m)};
+    int rc = make_map(&map_a, a.a, 2, dims, strides, box);
+    if (rc != FLYMOE_OK) return rc;
+  }
+  {
+    cuuint64_t dims[3] = {cuuint64_t(a.k_dim), cuuint64_t(wrows), cuuint64_t(a.experts)};
+    cuuint64_t strides[2] = {cuuint64_t(a.k_dim), cuuint64_t(wrows) * cuuint64_t(a.k_dim)};
+    cuuint32_t box[3] = {cuuint32_t(BK), cuuint32_t(stage == 1 ? 128 : BN), 1};
+    int rc = make_map(&map_b, a.w, 3, dims, strides, box);
+    if (rc != FLYMOE_OK) return rc;
+  }
+  const long long pairs = (long long)a.num_tokens * a.topk;
+  long long g = (pairs + (long long)a.experts * a.tile_m - 1) / ((long long)a.experts * a.tile_m);
+  const int group_m = int(g < 1 ? 1 : (g > 16 ? 16 : g));
+  const int ntiles = stage == 1 ? a.n_dim / 128 : ceil_div(a.n_dim, BN);
+  const long long max_tiles = (long long)a.size_expert_ids * ntiles;
+  const int grid = int(max_tiles < sm_count() ? max_tiles : sm_count());
+  if (grid <= 0) return FLYMOE_OK;
+  if (stage == 1) {
+    FLYMOE_CUDA_CHECK(cudaFuncSetAttribute(moe_gemm_sm100_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           int(kSmemBytes)));
+    moe_gemm_sm100_kernel<1><<<grid, kNumThreads, kSmemBytes, stream>>>(map_a, map_b, a, group_m);
+  } else {
+    FLYMOE_CUDA_CHECK(cudaFuncSetAttribute(moe_gemm_sm100_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           int(kSmemBytes)));
+    moe_gemm_sm100_kernel<2><<<grid, kNumThreads, kSmemBytes, stream>>>(map_a, map_b, a, group_m);
+  }
+  FLYMOE_CUDA_CHECK(cudaGetLastError());
+  return FLYMOE_OK;
+}
+
+}  // namespace flymoe

@@ -1,0 +1,149 @@
+/* flymoe_sm100 — C ABI of the B200 (sm_100a) FP8 block-scaled fused-MoE library.
+ *
+ * Every entry point takes raw device pointers, explicit sizes and a CUDA stream
+ * (cudaStream_t passed as void*), enqueues work on that stream and returns
+ * immediately: no host synchronisation and no allocation on the call path.  The
+ * caller owns every buffer, including scratch.  Return value: 0 on success or a
+ * negative FLYMOE_ERR_* code; flymoe_last_error() gives the text for the calling
+ * thread.  No C++ exceptions cross this boundary.
+ *
+ * Each declaration cites the interface of the reference project (FlyDSL) that it
+ * replaces, by file:line inside that project.
+ */
+#ifndef FLYMOE_H_
+#define FLYMOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FLYMOE_ABI_VERSION 1
+
+#define FLYMOE_OK 0
+#define FLYMOE_ERR_INVALID_ARGUMENT (-1)
+#define FLYMOE_ERR_CUDA (-2)
+#define FLYMOE_ERR_UNSUPPORTED (-3)
+#define FLYMOE_ERR_WORKSPACE (-4)
+#define FLYMOE_ERR_DEVICE_TIMEOUT (-5)
+
+/* element types */
+#define FLYMOE_F32 0
+#define FLYMOE_F16 1
+#define FLYMOE_BF16 2
+#define FLYMOE_E4M3 3
+
+/* row layouts of an activation matrix that is indexed through the sorted-id list */
+#define FLYMOE_ROWS_BY_TOKEN 0 /* row = token id                     (stage-1 input)   */
+#define FLYMOE_ROWS_BY_PAIR 1  /* row = token*topk + slot            (reference layout) */
+#define FLYMOE_ROWS_SORTED 2   /* row = position in the sorted list  (fused layer)      */
+
+/* GEMM implementations */
+#define FLYMOE_IMPL_TCGEN05 0 /* TMA + tcgen05.mma + TMEM (the product path)             */
+#define FLYMOE_IMPL_SIMT 1    /* plain CUDA-core kernel, used to cross-check on the GPU */
+
+int flymoe_abi_version(void);
+const char* flymoe_error_string(int code);
+const char* flymoe_last_error(void);
+
+/* Reads (with a device synchronisation) and clears the device-side status word that
+ * kernels set when a bounded wait gives up.  0 = no kernel reported a problem. */
+int flymoe_device_status(int* status_out);
+
+/* Top-k softmax gating.
+ * Replaces kernels/topk_gating_softmax_kernel.py:54-59 (builder) and the launcher
+ * :336-344 (GatingOutput, TopkWeights, TopkIndices, TokenExpertIndices, num_tokens, stream).
+ * gating [T,E] of gating_dtype (F32/F16/BF16), row-major.  topk_weights f32 [T,k],
+ * topk_indices i32 [T,k] (descending by logit, ties to the lower expert id),
+ * token_expert_indices i32 [T,k] = k_idx*T + t. */
+int flymoe_topk_gating_softmax(const void* gating, int gating_dtype, float* topk_weights,
+                               int32_t* topk_indices, int32_t* token_expert_indices,
+                               int num_tokens, int num_experts, int topk, int renormalize,
+                               void* stream);
+
+/* Scratch (int32 elements) flymoe_moe_sorting needs for this problem; 0 when the
+ * single-block path is taken.  Replaces kernels/moe_sorting_kernel.py:1588-1598. */
+int64_t flymoe_moe_sorting_workspace_elems(int num_tokens, int num_experts, int topk,
+                                           int unit_size);
+
+/* Token-to-expert counting sort with per-expert padding to unit_size rows.
+ * Replaces kernels/moe_sorting_kernel.py:1628-1772 (moe_sorting_flydsl).
+ * topk_ids i32 [T,k], topk_weights f32 [T,k]; outputs (caller-allocated):
+ * sorted_ids i32 [T*k + E*unit - k] packed (slot<<24)|token with pad (k<<24)|T,
+ * sorted_weights f32 (same length, pads 0), sorted_expert_ids i32 [ceil(len/unit)]
+ * (local expert index under expert_mask, -1 beyond the valid blocks),
+ * num_valid_ids i32 [2] = {padded row count, T}.  moe_buf (may be NULL) is zeroed
+ * over moe_buf_bytes.  expert_mask i32 [E] or NULL.  workspace: int32 scratch of at
+ * least flymoe_moe_sorting_workspace_elems() elements (may be NULL when that is 0). */
+int flymoe_moe_sorting(const int32_t* topk_ids, const float* topk_weights, int32_t* sorted_ids,
+                       float* sorted_weights, int32_t* sorted_expert_ids, int32_t* num_valid_ids,
+                       void* moe_buf, int64_t moe_buf_bytes, const int32_t* expert_mask,
+                       int32_t* workspace, int64_t workspace_elems, int num_tokens,
+                       int num_experts, int topk, int unit_size, void* stream);
+
+/* Copies rows of a one-byte-element matrix into sorted order: dst row r = src row
+ * selected by sorted_ids[r] under src_layout (BY_TOKEN or BY_PAIR); pad rows are
+ * zero-filled; rows at or beyond num_valid_ids[0] are left untouched.
+ * Replaces the in-kernel gather of kernels/moe_blockscale_2stage.py:401-427 and
+ * :1576-1590 (the tensor-core kernels here read contiguous sorted rows by TMA). */
+int flymoe_gather_rows(const void* src, void* dst, const int32_t* sorted_ids,
+                       const int32_t* num_valid_ids, int num_tokens, int topk, int row_bytes,
+                       int src_layout, int max_rows, void* stream);
+
+/* Stage 1: gate/up grouped FP8 GEMM over sorted rows + SiLU(gate)*up.
+ * Replaces kernels/moe_blockscale_2stage.py:70-84 (builder) and the launcher
+ * :1142-1157.  x e4m3: [T,H] when x_layout==BY_TOKEN and impl==SIMT, else the
+ * gathered [rows,H] matrix in sorted order (flymoe_gather_rows).  scale_x f32
+ * [H/128, sx_stride] indexed by token (x_scale_layout BY_TOKEN) or sorted row.
+ * w e4m3 [E,2I,H] row-major (gate rows first), scale_w f32 [E,2I/128,H/128].
+ * out: out_dtype F16/BF16 -> [rows,I] values; E4M3 -> codes [rows,I] plus
+ * out_scale f32 [I/128, out_scale_stride] (the per-1x128 requantisation that the
+ * reference performs outside the kernel, tests/kernels/test_moe_blockscale.py:447-452).
+ * out_layout BY_PAIR (reference) or SORTED.  tile_m = sort unit (16/32/64/128). */
+int flymoe_moe_gemm1(void* out, float* out_scale, int64_t out_scale_stride, const void* x,
+                     const float* scale_x, int64_t sx_stride, const void* w, const float* scale_w,
+                     const int32_t* sorted_ids, const int32_t* sorted_expert_ids,
+                     const float* sorted_weights, const int32_t* num_valid_ids, int num_tokens,
+                     int inter_dim, int model_dim, int size_expert_ids, int experts, int topk,
+                     int tile_m, int doweight, int out_dtype, int x_layout, int x_scale_layout,
+                     int out_layout, int impl, void* stream);
+
+/* Stage 2: down-projection grouped FP8 GEMM + top-k-weighted scatter-reduce.
+ * Replaces kernels/moe_blockscale_2stage.py:1189-1207 (builder) and the launcher
+ * :2335-2350.  a2 e4m3 [rows,I] under a_layout (BY_PAIR for SIMT, else sorted rows);
+ * scale_a f32 [I/128, sa_stride] indexed under a_scale_layout (BY_PAIR or SORTED).
+ * w e4m3 [E,H,I], scale_w f32 [E,H/128,I/128].  accumulate!=0: out [T,H] of
+ * out_dtype (F16/BF16/F32), pre-zeroed, receives atomic adds; accumulate==0: out
+ * [T*k,H] rows t*k+s receive plain stores (F16/BF16 only). */
+int flymoe_moe_gemm2(void* out, const void* a2, const float* scale_a, int64_t sa_stride,
+                     const void* w, const float* scale_w, const int32_t* sorted_ids,
+                     const int32_t* sorted_expert_ids, const float* sorted_weights,
+                     const int32_t* num_valid_ids, int num_tokens, int model_dim, int inter_dim,
+                     int size_expert_ids, int experts, int topk, int tile_m, int doweight,
+                     int out_dtype, int accumulate, int a_layout, int a_scale_layout, int impl,
+                     void* stream);
+
+/* Y[t,:] = sum_s X[t,s,:] with fp32 accumulation; optional u8 valid_mask [T,k] and
+ * optional f32 weights [T,k].  Replaces kernels/moe_blockscale_2stage.py:2383-2589. */
+int flymoe_moe_reduce(const void* x, void* y, const uint8_t* valid_mask, const float* weights,
+                      int num_tokens, int topk, int model_dim, int dtype, void* stream);
+
+/* Per-row, per-128-column FP8 quantiser: x [R,K] F16/BF16/F32 -> q e4m3 [R,K] and
+ * scale f32 stored transposed [K/128, scale_stride] (scale = amax/448, 0 -> 1).
+ * Replaces the test-side quantiser tests/utils.py:29-73 as used at
+ * tests/kernels/test_moe_blockscale.py:354-367. */
+int flymoe_quant_act_1x128(const void* x, int x_dtype, void* q, float* scale, int64_t scale_stride,
+                           int rows, int cols, void* stream);
+
+/* Converts weights between the reference's 16x16 preshuffle order
+ * (tests/utils.py:76-96; kernels/mfma_preshuffle_pipeline.py:168-225) and plain
+ * row-major [E*N, K]; to_plain!=0 undoes the shuffle.  src != dst. */
+int flymoe_shuffle_weight(const void* src, void* dst, int64_t rows, int cols, int to_plain,
+                          void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLYMOE_H_ */

@@ -1,0 +1,255 @@
+"""CPU oracle for the FP8 block-scaled fused-MoE path.  TEST INFRASTRUCTURE ONLY.
+
+This module restates, in plain torch/numpy on the CPU, the algorithm that the
+reference project uses as its own correctness oracle for this path.  It is the
+checker for the CUDA kernels: only the test-suite, the smoke check and the CPU
+baseline leg of the benchmark may import it.  Nothing in the shipped package
+imports it, and the shipped package has no CPU fallback.
+
+Parity pin: every function below is compared, on seeded inputs, against the
+reference's own torch functions executed from the reference checkout (see
+``tests/golden/make_golden.py``, which lifts those functions at generation
+time and stores their outputs as fixtures).
+
+Reference locations each function follows (paths inside the reference project):
+
+* gating          tests/kernels/test_topk_gating_softmax.py:84-94 (softmax ->
+                  top-k -> renormalise), tie rule (lower expert id wins) from
+                  kernels/topk_gating_softmax_kernel.py:156-174, eps :315-317,
+                  token_expert_indices convention :331-333
+* sorting         tests/kernels/test_moe_sorting.py:69-105
+* quantisers      tests/utils.py:29-73 (pertoken_quant),
+                  tests/kernels/test_moe_blockscale.py:269-276 (128x128 blocks)
+* weight shuffle  tests/utils.py:76-96
+* stage 1         tests/kernels/test_moe_blockscale.py:76-112
+* requant         tests/kernels/test_moe_blockscale.py:447-452
+* stage 2         tests/kernels/test_moe_blockscale.py:115-150
+* top-k reduce    tests/kernels/test_moe_reduce.py:88-93
+
+Differences from the reference text, all value-preserving: weights are
+dequantised one expert at a time (the reference expands every expert to fp32
+at once), and the top-k selection is made on the raw fp32 logits with a stable
+sort so that ties and probability collapses resolve to the lower expert id on
+every machine.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+FP8 = torch.float8_e4m3fn
+FP8_MAX = 448.0
+BLK = 128
+
+
+# --------------------------------------------------------------------------- gating
+def topk_gating_softmax(logits: torch.Tensor, topk: int, renormalize: bool = True):
+    """softmax over experts, pick the k largest (ties -> lower id), renormalise.
+
+    Returns (weights f32 [T,k], indices i32 [T,k], token_expert_indices i32 [T,k]).
+    """
+    x = logits.to(torch.float32)
+    T, _E = x.shape
+    probs = torch.softmax(x, dim=1)
+    order = torch.sort(x, dim=1, descending=True, stable=True).indices
+    idx = order[:, :topk].contiguous()
+    w = torch.gather(probs, 1, idx)
+    if renormalize:
+        w = w / w.sum(dim=1, keepdim=True).clamp(min=1e-20)
+    tei = (torch.arange(topk, dtype=torch.int32).view(1, topk) * T
+           + torch.arange(T, dtype=torch.int32).view(T, 1))
+    return w.to(torch.float32), idx.to(torch.int32), tei.to(torch.int32)
+
+
+def gating_prob_rule_differs(logits: torch.Tensor, topk: int) -> int:
+    """Number of rows where 'top-k on fp32 probabilities' selects a different set."""
+    x = logits.to(torch.float32)
+    probs = torch.softmax(x, dim=1)
+    a = torch.sort(x, dim=1, descending=True, stable=True).indices[:, :topk]
+    b = torch.sort(probs, dim=1, descending=True, stable=True).indices[:, :topk]
+    return int((a.sort(dim=1).values != b.sort(dim=1).values).any(dim=1).sum())
+
+
+# --------------------------------------------------------------------------- sorting
+def moe_sorting(topk_ids, topk_weights, num_experts: int, unit_size: int = 32,
+                expert_mask=None):
+    """Stable counting sort of (token, slot) pairs by expert with block padding.
+
+    Returns numpy arrays (sorted_ids i32 [Rmax], sorted_weights f32 [Rmax],
+    sorted_expert_ids i32 [B], num_valid_ids i32 [2]).  Packed id = slot<<24 | token,
+    pad sentinel = topk<<24 | T, unused block ids = -1.
+    """
+    ids = np.asarray(topk_ids, dtype=np.int64)
+    wts = np.asarray(topk_weights, dtype=np.float32)
+    M, topk = ids.shape
+    rmax = ids.size + num_experts * unit_size - topk
+    nblk = (rmax + unit_size - 1) // unit_size
+    sentinel = (topk << 24) | M
+    sorted_ids = np.full((rmax,), sentinel, dtype=np.int32)
+    sorted_w = np.zeros((rmax,), dtype=np.float32)
+    sorted_e = np.full((nblk,), -1, dtype=np.int32)
+    nvalid = np.zeros((2,), dtype=np.int32)
+    mask = None if expert_mask is None else np.asarray(expert_mask).astype(bool)
+
+    cur = 0
+    ecur = 0
+    skipped = 0
+    for e in range(num_experts):
+        if mask is not None and not mask[e]:
+            skipped += 1
+            continue
+        tok, slot = np.nonzero(ids == e)           # row-major: token ascending
+        cnt = tok.size
+        if cnt == 0:
+            continue
+        nb = (cnt + unit_size - 1) // unit_size
+        sorted_ids[cur:cur + cnt] = ((slot << 24) | tok).astype(np.int32)
+        sorted_w[cur:cur + cnt] = wts[tok, slot]
+        cur += nb * unit_size
+        sorted_e[ecur:ecur + nb] = e - skipped
+        ecur += nb
+    nvalid[0] = cur
+    nvalid[1] = M
+    return sorted_ids, sorted_w, sorted_e, nvalid
+
+
+# --------------------------------------------------------------------------- quantisers
+def pertoken_quant(x: torch.Tensor, quant_dtype=FP8, dtype_max: float | None = None):
+    """amax over the last dim / dtype max -> scale (0 -> 1); q = (x/scale).to(dtype)."""
+    x = x.to(torch.float32)
+    if dtype_max is None:
+        dtype_max = float(torch.finfo(quant_dtype).max)
+    x = torch.nan_to_num(x, nan=0.0, posinf=dtype_max, neginf=-dtype_max)
+    amax = torch.maximum(torch.amax(x, dim=-1, keepdim=True), -torch.amin(x, dim=-1, keepdim=True))
+    scale = amax / dtype_max
+    scale[scale == 0] = 1
+    scale = torch.nan_to_num(scale, nan=1.0, posinf=1.0, neginf=1.0)
+    q = (x / scale).to(quant_dtype)
+    return q, scale.to(torch.float32)
+
+
+def quant_act_1x128(x: torch.Tensor):
+    """[R,K] float -> (q e4m3 [R,K], scale f32 [R,K/128]) with 1x128 groups."""
+    R, K = x.shape
+    q, s = pertoken_quant(x.reshape(R, K // BLK, BLK))
+    return q.reshape(R, K), s.reshape(R, K // BLK)
+
+
+def quant_weight_128x128(w: torch.Tensor):
+    """[N,K] float -> (q e4m3 [N,K], scale f32 [N/128,K/128]) with 128x128 blocks."""
+    N, K = w.shape
+    nbn, nbk = N // BLK, K // BLK
+    t = w.to(torch.float32).view(nbn, BLK, nbk, BLK).permute(0, 2, 1, 3).reshape(nbn * nbk, BLK * BLK)
+    q, s = pertoken_quant(t)
+    q = q.view(nbn, nbk, BLK, BLK).permute(0, 2, 1, 3).reshape(N, K)
+    return q.contiguous(), s.view(nbn, nbk).contiguous()
+
+
+def shuffle_weight(w: torch.Tensor) -> torch.Tensor:
+    """[..., N, K] one-byte elements -> 16x16 preshuffle order (same shape)."""
+    assert w.element_size() == 1
+    N, K = w.shape[-2], w.shape[-1]
+    v = w.view(torch.uint8).reshape(-1, N // 16, 16, K // 32, 2, 16)
+    v = v.permute(0, 1, 3, 4, 2, 5).contiguous()
+    return v.view(*w.shape).view(w.dtype)
+
+
+def unshuffle_weight(w: torch.Tensor) -> torch.Tensor:
+    """Inverse of shuffle_weight."""
+    assert w.element_size() == 1
+    N, K = w.shape[-2], w.shape[-1]
+    v = w.view(torch.uint8).reshape(-1, N // 16, K // 32, 2, 16, 16)
+    v = v.permute(0, 1, 4, 2, 3, 5).contiguous()
+    return v.view(*w.shape).view(w.dtype)
+
+
+# --------------------------------------------------------------------------- GEMM stages
+def _dequant_w(wq_e: torch.Tensor, ws_e: torch.Tensor) -> torch.Tensor:
+    """One expert: e4m3 [N,K] * block scales [N/128,K/128] -> f32 [N,K]."""
+    N, K = wq_e.shape
+    s = ws_e.view(N // BLK, 1, K // BLK, 1).expand(N // BLK, BLK, K // BLK, BLK).reshape(N, K)
+    return wq_e.to(torch.float32) * s
+
+
+def _dequant_a(aq: torch.Tensor, a_scale: torch.Tensor) -> torch.Tensor:
+    R, K = aq.shape
+    return (aq.to(torch.float32).view(R, K // BLK, BLK) * a_scale.view(R, K // BLK, 1)).view(R, K)
+
+
+def stage1(xq, x_scale, w1q, w1_scale, topk_ids, inter_dim: int):
+    """silu(x W1g^T) * (x W1u^T) per (token, slot).  Returns f32 [T, k, I].
+
+    xq e4m3 [T,H]; x_scale f32 [T,H/128]; w1q e4m3 [E,2I,H];
+    w1_scale f32 [E,2I/128,H/128]; topk_ids [T,k].
+    """
+    T, _H = xq.shape
+    ids = torch.as_tensor(topk_ids).to(torch.int64)
+    k = ids.shape[1]
+    E = w1q.shape[0]
+    x = _dequant_a(xq, x_scale)
+    out = torch.zeros((T, k, inter_dim), dtype=torch.float32)
+    for e in range(E):
+        mask = ids == e
+        if mask.any():
+            tok = mask.nonzero()[:, 0]
+            act = x[tok] @ _dequant_w(w1q[e], w1_scale[e]).T
+            gate, up = act.split([inter_dim, inter_dim], dim=-1)
+            out[mask] = F.silu(gate) * up
+    return out
+
+
+def requant(out1: torch.Tensor, via_f16: bool = False):
+    """[T,k,I] f32 -> (a2q e4m3 [T*k,I], a2_scale f32 [T*k, I/128])."""
+    T, k, I = out1.shape
+    v = out1.to(torch.float16).to(torch.float32) if via_f16 else out1
+    return quant_act_1x128(v.reshape(T * k, I))
+
+
+def stage2(a2q, a2_scale, w2q, w2_scale, topk_ids, topk_weights, model_dim: int,
+           reduce: bool = True):
+    """out[t] = sum_s w[t,s] * (a2[t,s] W2_e^T).  Returns f32 [T,H] (or [T,k,H])."""
+    ids = torch.as_tensor(topk_ids).to(torch.int64)
+    T, k = ids.shape
+    E = w2q.shape[0]
+    I = a2q.shape[1]
+    a = _dequant_a(a2q, a2_scale).view(T, k, I)
+    out = torch.zeros((T, k, model_dim), dtype=torch.float32)
+    for e in range(E):
+        mask = ids == e
+        if mask.any():
+            out[mask] = a[mask] @ _dequant_w(w2q[e], w2_scale[e]).T
+    out = out * torch.as_tensor(topk_weights).to(torch.float32).view(T, k, 1)
+    return out.sum(dim=1) if reduce else out
+
+
+def topk_reduce(x: torch.Tensor, valid_mask=None) -> torch.Tensor:
+    """Y[t,:] = sum_s X[t,s,:] (fp32 accumulate), optional u8 mask [T,k]."""
+    v = x.to(torch.float32)
+    if valid_mask is not None:
+        v = v * valid_mask.to(torch.float32).unsqueeze(-1)
+    return v.sum(dim=1).to(x.dtype)
+
+
+def moe_layer(logits, xq, x_scale, w1q, w1_scale, w2q, w2_scale, topk: int,
+              out_dtype=torch.bfloat16, via_f16: bool = False):
+    """Whole path on identical pre-quantised inputs.  Returns a dict of every stage."""
+    I = w2q.shape[2]
+    H = w2q.shape[1]
+    w, idx, tei = topk_gating_softmax(logits, topk, True)
+    o1 = stage1(xq, x_scale, w1q, w1_scale, idx, I)
+    a2q, a2s = requant(o1, via_f16=via_f16)
+    o2 = stage2(a2q, a2s, w2q, w2_scale, idx, w, H)
+    return {"topk_weights": w, "topk_ids": idx, "tei": tei, "out1": o1,
+            "a2q": a2q, "a2_scale": a2s, "out": o2.to(out_dtype), "out_f32": o2}
+
+
+# --------------------------------------------------------------------------- comparisons
+def e4m3_ulp_distance(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """Distance in representable e4m3 steps between two code tensors (uint8 or fp8)."""
+    def ordinal(c):
+        c = c.view(torch.uint8).to(torch.int32)
+        mag = c & 0x7F
+        return torch.where((c & 0x80) != 0, -mag, mag)
+    return (ordinal(a) - ordinal(b)).abs()

@@ -1,0 +1,195 @@
+"""Generate the golden fixtures in this directory from the reference project's own code.
+
+Run once, in a container that has the reference checkout (default
+``/root/reference``, override with ``FLYMOE_REFERENCE_DIR``):
+
+    python tests/golden/make_golden.py
+
+The reference's torch oracles live in test files that import the (AMD-only)
+compiler at module level, so they cannot be imported; this script lifts the pure-torch
+functions out of those files by AST at generation time, executes them on seeded
+inputs and stores inputs/outputs as ``.npz``.  No reference source is copied into
+this repository; the fixtures hold only numbers.  The test-suite then checks the CPU
+oracle (``oracle/moe_oracle.py``) against these files, which pins the oracle to the
+reference's behaviour.
+
+Lifted functions (reference paths):
+  tests/kernels/test_moe_blockscale.py: _expand_blockscale, torch_stage1_blockscale_ref,
+      torch_stage2_blockscale_ref, torch_moe_blockscale_ref
+  tests/kernels/test_moe_sorting.py:    moe_sorting_reference
+  tests/utils.py (imported directly):   pertoken_quant, shuffle_weight
+Gating has no reference function; the fixture stores the result of the reference test's
+inline expression (softmax -> topk -> renormalise, test_topk_gating_softmax.py:84-89).
+"""
+
+from __future__ import annotations
+
+import ast
+import hashlib
+import importlib.util
+import math
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+HERE = Path(__file__).resolve().parent
+REPO = HERE.parent.parent
+REF = Path(os.environ.get("FLYMOE_REFERENCE_DIR", "/root/reference"))
+sys.path.insert(0, str(REPO))
+
+from flydsl_b200 import workloads as wl  # noqa: E402
+
+FP8 = torch.float8_e4m3fn
+
+
+def lift(path: Path, names: list[str], extra_globals: dict) -> dict:
+    tree = ast.parse(path.read_text())
+    wanted = [n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name in names]
+    missing = set(names) - {n.name for n in wanted}
+    if missing:
+        raise RuntimeError(f"{path}: functions not found: {sorted(missing)}")
+    mod = ast.Module(body=wanted, type_ignores=[])
+    ns = dict(extra_globals)
+    exec(compile(mod, str(path), "exec"), ns)
+    return {n: ns[n] for n in names}
+
+
+def import_file(path: Path, name: str):
+    spec = importlib.util.spec_from_file_location(name, path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def u8(t: torch.Tensor) -> np.ndarray:
+    return t.contiguous().view(torch.uint8).numpy()
+
+
+def bf16_bits(t: torch.Tensor) -> np.ndarray:
+    return t.contiguous().view(torch.int16).numpy()
+
+
+def sha(*arrays) -> str:
+    h = hashlib.sha256()
+    for a in arrays:
+        h.update(np.ascontiguousarray(a).tobytes())
+    return h.hexdigest()
+
+
+def main() -> None:
+    utils = import_file(REF / "tests" / "utils.py", "ref_tests_utils")
+    bs = lift(REF / "tests" / "kernels" / "test_moe_blockscale.py",
+              ["_expand_blockscale", "torch_stage1_blockscale_ref", "torch_stage2_blockscale_ref",
+               "torch_moe_blockscale_ref"], {"torch": torch, "F": F, "math": math})
+    srt = lift(REF / "tests" / "kernels" / "test_moe_sorting.py", ["moe_sorting_reference"],
+               {"torch": torch, "UNIT_SIZE": 32})
+    pertoken_quant, shuffle_weight = utils.pertoken_quant, utils.shuffle_weight
+
+    # ------------------------------------------------------------------ quantiser + shuffle
+    g = torch.Generator().manual_seed(11)
+    xs = torch.randn((24, 384), generator=g) * 3.0
+    xs[3, :128] = 0.0                       # an all-zero group -> scale 1
+    xs[5, 130] = 1e-9
+    q, s = pertoken_quant(xs.view(24, 3, 128), quant_dtype=FP8)
+    wq_small = (torch.randn((2, 64, 128), generator=g) * 50).to(FP8)
+    shuf = shuffle_weight(wq_small.clone(), layout=(16, 16))
+    np.savez_compressed(HERE / "quant_shuffle.npz", x=xs.numpy(), q=u8(q.view(24, 384)),
+                        scale=s.view(24, 3).numpy(), w=u8(wq_small), w_shuffled=u8(shuf))
+
+    # ------------------------------------------------------------------ sorting
+    sort_cases = [(1, 8, 2, 32, False), (7, 32, 5, 32, False), (31, 64, 6, 16, False), (64, 256, 8, 32, False),
+                  (16, 257, 9, 32, False), (128, 256, 8, 128, False), (300, 32, 5, 64, True),
+                  (1500, 256, 8, 128, False), (1500, 64, 6, 32, True)]
+    out = {}
+    for i, (T, E, k, unit, masked) in enumerate(sort_cases):
+        gg = torch.Generator().manual_seed(42 + T * 1000 + E * 10 + k)
+        ids = torch.stack([torch.randperm(E, generator=gg)[:k] for _ in range(T)]).to(torch.int32)
+        w = torch.rand((T, k), generator=gg, dtype=torch.float32)
+        mask = None
+        if masked:
+            mask = (torch.rand(E, generator=gg) < 0.5).to(torch.int32)
+            mask[0] = 1
+        a, b, c, d = srt["moe_sorting_reference"](ids, w, E, unit_size=unit, expert_mask=mask)
+        out[f"c{i}_cfg"] = np.array([T, E, k, unit, int(masked)], dtype=np.int32)
+        out[f"c{i}_ids"], out[f"c{i}_w"] = ids.numpy(), w.numpy()
+        if mask is not None:
+            out[f"c{i}_mask"] = mask.numpy()
+        out[f"c{i}_sorted_ids"], out[f"c{i}_sorted_w"] = a.numpy(), b.numpy()
+        out[f"c{i}_sorted_e"], out[f"c{i}_nvalid"] = c.numpy(), d.numpy()
+    out["n"] = np.array([len(sort_cases)], dtype=np.int32)
+    np.savez_compressed(HERE / "sorting.npz", **out)
+
+    # ------------------------------------------------------------------ gating
+    gate_cases = [(64, 8, 2, "f32", True), (64, 256, 8, "f32", True), (33, 128, 6, "bf16", True),
+                  (16, 64, 2, "f16", False)]
+    out = {}
+    for i, (T, E, k, dt, renorm) in enumerate(gate_cases):
+        gg = torch.Generator().manual_seed(1234 + i)
+        td = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[dt]
+        logits = (torch.rand((T, E), generator=gg) * 4.0 - 2.0).to(td)
+        lf = logits.to(torch.float32)
+        # rows whose k+1 largest probabilities are strictly decreasing leave torch.topk no tie freedom
+        probs = torch.softmax(lf, dim=1)
+        rw, ri = torch.topk(probs, k, dim=1)
+        if renorm:
+            rw = rw / rw.sum(dim=1, keepdim=True).clamp(min=1e-20)
+        top = torch.sort(probs, dim=1, descending=True).values[:, :min(k + 1, E)]
+        distinct = (top[:, :-1] > top[:, 1:]).all(dim=1)
+        out[f"g{i}_cfg"] = np.array([T, E, k, int(renorm)], dtype=np.int32)
+        out[f"g{i}_dtype"] = np.array([dt])
+        out[f"g{i}_logits_f32"] = lf.numpy()
+        out[f"g{i}_w"], out[f"g{i}_idx"] = rw.numpy(), ri.to(torch.int32).numpy()
+        out[f"g{i}_distinct"] = distinct.numpy()
+    out["n"] = np.array([len(gate_cases)], dtype=np.int32)
+    np.savez_compressed(HERE / "gating.npz", **out)
+
+    # ------------------------------------------------------------------ GEMM stages
+    def run_moe(cfg: wl.MoEConfig, store_inputs: bool, fname: str):
+        logits = wl.make_logits(cfg)
+        _x, xq, xs_ = wl.make_activations(cfg)
+        w1q, w1s, w2q, w2s = wl.make_weights(cfg)
+        # routing exactly as the reference test does it for given scores: topk then softmax is its
+        # own choice; here the routing under test is softmax -> topk -> renormalise
+        probs = torch.softmax(logits, dim=1)
+        tw, ti = torch.topk(probs, cfg.topk, dim=1)
+        tw = (tw / tw.sum(dim=1, keepdim=True)).to(torch.float32)
+        I, H = cfg.inter_dim, cfg.model_dim
+        out1 = bs["torch_stage1_blockscale_ref"](xq, w1q, ti, xs_, w1s.view(cfg.experts, -1), (128, 128), I)
+        out1_f16 = out1.to(torch.float16)
+        a2q_f16, a2s_f16 = pertoken_quant(out1_f16.float().view(-1, I // 128, 128), quant_dtype=FP8)
+        a2q_f32, a2s_f32 = pertoken_quant(out1.view(-1, I // 128, 128), quant_dtype=FP8)
+        a2q_f16, a2s_f16 = a2q_f16.view(-1, I), a2s_f16.squeeze(-1)
+        a2q_f32, a2s_f32 = a2q_f32.view(-1, I), a2s_f32.squeeze(-1)
+        out2_f16 = bs["torch_stage2_blockscale_ref"](a2q_f16, w2q, ti, tw, a2s_f16, w2s.view(cfg.experts, -1),
+                                                     (128, 128), cfg.tokens, H, I, cfg.topk)
+        out2_f32 = bs["torch_stage2_blockscale_ref"](a2q_f32, w2q, ti, tw, a2s_f32, w2s.view(cfg.experts, -1),
+                                                     (128, 128), cfg.tokens, H, I, cfg.topk)
+        fused = bs["torch_moe_blockscale_ref"](xq, w1q, w2q, tw, ti, torch.bfloat16, (128, 128), xs_,
+                                               w1s.view(cfg.experts, -1), w2s.view(cfg.experts, -1))
+        rec = {
+            "cfg": np.array([cfg.tokens, cfg.model_dim, cfg.inter_dim, cfg.experts, cfg.topk, cfg.seed], dtype=np.int32),
+            "input_sha": np.array([sha(logits.numpy(), u8(xq), xs_.numpy(), u8(w1q), w1s.numpy(), u8(w2q), w2s.numpy())]),
+            "topk_ids": ti.to(torch.int32).numpy(), "topk_weights": tw.numpy(),
+            "out1": out1.numpy(),
+            "a2q_via_f16": u8(a2q_f16), "a2_scale_via_f16": a2s_f16.numpy(),
+            "a2q_from_f32": u8(a2q_f32), "a2_scale_from_f32": a2s_f32.numpy(),
+            "out2_via_f16": out2_f16.numpy(), "out2_from_f32": out2_f32.numpy(),
+            "fused_bf16_bits": bf16_bits(fused),
+        }
+        if store_inputs:
+            rec.update({"logits": logits.numpy(), "xq": u8(xq), "x_scale": xs_.numpy(), "w1q": u8(w1q),
+                        "w1_scale": w1s.numpy(), "w2q": u8(w2q), "w2_scale": w2s.numpy()})
+        np.savez_compressed(HERE / fname, **rec)
+
+    run_moe(wl.MoEConfig("mini", 16, 256, 128, 4, 2, 7), True, "moe_mini.npz")
+    run_moe(wl.CONFIGS["c1"], False, "moe_c1.npz")
+    for f in sorted(HERE.glob("*.npz")):
+        print(f.name, f.stat().st_size)
+
+
+if __name__ == "__main__":
+    main()

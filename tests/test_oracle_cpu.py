@@ -1,0 +1,104 @@
+"""The CPU oracle against the golden fixtures produced by the reference's own functions."""
+import numpy as np
+import torch
+
+from flydsl_b200 import workloads as wl
+from oracle import moe_oracle as orc
+from tests import helpers as hp
+
+
+def test_pertoken_quant_and_shuffle_match_reference():
+    g = hp.load("quant_shuffle.npz")
+    x = torch.from_numpy(g["x"])
+    q, s = orc.quant_act_1x128(x)
+    assert np.array_equal(hp.u8(q), g["q"])
+    assert np.array_equal(s.numpy(), g["scale"])
+    # the workload generator's quantiser is the same function
+    q2, s2 = wl.quant_act_1x128(x)
+    assert np.array_equal(hp.u8(q2), g["q"]) and np.array_equal(s2.numpy(), g["scale"])
+    w = hp.fp8_from_u8(g["w"])
+    shuf = orc.shuffle_weight(w)
+    assert np.array_equal(hp.u8(shuf), g["w_shuffled"])
+    assert np.array_equal(hp.u8(orc.unshuffle_weight(shuf)), g["w"])
+
+
+def test_sorting_matches_reference():
+    g = hp.load("sorting.npz")
+    for i in range(int(g["n"][0])):
+        T, E, k, unit, masked = (int(v) for v in g[f"c{i}_cfg"])
+        mask = g[f"c{i}_mask"] if masked else None
+        a, b, c, d = orc.moe_sorting(g[f"c{i}_ids"], g[f"c{i}_w"], E, unit, mask)
+        assert np.array_equal(a, g[f"c{i}_sorted_ids"]), (T, E, k, unit)
+        assert np.array_equal(b, g[f"c{i}_sorted_w"])
+        assert np.array_equal(c, g[f"c{i}_sorted_e"])
+        assert np.array_equal(d, g[f"c{i}_nvalid"])
+        ids, w, m = hp.gen_sort_inputs(T, E, k, bool(masked))
+        assert np.array_equal(ids.numpy(), g[f"c{i}_ids"]) and np.array_equal(w.numpy(), g[f"c{i}_w"])
+
+
+def test_gating_matches_reference_expression():
+    g = hp.load("gating.npz")
+    for i in range(int(g["n"][0])):
+        T, E, k, renorm = (int(v) for v in g[f"g{i}_cfg"])
+        logits = torch.from_numpy(g[f"g{i}_logits_f32"])
+        w, idx, tei = orc.topk_gating_softmax(logits, k, bool(renorm))
+        rows = torch.from_numpy(g[f"g{i}_distinct"])
+        assert rows.sum() > 0
+        assert torch.equal(idx[rows], torch.from_numpy(g[f"g{i}_idx"])[rows])
+        assert torch.allclose(w[rows], torch.from_numpy(g[f"g{i}_w"])[rows], atol=1e-7, rtol=1e-6)
+        exp_tei = torch.arange(k, dtype=torch.int32).view(1, k) * T + torch.arange(T, dtype=torch.int32).view(T, 1)
+        assert torch.equal(tei, exp_tei)
+        assert orc.gating_prob_rule_differs(logits, k) == 0
+
+
+def _check_moe(fname, cfg, stored_inputs):
+    g = hp.load(fname)
+    if stored_inputs:
+        logits = torch.from_numpy(g["logits"])
+        xq, xs = hp.fp8_from_u8(g["xq"]), torch.from_numpy(g["x_scale"])
+        w1q, w1s = hp.fp8_from_u8(g["w1q"]), torch.from_numpy(g["w1_scale"])
+        w2q, w2s = hp.fp8_from_u8(g["w2q"]), torch.from_numpy(g["w2_scale"])
+    logits_g = wl.make_logits(cfg)
+    _x, xq_g, xs_g = wl.make_activations(cfg)
+    w1q_g, w1s_g, w2q_g, w2s_g = wl.make_weights(cfg)
+    digest = hp.sha(logits_g.numpy(), hp.u8(xq_g), xs_g.numpy(), hp.u8(w1q_g), w1s_g.numpy(), hp.u8(w2q_g),
+                    w2s_g.numpy())
+    assert digest == str(g["input_sha"][0]), "seeded generator no longer reproduces the fixture inputs"
+    if not stored_inputs:
+        logits, xq, xs, w1q, w1s, w2q, w2s = logits_g, xq_g, xs_g, w1q_g, w1s_g, w2q_g, w2s_g
+    else:
+        assert torch.equal(logits, logits_g) and np.array_equal(hp.u8(xq), hp.u8(xq_g))
+    res = orc.moe_layer(logits, xq, xs, w1q, w1s, w2q, w2s, cfg.topk, via_f16=False)
+    assert np.array_equal(res["topk_ids"].numpy(), g["topk_ids"])
+    assert np.allclose(res["topk_weights"].numpy(), g["topk_weights"], atol=1e-7, rtol=1e-6)
+    out1_ref = torch.from_numpy(g["out1"])
+    assert torch.allclose(res["out1"], out1_ref, rtol=2e-5, atol=1e-6)
+    # requantised intermediate: identical scales up to fp32 round-off of out1, codes within 1 step
+    d = orc.e4m3_ulp_distance(res["a2q"], hp.fp8_from_u8(g["a2q_from_f32"]))
+    assert int(d.max()) <= 1 and float((d == 0).float().mean()) > 0.999
+    assert np.allclose(res["a2_scale"].numpy(), g["a2_scale_from_f32"], rtol=1e-5)
+    out2_ref = torch.from_numpy(g["out2_from_f32"])
+    scale = out2_ref.abs().max().item()
+    assert torch.allclose(res["out_f32"], out2_ref, rtol=1e-3, atol=2e-3 * scale)
+    # the reference's own pipeline (intermediate rounded to f16 first) and its single-shot fused oracle
+    res16 = orc.moe_layer(logits, xq, xs, w1q, w1s, w2q, w2s, cfg.topk, via_f16=True)
+    d16 = orc.e4m3_ulp_distance(res16["a2q"], hp.fp8_from_u8(g["a2q_via_f16"]))
+    assert int(d16.max()) <= 1 and float((d16 == 0).float().mean()) > 0.999
+    out2_16 = torch.from_numpy(g["out2_via_f16"])
+    assert torch.allclose(res16["out_f32"], out2_16, rtol=1e-3, atol=2e-3 * scale)
+    fused = torch.from_numpy(g["fused_bf16_bits"]).view(torch.bfloat16).float()
+    assert torch.allclose(res["out"].float(), fused, rtol=2e-2, atol=2e-2 * max(scale, 1.0))
+
+
+def test_moe_mini_matches_reference():
+    _check_moe("moe_mini.npz", wl.MoEConfig("mini", 16, 256, 128, 4, 2, 7), True)
+
+
+def test_moe_c1_matches_reference():
+    _check_moe("moe_c1.npz", wl.CONFIGS["c1"], False)
+
+
+def test_ulp_distance():
+    a = torch.tensor([0.0, 1.0, -1.0, 448.0]).to(hp.FP8)
+    b = torch.tensor([0.0, 1.125, -0.9375, 416.0]).to(hp.FP8)
+    assert orc.e4m3_ulp_distance(a, b).tolist() == [0, 1, 1, 1]
