@@ -1,0 +1,306 @@
+#!/usr/bin/env python
+"""Benchmark of the FP8 block-scaled fused-MoE layer on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+One "step" = one pass of the whole path (gating -> sort -> gather -> stage 1 -> stage 2)
+over one batch of seeded synthetic tokens.  N=1 runs the DeepSeek-V3-shaped prefill
+layer (T=4096, H=7168, I=2048, E=256, top-8; workload ``c4a``); N>1 runs the
+expert-parallel configuration (T=16384 tokens per GPU, experts sharded over the ranks,
+NCCL all-to-all dispatch/combine; workload ``c5a``), launched by torchrun with one rank
+per GPU.  Rank 0 prints ONE JSON line.
+
+``value`` is algorithmic TFLOP/s (6*T*k*H*I per step, whole job) with inputs resident in
+HBM; ``e2e`` is the same metric through the public layer call with host (pinned) buffers,
+host<->device copies inside the timed region.  ``roofline`` describes the dominant kernel
+(stage 1), timed with CUDA events inside the timed region.  ``cpu_baseline`` times the CPU
+oracle (the reference's torch path restated) on a bounded sample on the host cores.
+``--impl reference`` times only that CPU path and prints the same line shape.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from flydsl_b200 import workloads as wl  # noqa: E402
+
+METRIC = "fp8_blockscale_moe_layer_tflops"
+UNIT = "TFLOP/s"
+
+
+def load_peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        p["source"] = "measured"
+        return p
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clock/throttle samples taken while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.proc = None
+        self.gpu = gpu_index
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.05)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def physical_gpu_index(local_index: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+    parts = [p.strip() for p in vis.split(",") if p.strip()]
+    if local_index < len(parts) and parts[local_index].isdigit():
+        return int(parts[local_index])
+    return local_index
+
+
+# ------------------------------------------------------------------------------------ CPU arm
+def cpu_baseline(cfg: wl.MoEConfig, n_sample_experts: int, device_weights=None, ids=None, tw=None,
+                 xq=None, xs=None) -> dict:
+    """Time the CPU oracle on the tokens routed to the first ``n_sample_experts`` experts."""
+    from oracle import moe_oracle as orc
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    if ids is None:
+        logits = wl.make_logits(cfg)
+        _x, xq, xs = wl.make_activations(cfg)
+        tw, ids, _ = orc.topk_gating_softmax(logits, cfg.topk)
+    n = min(n_sample_experts, cfg.experts)
+    if device_weights is not None:
+        w1q, w1s, w2q, w2s = (t[:n].cpu() for t in device_weights)
+    else:
+        w1q, w1s, w2q, w2s = wl.make_weights(cfg, experts=range(n))
+    ids_s = torch.where(ids < n, ids, torch.full_like(ids, -1))
+    pairs = int((ids_s >= 0).sum())
+    t0 = time.perf_counter()
+    tw_r, ids_r, _ = orc.topk_gating_softmax(wl.make_logits(cfg), cfg.topk)
+    orc.moe_sorting(ids_r.numpy(), tw_r.numpy(), cfg.experts, 128)
+    o1 = orc.stage1(xq, xs, w1q, w1s, ids_s, cfg.inter_dim)
+    a2q, a2s = orc.requant(o1)
+    orc.stage2(a2q, a2s, w2q, w2s, ids_s, tw, cfg.model_dim)
+    dt = time.perf_counter() - t0
+    flops = 6.0 * pairs * cfg.model_dim * cfg.inter_dim
+    return {"value": flops / dt / 1e12, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"whole routing plus experts 0..{n - 1} of {cfg.experts} with the {pairs} (token, slot) "
+                      f"pairs routed to them ({pairs / max(1, cfg.pairs):.3f} of the layer's FLOPs), "
+                      f"{dt:.2f} s of CPU work", "seconds": round(dt, 3)}
+
+
+def run_reference_arm(args, cfg, rank: int) -> None:
+    if rank != 0:
+        return
+    vals = []
+    last = None
+    for _ in range(max(1, min(args.steps, 3))):
+        last = cpu_baseline(cfg, args.cpu_experts)
+        vals.append(last["value"])
+    v = statistics.median(vals)
+    last["value"] = v
+    line = {"metric": METRIC, "value": v, "unit": UNIT, "impl": "reference", "n_gpus": args.gpus,
+            "steps": len(vals), "warmup": 0, "ms_per_step": last["seconds"] * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32 (CPU dequantised fp8)", "data": "synthetic",
+            "config": wl.describe(cfg), "cpu_baseline": last,
+            "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------ GPU arm
+def run_single_gpu(args, cfg) -> dict:
+    from flydsl_b200 import _lib
+    from flydsl_b200.layer import FusedMoEBlockscale
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks = load_peaks()
+    T, k, H, I, E = cfg.tokens, cfg.topk, cfg.model_dim, cfg.inter_dim, cfg.experts
+    w1q, w1s, w2q, w2s = wl.make_weights(cfg, device=dev)
+    logits = wl.make_logits(cfg).to(dev)
+    _x, xq_c, xs_c = wl.make_activations(cfg)
+    xq, xs_t = xq_c.to(dev), xs_c.t().contiguous().to(dev)
+    layer = FusedMoEBlockscale(w1q, w1s, w2q, w2s, k, max_tokens=T, tile_m=args.tile_m,
+                               stage2_mode=args.stage2_mode)
+    stream = torch.cuda.current_stream()
+
+    def step():
+        return layer(logits, xq, xs_t)
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    if _lib.device_status() != 0:
+        raise RuntimeError("a kernel reported a device-side timeout during warm-up")
+
+    # ---- timed region: K steps, stage-1/2 kernels bracketed by their own events
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    layer.timing_events = []
+    sampler = ClockSampler(physical_gpu_index(torch.cuda.current_device()))
+    torch.cuda.synchronize()
+    ev0.record(stream)
+    for _ in range(args.steps):
+        step()
+    ev1.record(stream)
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    total_ms = ev0.elapsed_time(ev1)
+    ms_per_step = total_ms / args.steps
+    g1 = [a.elapsed_time(b) for (name, a, b) in layer.timing_events if name == "gemm1"]
+    g2 = [a.elapsed_time(b) for (name, a, b) in layer.timing_events if name == "gemm2"]
+    layer.timing_events = None
+    if _lib.device_status() != 0:
+        raise RuntimeError("a kernel reported a device-side timeout during the timed region")
+    flops = cfg.flops()
+    value = flops / (ms_per_step * 1e-3) / 1e12
+
+    # ---- roofline of the dominant kernel (stage 1)
+    ids = layer.topk_ids[:T].cpu()
+    e_act = int(torch.unique(ids).numel())
+    rows = int(layer.num_valid_ids[0])
+    s1_bytes = (e_act * 2.0 * I * H * (1 + 4.0 / (128 * 128))      # W1 of active experts + block scales
+                + rows * H + T * (H // 128) * 4.0                  # gathered activations + their scales
+                + rows * I * (1 + 4.0 / 128))                      # e4m3 intermediate + scales written
+    s1_ms = statistics.mean(g1) if g1 else float("nan")
+    s2_ms = statistics.mean(g2) if g2 else float("nan")
+    achieved = s1_bytes / (s1_ms * 1e-3) / 1e9
+    s1_flops = 2.0 * T * k * 2 * I * H
+    fp8_peak = 2.0 * peaks["bf16_tflops"]
+    roofline = {"kernel": "moe_gemm_sm100_kernel<1> (stage 1)", "bound": "hbm", "achieved": round(achieved, 1),
+                "peak": peaks["hbm_gbs"], "peak_source": peaks["source"], "unit": "GB/s",
+                "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None,
+                "algorithmic_bytes_per_launch": int(s1_bytes), "ms_per_launch": round(s1_ms, 4),
+                "stage2_ms_per_launch": round(s2_ms, 4),
+                "tensor_tflops": round(s1_flops / (s1_ms * 1e-3) / 1e12, 1),
+                "tensor_frac_of_2x_bf16_peak": round(s1_flops / (s1_ms * 1e-3) / 1e12 / fp8_peak, 4),
+                "active_experts": e_act, "padded_rows": rows}
+    total_bytes = wl.weight_bytes_active(cfg, ids)
+
+    # ---- end to end: pinned host inputs -> device -> layer -> pinned host output
+    h_logits = logits.cpu().pin_memory()
+    h_xq = xq_c.view(torch.uint8).pin_memory()
+    h_xs = xs_c.t().contiguous().pin_memory()
+    h_out = torch.empty((T, H), dtype=torch.bfloat16).pin_memory()
+    d_logits, d_xq, d_xs = torch.empty_like(logits), torch.empty_like(xq.view(torch.uint8)), torch.empty_like(xs_t)
+
+    def e2e_step():
+        d_logits.copy_(h_logits, non_blocking=True)
+        d_xq.copy_(h_xq, non_blocking=True)
+        d_xs.copy_(h_xs, non_blocking=True)
+        out = layer(d_logits, d_xq, d_xs)
+        h_out.copy_(out, non_blocking=True)
+
+    for _ in range(min(3, args.warmup)):
+        e2e_step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1) / args.steps
+    h2d = h_logits.numel() * 4 + h_xq.numel() + h_xs.numel() * 4
+    d2h = h_out.numel() * 2
+    e2e = {"value": round(flops / (e2e_ms * 1e-3) / 1e12, 2), "unit": UNIT, "ms_per_step": round(e2e_ms, 4),
+           "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)}
+
+    cpu = None
+    if not args.no_cpu_baseline:
+        cpu = cpu_baseline(cfg, args.cpu_experts, device_weights=(w1q, w1s, w2q, w2s), ids=ids,
+                           tw=layer.topk_weights[:T].cpu(), xq=xq_c, xs=xs_c)
+
+    return {"metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate and scales)",
+            "data": "synthetic",
+            "config": {**wl.describe(cfg), "tile_m": args.tile_m, "stage2_mode": args.stage2_mode,
+                       "parallelism": "single GPU",
+                       "l2_policy": "inputs exceed L2: %.1f GB of expert weights stream per step" % (e_act * 3.0 * H * I / 1e9)},
+            "layer_hbm_gbs": round(total_bytes / (ms_per_step * 1e-3) / 1e9, 1),
+            "layer_hbm_frac": round(total_bytes / (ms_per_step * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
+            "gpu_launches": args.steps * layer.kernel_launches(T)}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=None, help="c1|c2|c3|c4a|c4b|c5a|c5b (default c4a, or c5a when --gpus > 1)")
+    ap.add_argument("--tokens", type=int, default=None, help="override the token count (c2 sweep)")
+    ap.add_argument("--tile-m", type=int, default=128)
+    ap.add_argument("--stage2-mode", default="atomic", choices=["atomic", "reduce"])
+    ap.add_argument("--cpu-experts", type=int, default=24, help="experts in the CPU baseline sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    name = args.workload or ("c4a" if args.gpus == 1 else "c5a")
+    cfg = wl.CONFIGS[name]
+    if args.tokens is not None:
+        cfg = cfg.with_tokens(args.tokens)
+
+    if args.impl == "reference":
+        run_reference_arm(args, cfg, rank)
+        return
+    if args.gpus > 1 or world > 1:
+        from flydsl_b200.ep_bench import run_expert_parallel
+        line = run_expert_parallel(args, cfg)
+        if line is not None:
+            print(json.dumps(line), flush=True)
+        return
+    line = run_single_gpu(args, cfg)
+    print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

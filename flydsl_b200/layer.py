@@ -72,7 +72,16 @@ class FusedMoEBlockscale:
         self.pair_out = (torch.empty((T * k, H), dtype=out_dtype, device=dev)
                          if stage2_mode == "reduce" else None)
         self.out_code = _lib.DTYPE_CODE[out_dtype]
-        self.launches_per_forward = 0
+        # When set to a list, forward() appends ("gemm1"|"gemm2", start, end) CUDA events recorded
+        # on torch's current stream around the two GEMM launches (used by the benchmark).
+        self.timing_events = None
+
+    def _mark(self):
+        if self.timing_events is None:
+            return None
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record(torch.cuda.current_stream())
+        return ev
 
     # ---------------------------------------------------------------- pieces
     def gate(self, logits: torch.Tensor, tokens: int, stream: int) -> None:
@@ -111,12 +120,14 @@ class FusedMoEBlockscale:
             xq.data_ptr(), self.xs.data_ptr(), self.sorted_ids.data_ptr(), self.num_valid_ids.data_ptr(),
             T, k, H, _lib.ROWS_BY_TOKEN, cap_rows, stream), "gather_rows")
         sx_stride = x_scale_t.numel() // (H // 128)
+        t0 = self._mark()
         _lib.check(lib.flymoe_moe_gemm1(
             self.a2q.data_ptr(), self.a2_scale.data_ptr(), self.cap_rows, self.xs.data_ptr(),
             x_scale_t.data_ptr(), sx_stride, self.w1q.data_ptr(), self.w1_scale.data_ptr(),
             self.sorted_ids.data_ptr(), self.sorted_expert_ids.data_ptr(), self.sorted_weights.data_ptr(),
             self.num_valid_ids.data_ptr(), T, I, H, blocks, E, k, U, 0, _lib.E4M3, _lib.ROWS_SORTED,
             _lib.ROWS_BY_TOKEN, _lib.ROWS_SORTED, self.impl, stream), "moe_gemm1")
+        t1 = self._mark()
         accumulate = self.stage2_mode == "atomic"
         target = out if accumulate else self.pair_out
         _lib.check(lib.flymoe_moe_gemm2(
@@ -125,6 +136,9 @@ class FusedMoEBlockscale:
             self.sorted_expert_ids.data_ptr(), self.sorted_weights.data_ptr(), self.num_valid_ids.data_ptr(),
             T, H, I, blocks, E, k, U, 1 if accumulate else 0, self.out_code, 1 if accumulate else 0,
             _lib.ROWS_SORTED, _lib.ROWS_SORTED, self.impl, stream), "moe_gemm2")
+        if self.timing_events is not None:
+            self.timing_events.append(("gemm1", t0, t1))
+            self.timing_events.append(("gemm2", t1, self._mark()))
         if not accumulate:
             # per-pair rows hold the unweighted expert outputs; weight and sum them here
             _lib.check(lib.flymoe_moe_reduce(

@@ -182,12 +182,13 @@ def stage1(xq, x_scale, w1q, w1_scale, topk_ids, inter_dim: int):
     """silu(x W1g^T) * (x W1u^T) per (token, slot).  Returns f32 [T, k, I].
 
     xq e4m3 [T,H]; x_scale f32 [T,H/128]; w1q e4m3 [E,2I,H];
-    w1_scale f32 [E,2I/128,H/128]; topk_ids [T,k].
+    w1_scale f32 [E,2I/128,H/128]; topk_ids [T,k].  w1q / w1_scale may be any
+    sequence indexable by expert id (only experts that received a token are read).
     """
     T, _H = xq.shape
     ids = torch.as_tensor(topk_ids).to(torch.int64)
     k = ids.shape[1]
-    E = w1q.shape[0]
+    E = len(w1q)
     x = _dequant_a(xq, x_scale)
     out = torch.zeros((T, k, inter_dim), dtype=torch.float32)
     for e in range(E):
@@ -212,7 +213,7 @@ def stage2(a2q, a2_scale, w2q, w2_scale, topk_ids, topk_weights, model_dim: int,
     """out[t] = sum_s w[t,s] * (a2[t,s] W2_e^T).  Returns f32 [T,H] (or [T,k,H])."""
     ids = torch.as_tensor(topk_ids).to(torch.int64)
     T, k = ids.shape
-    E = w2q.shape[0]
+    E = len(w2q)
     I = a2q.shape[1]
     a = _dequant_a(a2q, a2_scale).view(T, k, I)
     out = torch.zeros((T, k, model_dim), dtype=torch.float32)

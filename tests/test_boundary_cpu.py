@@ -1,0 +1,97 @@
+"""Host-side boundary: the C-ABI library loads without a GPU and exports every declared
+symbol; builders and launchers reject bad arguments before anything is launched."""
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+from flydsl_b200 import _lib
+from flydsl_b200.kernels import moe_blockscale_2stage as bs
+from flydsl_b200.kernels import moe_sorting_kernel as srt
+from flydsl_b200.kernels import topk_gating_softmax_kernel as gat
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_library_exports_every_declared_symbol(lib):
+    header = (ROOT / "include" / "flymoe.h").read_text()
+    declared = set(re.findall(r"\b(flymoe_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found in include/flymoe.h"
+    for name in declared:
+        assert hasattr(lib, name), f"{name} is declared in flymoe.h but not exported"
+    assert declared == set(_lib.EXPORTED_SYMBOLS), "ctypes signature table and header disagree"
+    assert lib.flymoe_abi_version() == 1
+    assert lib.flymoe_error_string(-4).decode() == "workspace too small"
+
+
+def test_workspace_size_is_host_only(lib):
+    assert lib.flymoe_moe_sorting_workspace_elems(64, 256, 8, 32) == 0
+    need = lib.flymoe_moe_sorting_workspace_elems(4096, 256, 8, 128)
+    assert need == (4096 * 8 // 512) * 256 + 256
+    assert srt.moe_sorting_get_workspace_size(4096, 256, 8, 128) >= need
+    assert srt.moe_sorting_get_workspace_size(16, 256, 8) == 0
+
+
+def test_c_abi_rejects_bad_arguments_without_launching(lib):
+    rc = lib.flymoe_topk_gating_softmax(None, 0, None, None, None, 4, 4096, 2, 1, None)
+    assert rc == -1 and b"num_experts" in lib.flymoe_last_error()
+    rc = lib.flymoe_moe_sorting(None, None, None, None, None, None, None, 0, None, None, 0, 4, 8, 300, 32, None)
+    assert rc == -1 and b"topk" in lib.flymoe_last_error()
+    rc = lib.flymoe_moe_gemm1(None, None, 0, None, None, 0, None, None, None, None, None, None,
+                              4, 100, 256, 1, 2, 2, 128, 0, 2, 0, 0, 1, 0, None)
+    assert rc == -1 and b"inter_dim" in lib.flymoe_last_error()
+    rc = lib.flymoe_quant_act_1x128(None, 2, None, None, 0, 4, 100, None)
+    assert rc == -1
+
+
+def test_builder_value_errors_match_reference_rules():
+    kw = dict(model_dim=1024, inter_dim=512, experts=8, topk=2, tile_m=128, tile_n=256, tile_k=128)
+    with pytest.raises(ValueError, match="out_dtype"):
+        bs.compile_moe_blockscale_gemm1(doweight_stage1=False, out_dtype="f32", **kw)
+    with pytest.raises(ValueError, match="scale_block_k"):
+        bs.compile_moe_blockscale_gemm1(doweight_stage1=False, **{**kw, "model_dim": 1000})
+    with pytest.raises(ValueError, match="divisible by 128"):
+        bs.compile_moe_blockscale_gemm1(doweight_stage1=False, **{**kw, "inter_dim": 96})
+    with pytest.raises(ValueError, match="tile_k_bytes"):
+        bs.compile_moe_blockscale_gemm2(doweight_stage2=True, **{**kw, "tile_k": 96})
+    with pytest.raises(ValueError, match="accumulate=False"):
+        bs.compile_moe_blockscale_gemm2(doweight_stage2=True, out_dtype="f32", accumulate=False, **kw)
+    with pytest.raises(ValueError, match="out_dtype"):
+        bs.compile_moe_blockscale_gemm2(doweight_stage2=True, out_dtype="int8", **kw)
+    with pytest.raises(ValueError, match="Unsupported dtype"):
+        bs.compile_moe_reduction(topk=2, model_dim=1024, dtype_str="i8")
+    with pytest.raises(ValueError, match="FP8-only"):
+        bs.compile_moe_blockscale_gemm2_ex(doweight_stage2=True, in_dtype="int8", **kw)
+    with pytest.raises(ValueError):
+        gat.build_topk_gating_softmax_module(8, 9)
+    with pytest.raises(ValueError):
+        gat.build_topk_gating_softmax_module(8, 2, "f64")
+    # builders are cached like the reference's lru_cache'd ones
+    a = bs.compile_moe_blockscale_gemm1(doweight_stage1=False, **kw)
+    assert a is bs.compile_moe_blockscale_gemm1(doweight_stage1=False, **kw)
+    assert bs.compile_moe_blockscale_gemm2_ex(doweight_stage2=True, mode=bs.MoeGemm2Mode.REDUCE, **kw).mode == "reduce"
+
+
+def test_launchers_reject_cpu_tensors():
+    launch = gat.build_topk_gating_softmax_module(8, 2, "f32")
+    g = torch.zeros((4, 8))
+    with pytest.raises(ValueError, match="CUDA tensor"):
+        launch(g, torch.zeros(4, 2), torch.zeros(4, 2, dtype=torch.int32), torch.zeros(4, 2, dtype=torch.int32), 4)
+    ids = torch.zeros((4, 2), dtype=torch.int32)
+    with pytest.raises(ValueError, match="CUDA tensor"):
+        srt.moe_sorting_flydsl(ids, torch.zeros(4, 2), ids, ids, ids, ids, None, 8)
+    exe = bs.compile_moe_blockscale_gemm1(model_dim=256, inter_dim=128, experts=4, topk=2, tile_m=128, tile_n=128,
+                                          tile_k=128, doweight_stage1=False)
+    z = torch.zeros(16)
+    with pytest.raises(ValueError, match="CUDA tensor"):
+        exe(z, z, z, z, z, z, z, z, z, 4, 128, 256, 1, None)
+    with pytest.raises(ValueError, match="launcher built for"):
+        exe(z, z, z, z, z, z, z, z, z, 4, 256, 256, 1, None)
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "nope.so")
+    with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
+        _lib.load()
