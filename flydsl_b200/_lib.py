@@ -34,13 +34,14 @@ _SIGNATURES = {
     "flymoe_moe_sorting": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int64, _P, _P, c_int64,
                                    c_int, c_int, c_int, c_int, _P]),
     "flymoe_gather_rows": (c_int, [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P]),
-    "flymoe_moe_gemm1": (c_int, [_P, _P, c_int64, _P, _P, c_int64, _P, _P, _P, _P, _P, _P,
+    "flymoe_moe_gemm1": (c_int, [_P, _P, c_int64, _P, _P, c_int64, c_int64, _P, _P, _P, _P, _P, _P,
                                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                  c_int, c_int, c_int, c_int, _P]),
     "flymoe_moe_gemm2": (c_int, [_P, _P, _P, c_int64, _P, _P, _P, _P, _P, _P,
                                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                  c_int, c_int, c_int, c_int, _P]),
-    "flymoe_moe_reduce": (c_int, [_P, _P, _P, _P, c_int, c_int, c_int, c_int, _P]),
+    "flymoe_moe_reduce": (c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P]),
+    "flymoe_sorted_inverse": (c_int, [_P, _P, _P, c_int, c_int, c_int, _P]),
     "flymoe_quant_act_1x128": (c_int, [_P, c_int, _P, _P, c_int64, c_int, c_int, _P]),
     "flymoe_shuffle_weight": (c_int, [_P, _P, c_int64, c_int, c_int, _P]),
 }

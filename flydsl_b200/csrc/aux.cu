@@ -76,7 +76,8 @@ template <> struct Vec8<float> {
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_reduce_kernel(const T* __restrict__ x, T* __restrict__ y, const uint8_t* __restrict__ mask,
-                  const float* __restrict__ weights, int topk, int model_dim) {
+                  const float* __restrict__ weights, const int* __restrict__ row_index, int topk,
+                  int model_dim) {
   const int t = blockIdx.x;
   const int col = (blockIdx.y * 256 + threadIdx.x) * 8;
   if (col >= model_dim) return;
@@ -84,12 +85,33 @@ moe_reduce_kernel(const T* __restrict__ x, T* __restrict__ y, const uint8_t* __r
   for (int s = 0; s < topk; ++s) {
     if (mask != nullptr && mask[size_t(t) * topk + s] == 0) continue;
     float f[8];
-    Vec8<T>::load(x + (size_t(t) * topk + s) * model_dim + col, f);
+    long long row = (long long)t * topk + s;
+    if (row_index != nullptr) {
+      row = __ldg(row_index + row);
+      if (row < 0) continue;
+    }
+    Vec8<T>::load(x + row * model_dim + col, f);
     const float w = weights != nullptr ? __ldg(weights + size_t(t) * topk + s) : 1.f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = weights != nullptr ? fmaf(f[i], w, acc[i]) : acc[i] + f[i];
   }
   Vec8<T>::store(y + size_t(t) * model_dim + col, acc);
+}
+
+// ---------------------------------------------------------------------------- inverse
+__global__ void __launch_bounds__(256)
+fill_i32_kernel(int* __restrict__ p, int n, int v) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) p[i] = v;
+}
+__global__ void __launch_bounds__(256)
+sorted_inverse_kernel(const int* __restrict__ sorted_ids, const int* __restrict__ num_valid_ids,
+                      int* __restrict__ inverse, int num_tokens, int topk, int max_rows) {
+  const int valid = min(__ldg(num_valid_ids), max_rows);
+  for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < valid; r += gridDim.x * blockDim.x) {
+    const int id = __ldg(sorted_ids + r);
+    const int t = id_token(id), s = id_slot(id);
+    if (t < num_tokens && s < topk) inverse[t * topk + s] = r;
+  }
 }
 
 // ---------------------------------------------------------------------------- quantiser
@@ -160,8 +182,8 @@ extern "C" int flymoe_gather_rows(const void* src, void* dst, const int32_t* sor
 }
 
 extern "C" int flymoe_moe_reduce(const void* x, void* y, const uint8_t* valid_mask,
-                                 const float* weights, int num_tokens, int topk, int model_dim,
-                                 int dtype, void* stream) {
+                                 const float* weights, const int32_t* row_index, int num_tokens,
+                                 int topk, int model_dim, int dtype, void* stream) {
   using namespace flymoe;
   FLYMOE_REQUIRE(num_tokens >= 0 && topk >= 1 && model_dim >= 8 && model_dim % 8 == 0,
                  "moe_reduce: model_dim must be a positive multiple of 8");
@@ -173,22 +195,41 @@ extern "C" int flymoe_moe_reduce(const void* x, void* y, const uint8_t* valid_ma
   switch (dtype) {
     case FLYMOE_F16:
       moe_reduce_kernel<__half><<<grid, 256, 0, s>>>(static_cast<const __half*>(x), static_cast<__half*>(y),
-                                                     valid_mask, weights, topk, model_dim);
+                                                     valid_mask, weights, row_index, topk, model_dim);
       break;
     case FLYMOE_BF16:
       moe_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x),
                                                             static_cast<__nv_bfloat16*>(y), valid_mask,
-                                                            weights, topk, model_dim);
+                                                            weights, row_index, topk, model_dim);
       break;
     case FLYMOE_F32:
       moe_reduce_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(x), static_cast<float*>(y),
-                                                    valid_mask, weights, topk, model_dim);
+                                                    valid_mask, weights, row_index, topk, model_dim);
       break;
     default:
       set_last_error_msg("moe_reduce: dtype must be F16, BF16 or F32");
       return FLYMOE_ERR_INVALID_ARGUMENT;
   }
   FLYMOE_CUDA_CHECK(cudaGetLastError());
+  return FLYMOE_OK;
+}
+
+extern "C" int flymoe_sorted_inverse(const int32_t* sorted_ids, const int32_t* num_valid_ids,
+                                     int32_t* inverse, int num_tokens, int topk, int max_rows,
+                                     void* stream) {
+  using namespace flymoe;
+  FLYMOE_REQUIRE(num_tokens >= 0 && topk >= 1 && max_rows >= 0, "sorted_inverse: bad sizes");
+  const int pairs = num_tokens * topk;
+  if (pairs == 0) return FLYMOE_OK;
+  FLYMOE_REQUIRE(sorted_ids && num_valid_ids && inverse, "sorted_inverse: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  fill_i32_kernel<<<std::min(ceil_div(pairs, 256), sm_count() * 8), 256, 0, s>>>(inverse, pairs, -1);
+  FLYMOE_CUDA_CHECK(cudaGetLastError());
+  if (max_rows > 0) {
+    sorted_inverse_kernel<<<std::min(ceil_div(max_rows, 256), sm_count() * 8), 256, 0, s>>>(
+        sorted_ids, num_valid_ids, inverse, num_tokens, topk, max_rows);
+    FLYMOE_CUDA_CHECK(cudaGetLastError());
+  }
   return FLYMOE_OK;
 }
 

@@ -15,7 +15,7 @@ static long long layout_rows(int layout, int num_tokens, int topk, int size_expe
 }
 
 extern "C" int flymoe_moe_gemm1(void* out, float* out_scale, int64_t out_scale_stride, const void* x,
-                                const float* scale_x, int64_t sx_stride, const void* w,
+                                const float* scale_x, int64_t sx_stride, int64_t sx_row_stride, const void* w,
                                 const float* scale_w, const int32_t* sorted_ids,
                                 const int32_t* sorted_expert_ids, const float* sorted_weights,
                                 const int32_t* num_valid_ids, int num_tokens, int inter_dim,
@@ -41,7 +41,9 @@ extern "C" int flymoe_moe_gemm1(void* out, float* out_scale, int64_t out_scale_s
   FLYMOE_REQUIRE(out_dtype != FLYMOE_E4M3 || out_scale, "gemm1: e4m3 output needs out_scale");
   FLYMOE_REQUIRE(aligned16(out) && aligned16(x) && aligned16(w), "gemm1: out/x/w must be 16-byte aligned");
   const long long srows = layout_rows(x_scale_layout, num_tokens, topk, size_expert_ids, tile_m);
-  FLYMOE_REQUIRE(sx_stride >= srows || x_scale_layout == FLYMOE_ROWS_SORTED, "gemm1: sx_stride smaller than row count");
+  FLYMOE_REQUIRE(sx_row_stride >= 1 && sx_stride >= 1, "gemm1: scale strides must be positive");
+  FLYMOE_REQUIRE(sx_row_stride != 1 || sx_stride >= srows || x_scale_layout == FLYMOE_ROWS_SORTED,
+                 "gemm1: sx_stride smaller than row count");
   int* status = device_status_ptr();
   FLYMOE_REQUIRE(status != nullptr, "gemm1: no CUDA device");
 
@@ -49,6 +51,7 @@ extern "C" int flymoe_moe_gemm1(void* out, float* out_scale, int64_t out_scale_s
   a.a = static_cast<const uint8_t*>(x);
   a.scale_a = scale_x;
   a.sa_stride = sx_stride;
+  a.sa_row_stride = sx_row_stride;
   a.a_layout = x_layout;
   a.a_scale_layout = x_scale_layout;
   a.a_rows = layout_rows(x_layout, num_tokens, topk, size_expert_ids, tile_m);
@@ -109,6 +112,7 @@ extern "C" int flymoe_moe_gemm2(void* out, const void* a2, const float* scale_a,
   a.a = static_cast<const uint8_t*>(a2);
   a.scale_a = scale_a;
   a.sa_stride = sa_stride;
+  a.sa_row_stride = 1;
   a.a_layout = a_layout;
   a.a_scale_layout = a_scale_layout;
   a.a_rows = layout_rows(a_layout, num_tokens, topk, size_expert_ids, tile_m);

@@ -8,8 +8,9 @@ namespace flymoe {
 struct GemmArgs {
   // A operand: e4m3 rows of k_dim bytes; layout says how a sorted row finds its A row.
   const uint8_t* a;
-  const float* scale_a;        // [k_dim/128, sa_stride]
+  const float* scale_a;        // element (kb, row) at kb * sa_stride + row * sa_row_stride
   long long sa_stride;
+  long long sa_row_stride;     // 1 for the transposed [k_dim/128, rows] layout, k_dim/128 for row-major
   int a_layout;                // FLYMOE_ROWS_*
   int a_scale_layout;          // FLYMOE_ROWS_*
   long long a_rows;            // rows addressable in `a` (bounds for the TMA descriptor)

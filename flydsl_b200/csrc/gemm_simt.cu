@@ -114,7 +114,7 @@ moe_gemm_simt_kernel(GemmArgs a) {
         const float s1 = __ldg(sw1 + kb);
 #pragma unroll
         for (int i = 0; i < kSimtRows; ++i) {
-          const float sa = rok[i] ? __ldg(a.scale_a + (long long)kb * a.sa_stride + sidx[i]) : 0.f;
+          const float sa = rok[i] ? __ldg(a.scale_a + (long long)kb * a.sa_stride + sidx[i] * a.sa_row_stride) : 0.f;
           acc[0][i] = fmaf(part[0][i], sa * s0, acc[0][i]);
           if (NACC == 2) acc[NACC - 1][i] = fmaf(part[NACC - 1][i], sa * s1, acc[NACC - 1][i]);
         }

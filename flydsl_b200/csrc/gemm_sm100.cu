@@ -319,7 +319,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         sidx = a.a_scale_layout == FLYMOE_ROWS_BY_TOKEN ? (long long)tok
              : a.a_scale_layout == FLYMOE_ROWS_BY_PAIR ? (long long)tok * a.topk + slot : (long long)r;
       }
-      const float* sa_ptr = a.scale_a + sidx;
+      const float* sa_ptr = a.scale_a + sidx * a.sa_row_stride;
       // weight block scales of this tile
       const int wblk_per_expert = (STAGE == 1 ? 2 * a.n_dim : a.n_dim) / 128;
       const int blk0 = STAGE == 1 ? n : n * 2 + wg;

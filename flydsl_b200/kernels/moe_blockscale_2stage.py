@@ -193,7 +193,7 @@ def compile_moe_blockscale_gemm1(*, model_dim: int, inter_dim: int, experts: int
             x_layout = _lib.ROWS_SORTED
         _lib.check(lib.flymoe_moe_gemm1(
             _lib.ptr(arg_out), _lib.ptr(arg_out_scale), out_scale_stride, x_ptr, _lib.ptr(arg_scale_x),
-            sx_stride, _lib.ptr(w_plain), _lib.ptr(arg_scale_w), _lib.ptr(arg_sorted_token_ids),
+            sx_stride, 1, _lib.ptr(w_plain), _lib.ptr(arg_scale_w), _lib.ptr(arg_sorted_token_ids),
             _lib.ptr(arg_expert_ids), _lib.ptr(arg_sorted_weights), _lib.ptr(arg_max_token_ids),
             tokens, inter_dim, model_dim, blocks, experts, topk, tile_m, 1 if doweight_stage1 else 0,
             out_code, x_layout, _lib.ROWS_SORTED if sorted_rows else _lib.ROWS_BY_TOKEN,
@@ -302,8 +302,8 @@ def compile_moe_reduction(*, topk: int, model_dim: int, dtype_str: str = "f16", 
             mask_ptr = _lib.ptr(valid_mask)
         if weights is not None:
             _lib.require_cuda("weights", weights, (torch.float32,), m * topk)
-        _lib.check(_lib.load().flymoe_moe_reduce(_lib.ptr(X), _lib.ptr(Y), mask_ptr, _lib.ptr(weights), m, topk,
-                                                 model_dim, code, _lib.stream_handle(stream)), "moe_reduce")
+        _lib.check(_lib.load().flymoe_moe_reduce(_lib.ptr(X), _lib.ptr(Y), mask_ptr, _lib.ptr(weights), None, m,
+                                                 topk, model_dim, code, _lib.stream_handle(stream)), "moe_reduce")
 
     return launch_moe_reduction
 

@@ -123,7 +123,7 @@ class FusedMoEBlockscale:
         t0 = self._mark()
         _lib.check(lib.flymoe_moe_gemm1(
             self.a2q.data_ptr(), self.a2_scale.data_ptr(), self.cap_rows, self.xs.data_ptr(),
-            x_scale_t.data_ptr(), sx_stride, self.w1q.data_ptr(), self.w1_scale.data_ptr(),
+            x_scale_t.data_ptr(), sx_stride, 1, self.w1q.data_ptr(), self.w1_scale.data_ptr(),
             self.sorted_ids.data_ptr(), self.sorted_expert_ids.data_ptr(), self.sorted_weights.data_ptr(),
             self.num_valid_ids.data_ptr(), T, I, H, blocks, E, k, U, 0, _lib.E4M3, _lib.ROWS_SORTED,
             _lib.ROWS_BY_TOKEN, _lib.ROWS_SORTED, self.impl, stream), "moe_gemm1")
@@ -142,7 +142,7 @@ class FusedMoEBlockscale:
         if not accumulate:
             # per-pair rows hold the unweighted expert outputs; weight and sum them here
             _lib.check(lib.flymoe_moe_reduce(
-                self.pair_out.data_ptr(), out.data_ptr(), None, topk_weights.data_ptr(), T, k, H,
+                self.pair_out.data_ptr(), out.data_ptr(), None, topk_weights.data_ptr(), None, T, k, H,
                 self.out_code, stream), "moe_reduce")
         return out
 

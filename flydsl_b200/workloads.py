@@ -12,7 +12,6 @@ the measured path.
 
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass, replace
 
 import torch
@@ -157,5 +156,4 @@ def describe(cfg: MoEConfig) -> dict:
     return {"workload": cfg.name, "tokens": cfg.tokens, "model_dim": cfg.model_dim,
             "inter_dim": cfg.inter_dim, "experts": cfg.experts, "topk": cfg.topk,
             "seed": cfg.seed, "routing": cfg.routing,
-            "gflop": round(cfg.flops() / 1e9, 3),
-            "sqrt_inter": round(math.sqrt(cfg.inter_dim), 3)}
+            "gflop": round(cfg.flops() / 1e9, 3)}

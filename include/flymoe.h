@@ -95,15 +95,18 @@ int flymoe_gather_rows(const void* src, void* dst, const int32_t* sorted_ids,
 /* Stage 1: gate/up grouped FP8 GEMM over sorted rows + SiLU(gate)*up.
  * Replaces kernels/moe_blockscale_2stage.py:70-84 (builder) and the launcher
  * :1142-1157.  x e4m3: [T,H] when x_layout==BY_TOKEN and impl==SIMT, else the
- * gathered [rows,H] matrix in sorted order (flymoe_gather_rows).  scale_x f32
- * [H/128, sx_stride] indexed by token (x_scale_layout BY_TOKEN) or sorted row.
+ * gathered [rows,H] matrix in sorted order (flymoe_gather_rows).  scale_x f32, element
+ * (kb, row) at kb*sx_stride + row*sx_row_stride: the reference's transposed layout
+ * [H/128, rows] is (sx_stride = rows, sx_row_stride = 1), row-major [rows, H/128] is
+ * (1, H/128); row = token (x_scale_layout BY_TOKEN) or sorted row.
  * w e4m3 [E,2I,H] row-major (gate rows first), scale_w f32 [E,2I/128,H/128].
  * out: out_dtype F16/BF16 -> [rows,I] values; E4M3 -> codes [rows,I] plus
  * out_scale f32 [I/128, out_scale_stride] (the per-1x128 requantisation that the
  * reference performs outside the kernel, tests/kernels/test_moe_blockscale.py:447-452).
  * out_layout BY_PAIR (reference) or SORTED.  tile_m = sort unit (16/32/64/128). */
 int flymoe_moe_gemm1(void* out, float* out_scale, int64_t out_scale_stride, const void* x,
-                     const float* scale_x, int64_t sx_stride, const void* w, const float* scale_w,
+                     const float* scale_x, int64_t sx_stride, int64_t sx_row_stride, const void* w,
+                     const float* scale_w,
                      const int32_t* sorted_ids, const int32_t* sorted_expert_ids,
                      const float* sorted_weights, const int32_t* num_valid_ids, int num_tokens,
                      int inter_dim, int model_dim, int size_expert_ids, int experts, int topk,
@@ -125,10 +128,20 @@ int flymoe_moe_gemm2(void* out, const void* a2, const float* scale_a, int64_t sa
                      int out_dtype, int accumulate, int a_layout, int a_scale_layout, int impl,
                      void* stream);
 
-/* Y[t,:] = sum_s X[t,s,:] with fp32 accumulation; optional u8 valid_mask [T,k] and
- * optional f32 weights [T,k].  Replaces kernels/moe_blockscale_2stage.py:2383-2589. */
+/* Y[t,:] = sum_s w[t,s] * X[row(t,s),:] with fp32 accumulation; row(t,s) = t*k+s, or
+ * row_index[t*k+s] when row_index is given (negative entries are skipped); optional u8
+ * valid_mask [T,k] and optional f32 weights [T,k] (NULL = 1).
+ * Replaces kernels/moe_blockscale_2stage.py:2383-2589. */
 int flymoe_moe_reduce(const void* x, void* y, const uint8_t* valid_mask, const float* weights,
-                      int num_tokens, int topk, int model_dim, int dtype, void* stream);
+                      const int32_t* row_index, int num_tokens, int topk, int model_dim, int dtype,
+                      void* stream);
+
+/* inverse[t*k+s] = position r of pair (t,s) in sorted_ids[0, num_valid_ids[0]); pairs that
+ * do not appear keep -1.  Used by the expert-parallel combine to read returned rows in
+ * (token, slot) order; the reference has no dispatch/combine, so this has no counterpart
+ * there beyond the packed-id format of kernels/moe_sorting_kernel.py:17-20. */
+int flymoe_sorted_inverse(const int32_t* sorted_ids, const int32_t* num_valid_ids, int32_t* inverse,
+                          int num_tokens, int topk, int max_rows, void* stream);
 
 /* Per-row, per-128-column FP8 quantiser: x [R,K] F16/BF16/F32 -> q e4m3 [R,K] and
  * scale f32 stored transposed [K/128, scale_stride] (scale = amax/448, 0 -> 1).

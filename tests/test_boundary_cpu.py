@@ -38,7 +38,7 @@ def test_c_abi_rejects_bad_arguments_without_launching(lib):
     assert rc == -1 and b"num_experts" in lib.flymoe_last_error()
     rc = lib.flymoe_moe_sorting(None, None, None, None, None, None, None, 0, None, None, 0, 4, 8, 300, 32, None)
     assert rc == -1 and b"topk" in lib.flymoe_last_error()
-    rc = lib.flymoe_moe_gemm1(None, None, 0, None, None, 0, None, None, None, None, None, None,
+    rc = lib.flymoe_moe_gemm1(None, None, 0, None, None, 0, 1, None, None, None, None, None, None,
                               4, 100, 256, 1, 2, 2, 128, 0, 2, 0, 0, 1, 0, None)
     assert rc == -1 and b"inter_dim" in lib.flymoe_last_error()
     rc = lib.flymoe_quant_act_1x128(None, 2, None, None, 0, 4, 100, None)

@@ -136,7 +136,8 @@ def test_dsv3_prefill_subset(name):
     det = make_layer(p, 128, mode="reduce")
     out_r = det(p.d_logits, p.d_xq, p.d_xs_t)
     torch.cuda.synchronize()
-    assert_close(out, out_r, RTOL, ATOL, f"{name} atomic vs reduce")
+    # bf16 atomics round every partial sum: allow one bf16 step of the largest partial sum on top of the bar
+    assert_close(out, out_r, RTOL, ATOL + 2.0 ** -7 * float(out_r.float().abs().max()), f"{name} atomic vs reduce")
 
 
 def test_quant_act_kernel_matches_reference_quantiser():
