@@ -35,74 +35,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 from flydsl_b200 import workloads as wl  # noqa: E402
-
-METRIC = "fp8_blockscale_moe_layer_tflops"
-UNIT = "TFLOP/s"
-
-
-def load_peaks() -> dict:
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(path):
-        with open(path) as f:
-            p = json.load(f)
-        p["source"] = "measured"
-        return p
-    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
-
-
-class ClockSampler:
-    """nvidia-smi clock/throttle samples taken while the timed region runs."""
-
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, gpu_index: int):
-        self.proc = None
-        self.gpu = gpu_index
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "20",
-                 "-i", str(gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.first = self.proc.stdout.readline()     # blocks until the sampler is running
-        except OSError:
-            self.proc = None
-
-    def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.05)
-        self.proc.terminate()
-        try:
-            out, _ = self.proc.communicate(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-            out, _ = self.proc.communicate()
-        out = out or ""
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in out.strip().splitlines():
-            f = [x.strip() for x in line.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1]))
-                mx.append(float(f[2]))
-            except ValueError:
-                continue
-            for name, val in zip(names, f[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
-
-
-def physical_gpu_index(local_index: int) -> int:
-    vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
-    parts = [p.strip() for p in vis.split(",") if p.strip()]
-    if local_index < len(parts) and parts[local_index].isdigit():
-        return int(parts[local_index])
-    return local_index
+from flydsl_b200.benchutil import METRIC, UNIT, ClockSampler, load_peaks, physical_gpu_index  # noqa: E402
 
 
 # ------------------------------------------------------------------------------------ CPU arm
@@ -278,6 +211,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, help="c1|c2|c3|c4a|c4b|c5a|c5b (default c4a, or c5a when --gpus > 1)")
     ap.add_argument("--tokens", type=int, default=None, help="override the token count (c2 sweep)")
+    ap.add_argument("--experts", type=int, default=None, help="override the expert count (small profiling cases)")
     ap.add_argument("--tile-m", type=int, default=128)
     ap.add_argument("--stage2-mode", default="atomic", choices=["atomic", "reduce"])
     ap.add_argument("--cpu-experts", type=int, default=24, help="experts in the CPU baseline sample")
@@ -290,6 +224,9 @@ def main() -> None:
     cfg = wl.CONFIGS[name]
     if args.tokens is not None:
         cfg = cfg.with_tokens(args.tokens)
+    if args.experts is not None:
+        from dataclasses import replace
+        cfg = replace(cfg, experts=args.experts, name=f"{cfg.name}-E{args.experts}")
 
     if args.impl == "reference":
         run_reference_arm(args, cfg, rank)

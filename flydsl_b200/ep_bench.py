@@ -1,0 +1,129 @@
+"""Multi-GPU leg of the benchmark: the expert-parallel layer under torchrun (one rank per GPU).
+
+Per-GPU work is fixed as the world grows (weak scaling): every rank gates, dispatches
+and combines its own ``cfg.tokens`` tokens and runs E/world local experts.  Timing is on the
+device (CUDA events between barriers), the maximum over ranks is reported.
+"""
+
+from __future__ import annotations
+
+import os
+import statistics
+
+import torch
+import torch.distributed as dist
+
+from . import workloads as wl
+from .benchutil import METRIC, UNIT, ClockSampler, load_peaks, physical_gpu_index
+
+
+def run_expert_parallel(args, cfg: wl.MoEConfig):
+    from . import _lib
+    from .ep import CudaOps, ExpertParallelMoE, expert_range
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29531")
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        T, k, H, I, E = cfg.tokens, cfg.topk, cfg.model_dim, cfg.inter_dim, cfg.experts
+        mine = expert_range(rank, world, E)
+        w1q, w1s, w2q, w2s = wl.make_weights(cfg, device=dev, experts=mine)
+        logits = wl.make_logits(cfg, rank=rank).to(dev)
+        _x, xq_c, xs_c = wl.make_activations(cfg, rank=rank)
+        xq, xs = xq_c.to(dev), xs_c.to(dev)
+        ops = CudaOps(w1q, w1s, w2q, w2s, E, k, T, tile_m=args.tile_m)
+        layer = ExpertParallelMoE(ops, E, k, H)
+        stream = torch.cuda.current_stream()
+
+        def timed(fn, steps):
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(steps):
+                fn()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            dist.barrier()
+            t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item()) / steps
+
+        for _ in range(args.warmup):
+            layer(logits, xq, xs)
+        torch.cuda.synchronize()
+        if _lib.device_status() != 0:
+            raise RuntimeError("a kernel reported a device-side timeout during warm-up")
+
+        sampler = ClockSampler(physical_gpu_index(local_rank)) if rank == 0 else None
+        ops.inner.timing_events = []
+        ms = timed(lambda: layer(logits, xq, xs), args.steps)
+        ev = ops.inner.timing_events
+        ops.inner.timing_events = None
+        clocks = sampler.stop() if sampler is not None else None
+        g1 = [a.elapsed_time(b) for (n, a, b) in ev if n == "gemm1"]
+        g2 = [a.elapsed_time(b) for (n, a, b) in ev if n == "gemm2"]
+        rows_in = layer.last_plan.rows_in
+        imb = torch.tensor([float(rows_in)], device=dev, dtype=torch.float64)
+        imb_max = imb.clone()
+        dist.all_reduce(imb_max, op=dist.ReduceOp.MAX)
+        dist.all_reduce(imb, op=dist.ReduceOp.SUM)
+        imbalance = float(imb_max.item()) / (float(imb.item()) / world)
+
+        # end to end: pinned host inputs in, pinned host output back, every step
+        h_logits, h_xq, h_xs = logits.cpu().pin_memory(), xq_c.view(torch.uint8).pin_memory(), xs_c.pin_memory()
+        h_out = torch.empty((T, H), dtype=torch.bfloat16).pin_memory()
+        d_logits, d_xq, d_xs = torch.empty_like(logits), torch.empty_like(xq.view(torch.uint8)), torch.empty_like(xs)
+
+        def e2e_step():
+            d_logits.copy_(h_logits, non_blocking=True)
+            d_xq.copy_(h_xq, non_blocking=True)
+            d_xs.copy_(h_xs, non_blocking=True)
+            h_out.copy_(layer(d_logits, d_xq, d_xs), non_blocking=True)
+
+        for _ in range(2):
+            e2e_step()
+        e2e_ms = timed(e2e_step, max(2, args.steps // 2))
+        if _lib.device_status() != 0:
+            raise RuntimeError("a kernel reported a device-side timeout during the timed region")
+
+        if rank != 0:
+            return None
+        peaks = load_peaks()
+        flops = cfg.flops() * world
+        fp8_peak = 2.0 * peaks["bf16_tflops_sustained"]
+        s1_ms = statistics.mean(g1) if g1 else float("nan")
+        s2_ms = statistics.mean(g2) if g2 else float("nan")
+        s1_flops = 2.0 * rows_in * 2 * I * H
+        nplan = layer.last_plan
+        remote = nplan.rows_out - nplan.send_counts[rank]
+        roofline = {"kernel": "moe_gemm_sm100_kernel<1> (stage 1, rank 0)", "bound": "tensor",
+                    "achieved": round(s1_flops / (s1_ms * 1e-3) / 1e12, 1), "peak": fp8_peak,
+                    "peak_source": peaks["source"] + ": 2 x sustained cuBLAS bf16 (no fp8 peak is measured)",
+                    "unit": "TFLOP/s", "frac": round(s1_flops / (s1_ms * 1e-3) / 1e12 / fp8_peak, 4),
+                    "traffic": None, "ms_per_launch": round(s1_ms, 4), "stage2_ms_per_launch": round(s2_ms, 4),
+                    "rows_received_rank0": rows_in}
+        return {"metric": METRIC, "value": round(flops / (ms * 1e-3) / 1e12, 2), "unit": UNIT, "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate and scales)",
+                "data": "synthetic",
+                "config": {**wl.describe(cfg), "tokens_per_gpu": T, "experts_per_gpu": len(mine),
+                           "tile_m": args.tile_m, "parallelism": f"ep{world}",
+                           "l2_policy": "inputs exceed L2 (dispatched rows and expert weights are GBs per step)"},
+                "roofline": roofline,
+                "comm": {"dispatch_bytes_rank0": int(remote * (H + H // 128 * 4 + 4)),
+                         "combine_bytes_rank0": int(remote * H * 2), "load_imbalance_max_over_mean": round(imbalance, 3)},
+                "cpu_baseline": None,
+                "e2e": {"value": round(flops / (e2e_ms * 1e-3) / 1e12, 2), "unit": UNIT, "ms_per_step": round(e2e_ms, 4),
+                        "h2d_bytes_per_step": int(world * (h_logits.numel() * 4 + h_xq.numel() + h_xs.numel() * 4)),
+                        "d2h_bytes_per_step": int(world * h_out.numel() * 2)},
+                "clocks": clocks,
+                "gpu_launches": args.steps * (1 + (1 if T * k <= 8192 else 3) + 2
+                                              + ops.inner.experts_kernel_launches(rows_in) + 3)}
+    finally:
+        dist.destroy_process_group()

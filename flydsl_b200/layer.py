@@ -34,8 +34,10 @@ class FusedMoEBlockscale:
             raise ValueError(f"w2q must be [E, H, I] = {(E, H, I)}, got {tuple(w2q.shape)}")
         if H % 128 or I % 128:
             raise ValueError("model_dim and inter_dim must be multiples of 128")
-        if stage2_mode not in ("atomic", "reduce"):
-            raise ValueError("stage2_mode must be 'atomic' or 'reduce'")
+        if stage2_mode not in ("atomic", "reduce", "rows"):
+            raise ValueError("stage2_mode must be 'atomic', 'reduce' or 'rows'")
+        if stage2_mode == "rows" and int(topk) != 1:
+            raise ValueError("stage2_mode='rows' (one unweighted output row per input row) needs topk == 1")
         if out_dtype not in (torch.bfloat16, torch.float16):
             raise ValueError("out_dtype must be torch.bfloat16 or torch.float16")
         for name, t, dts in (("w1q", w1q, _FP8), ("w2q", w2q, _FP8), ("w1_scale", w1_scale, (torch.float32,)),
@@ -93,12 +95,15 @@ class FusedMoEBlockscale:
             1 if self.renormalize else 0, stream), "topk_gating_softmax")
 
     def experts_forward(self, topk_ids, topk_weights, xq, x_scale_t, tokens: int, stream: int,
-                        out: torch.Tensor | None = None) -> torch.Tensor:
+                        out: torch.Tensor | None = None, x_scale_row_major: bool = False) -> torch.Tensor:
         """sort -> gather -> stage 1 -> stage 2 for already-routed tokens.
 
         topk_ids i32 [tokens, k] (ids in [0, E) of this layer's experts; ids outside
         that range are ignored), topk_weights f32 [tokens, k], xq e4m3 [tokens, H],
-        x_scale_t f32 [H/128, tokens].
+        x_scale_t f32 [H/128, tokens] (or row-major [tokens, H/128] with
+        ``x_scale_row_major``).  stage2_mode "atomic": weighted atomic accumulation into the
+        zeroed ``out``; "reduce": per-pair rows then a weighted top-k reduce (deterministic);
+        "rows" (topk == 1): the unweighted expert output of every input row.
         """
         T, k, U, E, H, I = tokens, self.topk, self.tile_m, self.E, self.H, self.I
         if T > self.max_tokens:
@@ -114,22 +119,23 @@ class FusedMoEBlockscale:
         _lib.check(lib.flymoe_moe_sorting(
             topk_ids.data_ptr(), topk_weights.data_ptr(), self.sorted_ids.data_ptr(),
             self.sorted_weights.data_ptr(), self.sorted_expert_ids.data_ptr(), self.num_valid_ids.data_ptr(),
-            out.data_ptr(), T * H * out.element_size(), None, self.workspace.data_ptr(),
+            out.data_ptr() if self.stage2_mode == "atomic" else None,
+            T * H * out.element_size() if self.stage2_mode == "atomic" else 0, None, self.workspace.data_ptr(),
             self.workspace.numel(), T, E, k, U, stream), "moe_sorting")
         _lib.check(lib.flymoe_gather_rows(
             xq.data_ptr(), self.xs.data_ptr(), self.sorted_ids.data_ptr(), self.num_valid_ids.data_ptr(),
             T, k, H, _lib.ROWS_BY_TOKEN, cap_rows, stream), "gather_rows")
-        sx_stride = x_scale_t.numel() // (H // 128)
+        sx_stride, sx_row_stride = (1, H // 128) if x_scale_row_major else (x_scale_t.numel() // (H // 128), 1)
         t0 = self._mark()
         _lib.check(lib.flymoe_moe_gemm1(
             self.a2q.data_ptr(), self.a2_scale.data_ptr(), self.cap_rows, self.xs.data_ptr(),
-            x_scale_t.data_ptr(), sx_stride, 1, self.w1q.data_ptr(), self.w1_scale.data_ptr(),
+            x_scale_t.data_ptr(), sx_stride, sx_row_stride, self.w1q.data_ptr(), self.w1_scale.data_ptr(),
             self.sorted_ids.data_ptr(), self.sorted_expert_ids.data_ptr(), self.sorted_weights.data_ptr(),
             self.num_valid_ids.data_ptr(), T, I, H, blocks, E, k, U, 0, _lib.E4M3, _lib.ROWS_SORTED,
             _lib.ROWS_BY_TOKEN, _lib.ROWS_SORTED, self.impl, stream), "moe_gemm1")
         t1 = self._mark()
         accumulate = self.stage2_mode == "atomic"
-        target = out if accumulate else self.pair_out
+        target = self.pair_out if self.stage2_mode == "reduce" else out
         _lib.check(lib.flymoe_moe_gemm2(
             target.data_ptr(), self.a2q.data_ptr(), self.a2_scale.data_ptr(), self.cap_rows,
             self.w2q.data_ptr(), self.w2_scale.data_ptr(), self.sorted_ids.data_ptr(),
@@ -139,7 +145,7 @@ class FusedMoEBlockscale:
         if self.timing_events is not None:
             self.timing_events.append(("gemm1", t0, t1))
             self.timing_events.append(("gemm2", t1, self._mark()))
-        if not accumulate:
+        if self.stage2_mode == "reduce":
             # per-pair rows hold the unweighted expert outputs; weight and sum them here
             _lib.check(lib.flymoe_moe_reduce(
                 self.pair_out.data_ptr(), out.data_ptr(), None, topk_weights.data_ptr(), None, T, k, H,
@@ -162,6 +168,10 @@ class FusedMoEBlockscale:
         """Kernels this layer enqueues per forward (memset of the output not counted)."""
         sort = 1 if tokens * self.topk <= 8192 else 3
         return 1 + sort + 1 + 1 + 1 + (1 if self.stage2_mode == "reduce" else 0)
+
+    def experts_kernel_launches(self, rows: int) -> int:
+        """Kernels experts_forward enqueues for ``rows`` input rows."""
+        return self.kernel_launches(rows) - 1
 
 
 def quant_act_1x128(x: torch.Tensor, stream=None):

@@ -1,0 +1,119 @@
+"""Host-side logic of the expert-parallel layer on CPU ranks (gloo, world size 2 and 4):
+split sizes from the unit-1 sort, count exchange, dispatch/combine ordering and the inverse
+permutation.  Device kernels are replaced by numpy/torch stand-ins behind the ``ops`` seam; the
+expert computation is a stand-in function that depends on (row bytes, scale, global expert id),
+so any mis-routed or mis-ordered row changes the result."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from flydsl_b200 import ep
+from oracle import moe_oracle as orc
+
+T, E, K, H = 37, 8, 3, 256
+
+
+class FakeOps:
+    def __init__(self):
+        self.nvalid = None
+
+    def gate(self, logits):
+        w, idx, _ = orc.topk_gating_softmax(logits, K)
+        return w, idx
+
+    def sort_by_expert(self, ids, w, tokens):
+        s_ids, _, s_e, nv = orc.moe_sorting(ids.numpy(), w.numpy(), E, 1)
+        return torch.from_numpy(s_ids), torch.from_numpy(s_e)
+
+    def pack(self, xq, xs, s_ids, tokens):
+        tok = (s_ids[: tokens * K] & 0xFFFFFF).long()
+        return xq[tok].contiguous(), xs[tok].contiguous()
+
+    def empty_rows(self, rows, like):
+        return torch.empty((rows,) + tuple(like.shape[1:]), dtype=like.dtype)
+
+    def local_experts(self, rx, rs, re_, first, rows):
+        assert rows == 0 or (int(re_.min()) >= first and int(re_.max()) < first + E // dist.get_world_size())
+        return rx.float() * rs.mean(dim=1, keepdim=True) * (re_.view(-1, 1).float() + 1.0)
+
+    def combine(self, back, s_ids, w, tokens):
+        tok = (s_ids[: tokens * K] & 0xFFFFFF).long()
+        slot = (s_ids[: tokens * K] >> 24).long()
+        out = torch.zeros((tokens, back.shape[1]), dtype=torch.float32)
+        out.index_add_(0, tok, back * w[tok, slot].view(-1, 1))
+        return out
+
+
+def _inputs(rank):
+    g = torch.Generator().manual_seed(100 + rank)
+    logits = torch.randn((T, E), generator=g)
+    xq = torch.randint(0, 255, (T, H), generator=g, dtype=torch.uint8)
+    xs = torch.rand((T, H // 128), generator=g) + 0.5
+    return logits, xq, xs
+
+
+def _worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        logits, xq, xs = _inputs(rank)
+        layer = ep.ExpertParallelMoE(FakeOps(), E, K, H)
+        out = layer(logits, xq, xs)
+        w, idx, _ = orc.topk_gating_softmax(logits, K)
+        want = (xq.float() * xs.mean(dim=1, keepdim=True)).unsqueeze(1) * (idx.float() + 1.0).unsqueeze(-1)
+        want = (want * w.unsqueeze(-1)).sum(dim=1)
+        plan = layer.last_plan
+        ok = torch.allclose(out, want, rtol=1e-5, atol=1e-4)
+        counts_ok = sum(plan.send_counts) == T * K and plan.rows_out == T * K
+        gathered = [None] * world
+        dist.all_gather_object(gathered, (plan.send_counts, plan.recv_counts))
+        transposed_ok = all(gathered[r][0][rank] == plan.recv_counts[r] for r in range(world))
+        q.put((rank, bool(ok), bool(counts_ok), bool(transposed_ok), float((out - want).abs().max())))
+    finally:
+        dist.destroy_process_group()
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_dispatch_combine_roundtrip_on_cpu_ranks(world):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, ok, counts_ok, transposed_ok, err in res:
+        assert ok, f"rank {rank}: combined output differs (max abs err {err})"
+        assert counts_ok and transposed_ok
+
+
+def test_split_counts_and_checks():
+    eids = torch.tensor([0, 0, 1, 3, 3, 3, 4, 7, 7], dtype=torch.int32)
+    assert ep.split_counts(eids, 2, 4).tolist() == [6, 3]
+    assert ep.split_counts(eids, 4, 2).tolist() == [3, 3, 1, 2]
+    assert ep.split_counts(eids, 8, 1).tolist() == [2, 1, 0, 3, 1, 0, 0, 2]
+    assert list(ep.expert_range(3, 4, 256)) == list(range(192, 256))
+    with pytest.raises(ValueError):
+        ep.expert_range(0, 3, 256)
+    good = torch.tensor([6, 3])
+    ep.check_counts(good, torch.tensor([1, 2]), 9)
+    with pytest.raises(RuntimeError, match="covers"):
+        ep.check_counts(torch.tensor([6, 2]), good, 9)          # a rank lost a row: caught on the host
+    with pytest.raises(RuntimeError, match="negative"):
+        ep.check_counts(torch.tensor([10, -1]), good, 9)
