@@ -33,6 +33,9 @@ _SIGNATURES = {
     "flymoe_moe_sorting_workspace_elems": (c_int64, [c_int, c_int, c_int, c_int]),
     "flymoe_moe_sorting": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int64, _P, _P, c_int64,
                                    c_int, c_int, c_int, c_int, _P]),
+    "flymoe_moe_sorting_noalloc_max_elems": (c_int64, []),
+    "flymoe_moe_sorting_noalloc": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int64, _P,
+                                           c_int, c_int, c_int, c_int, _P]),
     "flymoe_gather_rows": (c_int, [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P]),
     "flymoe_moe_gemm1": (c_int, [_P, _P, c_int64, _P, _P, c_int64, c_int64, _P, _P, _P, _P, _P, _P,
                                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,

@@ -8,6 +8,8 @@
 //   * P <= kOneBlockMaxPairs : one launch, one block, everything in shared memory.
 //   * otherwise              : count (grid) -> scan (one block) -> scatter (grid),
 //                              per-segment histograms kept in caller-provided scratch.
+#include <stdio.h>
+
 #include "common.cuh"
 
 namespace flymoe {
@@ -308,4 +310,64 @@ extern "C" int flymoe_moe_sorting(const int32_t* topk_ids, const float* topk_wei
   moe_sort_scatter_kernel<<<nblk, kSortThreads, smem_sct, s>>>(a);
   FLYMOE_CUDA_CHECK(cudaGetLastError());
   return FLYMOE_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// Allocation-free variant of the sort.
+//
+// Some hosts of this library may not allocate device memory on their call path at all: a
+// serving loop that has handed the whole device heap to its own pool, a plugin running
+// inside another framework's memory budget, or code that must not touch the allocator
+// because allocation can synchronise the device.  For them the multi-block path's scratch
+// lives in the array below, which every GPU that loads the library holds until exit
+// (kNoAllocScratchElems * 4 bytes = 4 MiB).
+constexpr long long kNoAllocScratchElems = 1ll << 20;
+static __device__ __align__(256) int32_t g_sort_scratch[kNoAllocScratchElems];
+
+namespace flymoe {
+
+// In host code `g_sort_scratch` is only a handle for the symbol, not a device address, so
+// the address is looked up once per device (with that device current) and cached.
+static int noalloc_scratch(int32_t** out) {
+  static int32_t* cached[64] = {nullptr};
+  int dev = 0;
+  FLYMOE_CUDA_CHECK(cudaGetDevice(&dev));
+  FLYMOE_REQUIRE(dev >= 0 && dev < 64, "sorting (no-alloc): device ordinal out of range");
+  if (cached[dev] == nullptr) {
+    int32_t* p = nullptr;
+    FLYMOE_CUDA_CHECK(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_sort_scratch));
+    FLYMOE_REQUIRE(p != nullptr, "sorting (no-alloc): scratch symbol has no device address");
+    cached[dev] = p;
+  }
+  *out = cached[dev];
+  return FLYMOE_OK;
+}
+
+}  // namespace flymoe
+
+extern "C" int64_t flymoe_moe_sorting_noalloc_max_elems(void) { return kNoAllocScratchElems; }
+
+extern "C" int flymoe_moe_sorting_noalloc(const int32_t* topk_ids, const float* topk_weights,
+                                          int32_t* sorted_ids, float* sorted_weights,
+                                          int32_t* sorted_expert_ids, int32_t* num_valid_ids,
+                                          void* moe_buf, int64_t moe_buf_bytes,
+                                          const int32_t* expert_mask, int num_tokens, int num_experts,
+                                          int topk, int unit_size, void* stream) {
+  using namespace flymoe;
+  const int64_t need = flymoe_moe_sorting_workspace_elems(num_tokens, num_experts, topk, unit_size);
+  if (need > kNoAllocScratchElems) {
+    char msg[200];
+    snprintf(msg, sizeof(msg),
+             "sorting (no-alloc): this problem needs %lld int32 of scratch, the built-in array holds %lld; "
+             "use flymoe_moe_sorting with a caller-provided workspace",
+             (long long)need, (long long)kNoAllocScratchElems);
+    set_last_error_msg(msg);
+    return FLYMOE_ERR_WORKSPACE;
+  }
+  int32_t* scratch = nullptr;
+  const int rc = noalloc_scratch(&scratch);
+  if (rc != FLYMOE_OK) return rc;
+  return flymoe_moe_sorting(topk_ids, topk_weights, sorted_ids, sorted_weights, sorted_expert_ids,
+                            num_valid_ids, moe_buf, moe_buf_bytes, expert_mask, scratch,
+                            kNoAllocScratchElems, num_tokens, num_experts, topk, unit_size, stream);
 }

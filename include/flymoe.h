@@ -83,6 +83,24 @@ int flymoe_moe_sorting(const int32_t* topk_ids, const float* topk_weights, int32
                        int32_t* workspace, int64_t workspace_elems, int num_tokens,
                        int num_experts, int topk, int unit_size, void* stream);
 
+/* Same sort for callers that may not allocate device memory on their call path (a serving
+ * loop whose memory pool owns the whole device heap, a plugin living inside another
+ * framework's memory budget, code that must never reach the allocator because allocating
+ * can synchronise the device).  No counterpart in the reference project.  The scratch the
+ * multi-block path needs lives in a 4 MiB array inside the library (held by every GPU that
+ * loads it, until exit): problems whose flymoe_moe_sorting_workspace_elems() exceeds
+ * flymoe_moe_sorting_noalloc_max_elems() (2^20 int32) are rejected with
+ * FLYMOE_ERR_WORKSPACE.  The call itself allocates nothing.  The first call on each
+ * device looks up the array's device address; make that first call outside any stream
+ * capture.  All calls share the one array: two calls whose kernels may overlap on the
+ * GPU (different streams, no dependency between them) race on it. */
+int64_t flymoe_moe_sorting_noalloc_max_elems(void);
+int flymoe_moe_sorting_noalloc(const int32_t* topk_ids, const float* topk_weights,
+                               int32_t* sorted_ids, float* sorted_weights,
+                               int32_t* sorted_expert_ids, int32_t* num_valid_ids, void* moe_buf,
+                               int64_t moe_buf_bytes, const int32_t* expert_mask, int num_tokens,
+                               int num_experts, int topk, int unit_size, void* stream);
+
 /* Copies rows of a one-byte-element matrix into sorted order: dst row r = src row
  * selected by sorted_ids[r] under src_layout (BY_TOKEN or BY_PAIR); pad rows are
  * zero-filled; rows at or beyond num_valid_ids[0] are left untouched.
