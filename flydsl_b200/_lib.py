@@ -8,13 +8,15 @@ error.  Tensors cross the boundary as raw device pointers plus explicit sizes.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_uint8, c_void_p, POINTER
 from pathlib import Path
 
 import torch
 
 LIB_NAME = "libflymoe_sm100.so"
-LIB_PATH = Path(__file__).resolve().parent / LIB_NAME
+# FLYMOE_LIB overrides the path (e.g. an instrumented build of the same sources).
+LIB_PATH = Path(os.environ.get("FLYMOE_LIB", Path(__file__).resolve().parent / LIB_NAME))
 
 F32, F16, BF16, E4M3 = 0, 1, 2, 3
 ROWS_BY_TOKEN, ROWS_BY_PAIR, ROWS_SORTED = 0, 1, 2

@@ -58,6 +58,26 @@ struct __align__(16) SmemCtrl {
 };
 constexpr size_t kSmemBytes = size_t(kStages) * kStageBytes + sizeof(SmemCtrl) + 1024;
 
+// Optional timeline instrumentation (build with -DFLYMOE_TRACE): CTA 0 records clock64()
+// stamps of its producer thread, MMA thread and first epilogue thread for the first
+// kTraceSlots K blocks; flymoe_trace_read() copies them out.
+#ifdef FLYMOE_TRACE
+constexpr int kTraceSlots = 256;
+__device__ long long g_trace[4][kTraceSlots][8];
+__device__ int g_trace_cfg[3] = {0, 0, 0};   // first K-block slot, first tile, CTA to record
+#define TRACE_AT(role, rel, idx) \
+  do { if (int(blockIdx.x) == g_trace_cfg[2] && (rel) >= 0 && (rel) < kTraceSlots) g_trace[role][rel][idx] = clock64(); } while (0)
+#define TRACE(role, slot, idx) TRACE_AT(role, int(slot) - g_trace_cfg[0], idx)
+#define TRACE_E(slot, idx) \
+  do { if (threadIdx.x == 128) TRACE(2, slot, idx); } while (0)
+#define TRACE_T(slot, idx) \
+  do { if (threadIdx.x == 128) TRACE_AT(3, int(slot) - g_trace_cfg[1], idx); } while (0)
+#else
+#define TRACE(role, slot, idx) do {} while (0)
+#define TRACE_E(slot, idx) do {} while (0)
+#define TRACE_T(slot, idx) do {} while (0)
+#endif
+
 // ------------------------------------------------------------------------------ PTX
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -76,6 +96,15 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+  return done;
+}
+__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(done) : "r"(bar), "r"(parity) : "memory");
   return done;
@@ -142,6 +171,16 @@ __device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t* v) {
         "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
         "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
       : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float fast_rcp(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
@@ -236,13 +275,23 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       uint32_t phase = 0;
       const uint32_t tx_bytes = uint32_t(a.tile_m) * BK + kBTileBytes;
       bool ok = true;
+      int tslot = 0;
+      int mb_next = 0, n_next = 0, e_next = -1;
+      if (int(blockIdx.x) < sched.total) {
+        sched.decode(blockIdx.x, mb_next, n_next);
+        e_next = __ldg(a.sorted_expert_ids + mb_next);
+      }
       for (int t = blockIdx.x; t < sched.total && ok; t += gridDim.x) {
-        int mb, n;
-        sched.decode(t, mb, n);
-        const int e = __ldg(a.sorted_expert_ids + mb);
+        const int mb = mb_next, n = n_next, e = e_next;
+        if (t + int(gridDim.x) < sched.total) {          // next tile's expert id: loaded a whole tile early
+          sched.decode(t + gridDim.x, mb_next, n_next);
+          e_next = __ldg(a.sorted_expert_ids + mb_next);
+        }
         if (e < 0 || e >= a.experts) continue;
-        for (int kb = 0; kb < KB; ++kb) {
+        for (int kb = 0; kb < KB; ++kb, ++tslot) {
+          TRACE(0, tslot, 0);
           if (!mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, a.status, 1)) { ok = false; break; }
+          TRACE(0, tslot, 1);
           const uint32_t full = smem_u32(&ctrl->full[stage]);
           const uint32_t sa = smem_u32(smem + size_t(stage) * kStageBytes);
           const uint32_t sb = sa + kATileBytes;
@@ -254,6 +303,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           } else {
             tma_load_3d(sb, &tmap_b, full, kb * BK, n * BN, e);
           }
+          TRACE(0, tslot, 2);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -261,27 +311,53 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       // ---------------------------------------------------------------- MMA issuer
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
-      bool ok = true;
+      bool ok = true, primed = false;
+      int tslot = 0;
+      int mb_next = 0, n_next = 0, e_next = -1;
+      if (int(blockIdx.x) < sched.total) {
+        sched.decode(blockIdx.x, mb_next, n_next);
+        e_next = __ldg(a.sorted_expert_ids + mb_next);
+      }
       for (int t = blockIdx.x; t < sched.total && ok; t += gridDim.x) {
-        int mb, n;
-        sched.decode(t, mb, n);
-        const int e = __ldg(a.sorted_expert_ids + mb);
+        const int e = e_next;
+        if (t + int(gridDim.x) < sched.total) {
+          sched.decode(t + gridDim.x, mb_next, n_next);
+          e_next = __ldg(a.sorted_expert_ids + mb_next);
+        }
         if (e < 0 || e >= a.experts) continue;
-        for (int kb = 0; kb < KB; ++kb) {
-          if (!mbar_wait(smem_u32(&ctrl->tmem_empty[acc]), acc_phase ^ 1, abort_flag, a.status, 2)) { ok = false; break; }
-          if (!mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag, a.status, 3)) { ok = false; break; }
+        const bool next_tile_ok = (t + int(gridDim.x) < sched.total) && e_next >= 0 && e_next < a.experts;
+        for (int kb = 0; kb < KB; ++kb, ++tslot) {
+          TRACE(1, tslot, 0);
+          if (!primed) {
+            if (!mbar_wait(smem_u32(&ctrl->tmem_empty[acc]), acc_phase ^ 1, abort_flag, a.status, 2)) { ok = false; break; }
+            if (!mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag, a.status, 3)) { ok = false; break; }
+          }
+          TRACE(1, tslot, 2);
           tcgen05_fence_after();
           const uint32_t sa = smem_u32(smem + size_t(stage) * kStageBytes);
           const uint64_t adesc = make_smem_desc(sa);
           const uint64_t bdesc = make_smem_desc(sa + kATileBytes);
           const uint32_t d_tmem = tmem_base + uint32_t(acc) * BN;
 #pragma unroll
-          for (int k = 0; k < BK / 32; ++k)
+          for (int k = 0; k < BK / 32 - 1; ++k)
             umma_f8(d_tmem, adesc + uint64_t(k * 2), bdesc + uint64_t(k * 2), kInstrDesc, k > 0 ? 1u : 0u);
+          // While the tensor pipe works on this K block, look whether the next one's operands and
+          // accumulator stage are ready, so that its first MMA can follow this block's last at once.
+          const int nstage = stage + 1 == kStages ? 0 : stage + 1;
+          const uint32_t nphase = stage + 1 == kStages ? phase ^ 1 : phase;
+          const int nacc = acc + 1 == kAccStages ? 0 : acc + 1;
+          const uint32_t nacc_phase = acc + 1 == kAccStages ? acc_phase ^ 1 : acc_phase;
+          // Non-blocking: if either is not ready yet, the blocking wait happens at the top of the
+          // next iteration, after this block has been committed (never hold back a commit).
+          primed = (kb + 1 < KB || next_tile_ok) &&
+                   mbar_test_wait(smem_u32(&ctrl->tmem_empty[nacc]), nacc_phase ^ 1) &&
+                   mbar_test_wait(smem_u32(&ctrl->full[nstage]), nphase);
+          umma_f8(d_tmem, adesc + uint64_t((BK / 32 - 1) * 2), bdesc + uint64_t((BK / 32 - 1) * 2), kInstrDesc, 1u);
           umma_commit(smem_u32(&ctrl->empty[stage]));
           umma_commit(smem_u32(&ctrl->tmem_full[acc]));
-          if (++stage == kStages) { stage = 0; phase ^= 1; }
-          if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
+          TRACE(1, tslot, 3);
+          stage = nstage; phase = nphase;
+          acc = nacc; acc_phase = nacc_phase;
         }
       }
     }
@@ -297,23 +373,27 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     uint32_t acc_phase = 0;
     uint32_t tile_iter = 0;
     bool ok = true;
+    int tslot = 0;
     constexpr int NACC = 128;                // fp32 accumulators per thread
+    // Routing of a tile (expert id, this thread's packed row id) is loaded one tile ahead.
+    const int pad_id = (a.topk << 24) | a.num_tokens;
+    int mb_next = 0, n_next = 0, e_next = -1, id_next = pad_id;
+    auto load_routing = [&](int tt) {
+      sched.decode(tt, mb_next, n_next);
+      e_next = __ldg(a.sorted_expert_ids + mb_next);
+      const int rr = mb_next * a.tile_m + row_in_tile;
+      id_next = (row_in_tile < a.tile_m && rr < valid_rows) ? __ldg(a.sorted_ids + rr) : pad_id;
+    };
+    if (int(blockIdx.x) < sched.total) load_routing(blockIdx.x);
     for (int t = blockIdx.x; t < sched.total && ok; t += gridDim.x) {
-      int mb, n;
-      sched.decode(t, mb, n);
-      const int e = __ldg(a.sorted_expert_ids + mb);
+      const int mb = mb_next, n = n_next, e = e_next, id = id_next;
+      if (t + int(gridDim.x) < sched.total) load_routing(t + gridDim.x);
       if (e < 0 || e >= a.experts) continue;
 
       const int r = mb * a.tile_m + row_in_tile;
       const bool in_tile = row_in_tile < a.tile_m && r < valid_rows;
-      int tok = 0, slot = 0;
-      bool valid = false;
-      if (in_tile) {
-        const int id = __ldg(a.sorted_ids + r);
-        tok = id_token(id);
-        slot = id_slot(id);
-        valid = tok < a.num_tokens && slot < a.topk;
-      }
+      const int tok = id_token(id), slot = id_slot(id);
+      const bool valid = in_tile && tok < a.num_tokens && slot < a.topk;
       long long sidx = 0;
       if (valid) {
         sidx = a.a_scale_layout == FLYMOE_ROWS_BY_TOKEN ? (long long)tok
@@ -335,7 +415,8 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       float sa_next = valid ? __ldg(sa_ptr) : 0.f;
       float s0_next = __ldg(sw0_ptr);
       float s1_next = STAGE == 1 ? __ldg(sw1_ptr) : 0.f;
-      for (int kb = 0; kb < KB; ++kb) {
+      for (int kb = 0; kb < KB; ++kb, ++tslot) {
+        TRACE_E(tslot, 0);
         const float c0 = sa_next * s0_next;
         const float c1 = sa_next * s1_next;
         if (kb + 1 < KB) {
@@ -343,8 +424,10 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           s0_next = __ldg(sw0_ptr + kb + 1);
           if (STAGE == 1) s1_next = __ldg(sw1_ptr + kb + 1);
         }
+        TRACE_E(tslot, 1);
         if (!mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, abort_flag, a.status, 4)) { ok = false; break; }
         tcgen05_fence_after();
+        TRACE_E(tslot, 2);
         if (warp_active && half_ok) {
           const uint32_t tbase = tmem_base + lane_base + uint32_t(acc) * BN;
 #pragma unroll
@@ -356,54 +439,61 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             tmem_ld_x32(tbase + col, v);
             tmem_ld_x32(tbase + col + 32, v + 32);
             tmem_ld_wait();
+            TRACE_E(tslot, 3 + 2 * h);
 #pragma unroll
             for (int j = 0; j < 64; ++j) accv[h * 64 + j] = fmaf(__uint_as_float(v[j]), c, accv[h * 64 + j]);
+            TRACE_E(tslot, 4 + 2 * h);
           }
         }
         tcgen05_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&ctrl->tmem_empty[acc]));
+        TRACE_E(tslot, 7);
         if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
       }
       if (!ok) break;
 
       // ---- tile epilogue -----------------------------------------------------------
+      // Kept short on purpose: this code runs once per tile between two main loops, and a long
+      // straight-line tail (IEEE division, accurate exp) costs more in instruction fetch than in math.
+      TRACE_T(tile_iter, 0);
       const float wgt = (a.doweight && valid) ? __ldg(a.sorted_weights + r) : 1.f;
       if (STAGE == 1) {
         // accv[0..63] = gate, accv[64..127] = up, columns n*128 + wg*64 + j
         float amax = 0.f;
 #pragma unroll
         for (int j = 0; j < 64; ++j) {
-          const float hval = valid ? silu_f32(accv[j]) * accv[64 + j] * wgt : 0.f;
+          const float g = accv[j];
+          const float hval = g * fast_rcp(1.0f + fast_exp2(-1.4426950408889634f * g)) * (accv[64 + j] * wgt);
           accv[j] = hval;
           amax = fmaxf(amax, fabsf(hval));
         }
+        TRACE_T(tile_iter, 1);
         const long long orow = a.out_layout == FLYMOE_ROWS_SORTED ? (long long)r : (long long)tok * a.topk + slot;
         const long long ocol = (long long)n * 128 + wg * 64;
         if (a.out_dtype == FLYMOE_E4M3) {
           const int buf = tile_iter & 1;
           const uint32_t bar = smem_u32(&ctrl->amax_bar[buf]);
-          if (warp_active) ctrl->amax[buf][wg][row_in_tile] = amax;
+          if (warp_active) ctrl->amax[buf][wg][row_in_tile] = valid ? amax : 0.f;
           __syncwarp();
           if (lane == 0) mbar_arrive(bar);
           if (!mbar_wait(bar, (tile_iter >> 1) & 1, abort_flag, a.status, 5)) { ok = false; break; }
+          TRACE_T(tile_iter, 2);
           const bool wr = warp_active && (valid || (in_tile && a.out_layout == FLYMOE_ROWS_SORTED));
           if (wr) {
             const float m = fmaxf(ctrl->amax[buf][0][row_in_tile], ctrl->amax[buf][1][row_in_tile]);
             float sc = __fdiv_rn(m, 448.0f);
             if (sc == 0.f) sc = 1.f;
+            const float inv = valid ? __fdiv_rn(1.0f, sc) : 0.f;     // pad rows: every code becomes 0
             uint8_t* op = static_cast<uint8_t*>(a.out) + orow * a.n_dim + ocol;
 #pragma unroll
             for (int j = 0; j < 64; j += 16) {
               uint4 pk;
-              pk.x = float4_to_e4m3x4(__fdiv_rn(accv[j + 0], sc), __fdiv_rn(accv[j + 1], sc),
-                                      __fdiv_rn(accv[j + 2], sc), __fdiv_rn(accv[j + 3], sc));
-              pk.y = float4_to_e4m3x4(__fdiv_rn(accv[j + 4], sc), __fdiv_rn(accv[j + 5], sc),
-                                      __fdiv_rn(accv[j + 6], sc), __fdiv_rn(accv[j + 7], sc));
-              pk.z = float4_to_e4m3x4(__fdiv_rn(accv[j + 8], sc), __fdiv_rn(accv[j + 9], sc),
-                                      __fdiv_rn(accv[j + 10], sc), __fdiv_rn(accv[j + 11], sc));
-              pk.w = float4_to_e4m3x4(__fdiv_rn(accv[j + 12], sc), __fdiv_rn(accv[j + 13], sc),
-                                      __fdiv_rn(accv[j + 14], sc), __fdiv_rn(accv[j + 15], sc));
+              pk.x = float4_to_e4m3x4(accv[j + 0] * inv, accv[j + 1] * inv, accv[j + 2] * inv, accv[j + 3] * inv);
+              pk.y = float4_to_e4m3x4(accv[j + 4] * inv, accv[j + 5] * inv, accv[j + 6] * inv, accv[j + 7] * inv);
+              pk.z = float4_to_e4m3x4(accv[j + 8] * inv, accv[j + 9] * inv, accv[j + 10] * inv, accv[j + 11] * inv);
+              pk.w = float4_to_e4m3x4(accv[j + 12] * inv, accv[j + 13] * inv, accv[j + 14] * inv, accv[j + 15] * inv);
+              if (!valid) pk = make_uint4(0, 0, 0, 0);
               *reinterpret_cast<uint4*>(op + j) = pk;
             }
             if (wg == 0) a.out_scale[(long long)n * a.out_scale_stride + orow] = sc;
@@ -463,6 +553,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           }
         }
       }
+      TRACE_T(tile_iter, 3);
       ++tile_iter;
     }
   }
@@ -475,6 +566,24 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                  : "memory");
   }
 }
+
+}  // namespace flymoe
+
+#ifdef FLYMOE_TRACE
+// Copies the timeline of the last traced launch to host memory: [4 roles][256 slots][8] int64.
+extern "C" int flymoe_trace_config(int first_slot, int first_tile, int cta) {
+  const int cfg[3] = {first_slot, first_tile, cta};
+  FLYMOE_CUDA_CHECK(cudaMemcpyToSymbol(flymoe::g_trace_cfg, cfg, sizeof(cfg)));
+  return FLYMOE_OK;
+}
+extern "C" int flymoe_trace_read(long long* host_out) {
+  FLYMOE_CUDA_CHECK(cudaDeviceSynchronize());
+  FLYMOE_CUDA_CHECK(cudaMemcpyFromSymbol(host_out, flymoe::g_trace, sizeof(flymoe::g_trace)));
+  return FLYMOE_OK;
+}
+#endif
+
+namespace flymoe {
 
 // ------------------------------------------------------------------------------ host
 static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {

@@ -1,0 +1,87 @@
+"""Expert-parallel layer on 2 (4, 8) GPUs of one box against the single-GPU fused layer.
+
+Each rank gates and dispatches its own tokens; experts are sharded over the ranks.  The
+single-GPU layer in "reduce" mode performs the same arithmetic per (token, slot) pair
+(unweighted bf16 expert output, fp32 weighted sum), so the two results must be bit-identical;
+a token subset is also checked against the CPU oracle.  Skipped when the box has fewer GPUs
+than ranks."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, routing, q):
+    import torch.distributed as dist
+    from flydsl_b200 import _lib, workloads as wl
+    from flydsl_b200.ep import CudaOps, ExpertParallelMoE, expert_range
+    from flydsl_b200.layer import FusedMoEBlockscale
+    from oracle import moe_oracle as orc
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        cfg = wl.MoEConfig("ep-test", 300, 512, 256, 16, 4, 11, routing)
+        T, k, H, E = cfg.tokens, cfg.topk, cfg.model_dim, cfg.experts
+        w1q, w1s, w2q, w2s = wl.make_weights(cfg, device=dev)                    # all experts (for the check)
+        mine = expert_range(rank, world, E)
+        sl = slice(mine.start, mine.stop)
+        logits = wl.make_logits(cfg, rank=rank).to(dev)
+        _x, xq_c, xs_c = wl.make_activations(cfg, rank=rank)
+        xq, xs = xq_c.to(dev), xs_c.to(dev)
+        ops = CudaOps(w1q[sl].contiguous(), w1s[sl].contiguous(), w2q[sl].contiguous(), w2s[sl].contiguous(),
+                      E, k, T, tile_m=128, headroom=1.0)
+        layer = ExpertParallelMoE(ops, E, k, H)
+        out = layer(logits, xq, xs).clone()
+        out2 = layer(logits, xq, xs).clone()                                     # buffers are reused
+        torch.cuda.synchronize()
+        single = FusedMoEBlockscale(w1q, w1s, w2q, w2s, k, max_tokens=T, tile_m=128, stage2_mode="reduce")
+        want = single(logits, xq, xs.t().contiguous())
+        torch.cuda.synchronize()
+        sel = torch.tensor([0, 7, 299])
+        tw, ids, _ = orc.topk_gating_softmax(logits.cpu(), k)
+        o1 = orc.stage1(xq_c[sel], xs_c[sel], w1q.cpu(), w1s.cpu(), ids[sel], cfg.inter_dim)
+        a2q, a2s = orc.requant(o1)
+        ref = orc.stage2(a2q, a2s, w2q.cpu(), w2s.cpu(), ids[sel], tw[sel], H)
+        got = out[sel.to(dev)].float().cpu()
+        oracle_ok = bool(((got - ref).abs() <= 2e-2 + 2e-2 * ref.abs()).all())
+        q.put((rank, bool(torch.equal(out, want)), bool(torch.equal(out, out2)), oracle_ok, _lib.device_status(),
+               layer.last_plan.rows_in))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,routing", [(2, "uniform"), (2, "zipf"), (4, "uniform"), (8, "zipf")])
+def test_expert_parallel_matches_single_gpu(world, routing):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs, found {torch.cuda.device_count()}")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, routing, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    total_rows = 0
+    for rank, same_as_single, repeatable, oracle_ok, status, rows_in in res:
+        assert status == 0, f"rank {rank}: device-side timeout reported"
+        assert same_as_single, f"rank {rank}: expert-parallel output differs from the single-GPU layer"
+        assert repeatable and oracle_ok
+        total_rows += rows_in
+    assert total_rows == world * 300 * 4          # every dispatched row was received exactly once
