@@ -36,7 +36,10 @@ namespace flymoe {
 constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 128;
-constexpr int kStages = 4;
+#ifndef FLYMOE_STAGES
+#define FLYMOE_STAGES 4
+#endif
+constexpr int kStages = FLYMOE_STAGES;
 constexpr int kATileBytes = BM * BK;            // 16 KB
 constexpr int kBTileBytes = BN * BK;            // 32 KB
 constexpr int kStageBytes = kATileBytes + kBTileBytes;
@@ -65,17 +68,43 @@ constexpr size_t kSmemBytes = size_t(kStages) * kStageBytes + sizeof(SmemCtrl) +
 constexpr int kTraceSlots = 256;
 __device__ long long g_trace[4][kTraceSlots][8];
 __device__ int g_trace_cfg[3] = {0, 0, 0};   // first K-block slot, first tile, CTA to record
+// trc_slot0 / trc_tile0 / trc_on are per-thread copies read once at kernel start, so that a
+// trace point costs one clock read and (inside the window) one store, and nothing else.
 #define TRACE_AT(role, rel, idx) \
-  do { if (int(blockIdx.x) == g_trace_cfg[2] && (rel) >= 0 && (rel) < kTraceSlots) g_trace[role][rel][idx] = clock64(); } while (0)
-#define TRACE(role, slot, idx) TRACE_AT(role, int(slot) - g_trace_cfg[0], idx)
+  do { if (trc_on && unsigned(rel) < unsigned(kTraceSlots)) g_trace[role][rel][idx] = clock64(); } while (0)
+#define TRACE(role, slot, idx) TRACE_AT(role, int(slot) - trc_slot0, idx)
 #define TRACE_E(slot, idx) \
   do { if (threadIdx.x == 128) TRACE(2, slot, idx); } while (0)
 #define TRACE_T(slot, idx) \
-  do { if (threadIdx.x == 128) TRACE_AT(3, int(slot) - g_trace_cfg[1], idx); } while (0)
+  do { if (threadIdx.x == 128) TRACE_AT(3, int(slot) - trc_tile0, idx); } while (0)
 #else
 #define TRACE(role, slot, idx) do {} while (0)
 #define TRACE_E(slot, idx) do {} while (0)
 #define TRACE_T(slot, idx) do {} while (0)
+#endif
+
+// Optional whole-kernel wait accounting (build with -DFLYMOE_PROF): every CTA's producer thread,
+// MMA thread and first epilogue thread add up the cycles they spend in each wait and write the
+// sums once at the end; flymoe_prof_read() copies them out: [CTA][role][8].
+#ifdef FLYMOE_PROF
+__device__ long long g_prof[256][3][8];
+#define PROF_DECL long long prof_t0 = clock64(), prof_s = 0, prof_w[6] = {0, 0, 0, 0, 0, 0};
+#define PROF_START prof_s = clock64();
+#define PROF_STOP(i) prof_w[i] += clock64() - prof_s;
+#define PROF_COUNT(i) prof_w[i] += 1;
+#define PROF_WRITE(role)                                                         \
+  do {                                                                           \
+    if (blockIdx.x < 256) {                                                      \
+      g_prof[blockIdx.x][role][0] = clock64() - prof_t0;                         \
+      for (int pi = 0; pi < 6; ++pi) g_prof[blockIdx.x][role][1 + pi] = prof_w[pi]; \
+    }                                                                            \
+  } while (0)
+#else
+#define PROF_DECL
+#define PROF_START
+#define PROF_STOP(i)
+#define PROF_COUNT(i)
+#define PROF_WRITE(role) do {} while (0)
 #endif
 
 // ------------------------------------------------------------------------------ PTX
@@ -115,13 +144,16 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
   return t;
 }
 // Bounded wait.  Returns false when the CTA is aborting or the time limit ran out.
+// `backoff_ns` > 0 makes a role that has slack sleep between polls instead of competing for
+// issue slots with the epilogue warps of its scheduler partition.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int code) {
+                                          int* status, int code, unsigned backoff_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_timer_ns();
 #pragma unroll 1
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (backoff_ns) __nanosleep(backoff_ns);
     if ((it & 0xFF) == 0) {
       if (*abort_flag) return false;
       if (global_timer_ns() - t0 > kWaitLimitNs) {
@@ -171,6 +203,20 @@ __device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t* v) {
         "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
         "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
       : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ unsigned long long pack_f32x2(float x) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %1};" : "=l"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(unsigned long long p, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(p));
+}
+// acc.lo += v0 * c.lo ; acc.hi += v1 * c.hi  (one instruction on sm_100)
+__device__ __forceinline__ void ffma2(unsigned long long& acc, uint32_t v0, uint32_t v1, unsigned long long c) {
+  unsigned long long v;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "r"(v0), "r"(v1));
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(v), "l"(c));
 }
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -235,6 +281,10 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int KB = a.k_dim / BK;
+#ifdef FLYMOE_TRACE
+  const int trc_slot0 = g_trace_cfg[0], trc_tile0 = g_trace_cfg[1];
+  const bool trc_on = int(blockIdx.x) == g_trace_cfg[2];
+#endif
 
   const int valid_rows = min(__ldg(a.num_valid_ids), a.size_expert_ids * a.tile_m);
   TileSched sched;
@@ -267,15 +317,26 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   tcgen05_fence_after();
   const uint32_t tmem_base = ctrl->tmem_base;
 
+  // Register re-split: 384 threads x 168 registers are allocated at launch; the producer warpgroup
+  // drops to 40 and the two epilogue warpgroups rise to 232 (128*40 + 256*232 = 384*168 exactly --
+  // a larger request would wait forever for registers that are never released).
+  static_assert(128 * 40 + 256 * 232 <= kNumThreads * 168, "setmaxnreg split exceeds the launch allocation");
   if (warp < 4) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
     if (warp == 0 && lane == 0) {
       // ---------------------------------------------------------------- TMA producer
       int stage = 0;
       uint32_t phase = 0;
+#if defined(FLYMOE_EXP_SMALL_A)
+      const uint32_t tx_bytes = 16u * BK + kBTileBytes;          // timing experiment: 16-row A box
+#elif defined(FLYMOE_EXP_HALF_B)
+      const uint32_t tx_bytes = uint32_t(a.tile_m) * BK + kBTileBytes / 2;   // timing experiment: half of B
+#else
       const uint32_t tx_bytes = uint32_t(a.tile_m) * BK + kBTileBytes;
+#endif
       bool ok = true;
       int tslot = 0;
+      PROF_DECL
       int mb_next = 0, n_next = 0, e_next = -1;
       if (int(blockIdx.x) < sched.total) {
         sched.decode(blockIdx.x, mb_next, n_next);
@@ -290,7 +351,9 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         if (e < 0 || e >= a.experts) continue;
         for (int kb = 0; kb < KB; ++kb, ++tslot) {
           TRACE(0, tslot, 0);
-          if (!mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, a.status, 1)) { ok = false; break; }
+          PROF_START
+          if (!mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, a.status, 1, 64)) { ok = false; break; }
+          PROF_STOP(0) PROF_COUNT(5)
           TRACE(0, tslot, 1);
           const uint32_t full = smem_u32(&ctrl->full[stage]);
           const uint32_t sa = smem_u32(smem + size_t(stage) * kStageBytes);
@@ -299,7 +362,9 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           tma_load_2d(sa, &tmap_a, full, kb * BK, mb * a.tile_m);
           if (STAGE == 1) {
             tma_load_3d(sb, &tmap_b, full, kb * BK, n * 128, e);
+#ifndef FLYMOE_EXP_HALF_B
             tma_load_3d(sb + 128 * BK, &tmap_b, full, kb * BK, a.n_dim + n * 128, e);
+#endif
           } else {
             tma_load_3d(sb, &tmap_b, full, kb * BK, n * BN, e);
           }
@@ -307,12 +372,14 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
+      PROF_WRITE(0);
     } else if (warp == 1 && lane == 0) {
       // ---------------------------------------------------------------- MMA issuer
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true, primed = false;
       int tslot = 0;
+      PROF_DECL
       int mb_next = 0, n_next = 0, e_next = -1;
       if (int(blockIdx.x) < sched.total) {
         sched.decode(blockIdx.x, mb_next, n_next);
@@ -329,9 +396,13 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         for (int kb = 0; kb < KB; ++kb, ++tslot) {
           TRACE(1, tslot, 0);
           if (!primed) {
+            PROF_START
             if (!mbar_wait(smem_u32(&ctrl->tmem_empty[acc]), acc_phase ^ 1, abort_flag, a.status, 2)) { ok = false; break; }
+            PROF_STOP(0) PROF_START
             if (!mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag, a.status, 3)) { ok = false; break; }
-          }
+            PROF_STOP(1)
+          } else { PROF_COUNT(2) }
+          PROF_COUNT(5) PROF_START
           TRACE(1, tslot, 2);
           tcgen05_fence_after();
           const uint32_t sa = smem_u32(smem + size_t(stage) * kStageBytes);
@@ -355,11 +426,14 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           umma_f8(d_tmem, adesc + uint64_t((BK / 32 - 1) * 2), bdesc + uint64_t((BK / 32 - 1) * 2), kInstrDesc, 1u);
           umma_commit(smem_u32(&ctrl->empty[stage]));
           umma_commit(smem_u32(&ctrl->tmem_full[acc]));
+          PROF_STOP(3)
           TRACE(1, tslot, 3);
+
           stage = nstage; phase = nphase;
           acc = nacc; acc_phase = nacc_phase;
         }
       }
+      PROF_WRITE(1);
     }
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
@@ -372,8 +446,12 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     int acc = 0;
     uint32_t acc_phase = 0;
     uint32_t tile_iter = 0;
-    bool ok = true;
+    bool ok = true, full_seen = false;
     int tslot = 0;
+    PROF_DECL
+    static_assert(kAccStages == 2, "the epilogue's stage/phase stepping assumes two accumulator stages");
+    const uint32_t full_bar0 = smem_u32(&ctrl->tmem_full[0]);     // stage 1's barrier is 8 bytes further
+    const uint32_t empty_bar0 = smem_u32(&ctrl->tmem_empty[0]);
     constexpr int NACC = 128;                // fp32 accumulators per thread
     // Routing of a tile (expert id, this thread's packed row id) is loaded one tile ahead.
     const int pad_id = (a.topk << 24) | a.num_tokens;
@@ -406,56 +484,89 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       const int blk1 = STAGE == 1 ? a.n_dim / 128 + n : blk0;
       const bool half_ok = STAGE == 1 ? true : (n * BN + wg * 128 < a.n_dim);
       const float* sw0_ptr = a.scale_w + ((long long)e * wblk_per_expert + (half_ok ? blk0 : 0)) * KB;
-      const float* sw1_ptr = a.scale_w + ((long long)e * wblk_per_expert + blk1) * KB;
+      const int sw1_off = (blk1 - (half_ok ? blk0 : 0)) * KB;      // up-projection scales, relative to sw0_ptr
 
-      float accv[NACC];
+      // fp32 accumulators held as packed pairs so the scale-FMA runs as fma.rn.f32x2
+      unsigned long long acc2[NACC / 2];
 #pragma unroll
-      for (int j = 0; j < NACC; ++j) accv[j] = 0.f;
+      for (int j = 0; j < NACC / 2; ++j) acc2[j] = 0ull;
 
       float sa_next = valid ? __ldg(sa_ptr) : 0.f;
       float s0_next = __ldg(sw0_ptr);
-      float s1_next = STAGE == 1 ? __ldg(sw1_ptr) : 0.f;
+      float s1_next = STAGE == 1 ? __ldg(sw0_ptr + sw1_off) : 0.f;
+      const float* sa_run = sa_ptr;            // running pointer: one add per K block, no multiply
+      const bool more_tiles = (t + int(gridDim.x) < sched.total) && e_next >= 0 && e_next < a.experts;
+      const bool work = warp_active && half_ok;
+      // stage 1: first half = gate columns, second half = up columns; stage 2: two halves of 128 columns
+      const uint32_t tcol0 = tmem_base + lane_base + (STAGE == 1 ? uint32_t(wg * 64) : uint32_t(wg * 128));
+      const uint32_t tcol1 = tmem_base + lane_base + (STAGE == 1 ? uint32_t(128 + wg * 64) : uint32_t(wg * 128 + 64));
       for (int kb = 0; kb < KB; ++kb, ++tslot) {
         TRACE_E(tslot, 0);
-        const float c0 = sa_next * s0_next;
-        const float c1 = sa_next * s1_next;
-        if (kb + 1 < KB) {
-          sa_next = valid ? __ldg(sa_ptr + (long long)(kb + 1) * a.sa_stride) : 0.f;
-          s0_next = __ldg(sw0_ptr + kb + 1);
-          if (STAGE == 1) s1_next = __ldg(sw1_ptr + kb + 1);
-        }
+        const unsigned long long c0 = pack_f32x2(sa_next * s0_next);
+        const unsigned long long c1 = STAGE == 1 ? pack_f32x2(sa_next * s1_next) : c0;
         TRACE_E(tslot, 1);
-        if (!mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, abort_flag, a.status, 4)) { ok = false; break; }
+        PROF_START
+        if (!full_seen &&
+            !mbar_wait(full_bar0 + uint32_t(acc) * 8u, acc_phase, abort_flag, a.status, 4)) { ok = false; break; }
+        PROF_STOP(0) PROF_COUNT(5)
+        if (full_seen) { PROF_COUNT(2) }
         tcgen05_fence_after();
         TRACE_E(tslot, 2);
-        if (warp_active && half_ok) {
-          const uint32_t tbase = tmem_base + lane_base + uint32_t(acc) * BN;
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            // stage 1: h=0 gate columns, h=1 up columns; stage 2: two halves of 128 columns
-            const uint32_t col = STAGE == 1 ? uint32_t(h * 128 + wg * 64) : uint32_t(wg * 128 + h * 64);
-            const float c = (STAGE == 1 && h == 1) ? c1 : c0;
-            uint32_t v[64];
-            tmem_ld_x32(tbase + col, v);
-            tmem_ld_x32(tbase + col + 32, v + 32);
-            tmem_ld_wait();
-            TRACE_E(tslot, 3 + 2 * h);
-#pragma unroll
-            for (int j = 0; j < 64; ++j) accv[h * 64 + j] = fmaf(__uint_as_float(v[j]), c, accv[h * 64 + j]);
-            TRACE_E(tslot, 4 + 2 * h);
-          }
+        if (kb + 1 < KB) {                     // next K block's scales: in flight during this block's math
+          sa_run += a.sa_stride;
+          sa_next = valid ? __ldg(sa_run) : 0.f;
+          s0_next = __ldg(sw0_ptr + kb + 1);
+          if (STAGE == 1) s1_next = __ldg(sw0_ptr + kb + 1 + sw1_off);
         }
+        const uint32_t stage_off = uint32_t(acc) * BN;
+        uint32_t v0[32], v1[32];
+        // Four 32-column chunks through two register buffers: each tcgen05.ld is in flight while the
+        // previous chunk is folded into the accumulators.
+        if (work) {
+          tmem_ld_x32(tcol0 + stage_off, v0);
+          tmem_ld_wait();
+          tmem_ld_x32(tcol0 + stage_off + 32, v1);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) ffma2(acc2[j], v0[2 * j], v0[2 * j + 1], c0);
+          tmem_ld_wait();
+          TRACE_E(tslot, 3);
+          tmem_ld_x32(tcol1 + stage_off, v0);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) ffma2(acc2[16 + j], v1[2 * j], v1[2 * j + 1], c0);
+          tmem_ld_wait();
+          TRACE_E(tslot, 4);
+          tmem_ld_x32(tcol1 + stage_off + 32, v1);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) ffma2(acc2[32 + j], v0[2 * j], v0[2 * j + 1], c1);
+          tmem_ld_wait();
+          TRACE_E(tslot, 5);
+        }
+        // The K block's partial sums are in registers now: hand the TMEM stage back before the
+        // last chunk's FMAs, and look (without blocking) whether the next stage is already full.
         tcgen05_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&ctrl->tmem_empty[acc]));
+        if (lane == 0) mbar_arrive(empty_bar0 + uint32_t(acc) * 8u);
+        const int nacc = acc ^ 1;
+        const uint32_t nacc_phase = acc_phase ^ uint32_t(acc);
+        full_seen = (kb + 1 < KB || more_tiles) && mbar_test_wait(full_bar0 + uint32_t(nacc) * 8u, nacc_phase);
+        TRACE_E(tslot, 6);
+        if (work) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) ffma2(acc2[48 + j], v1[2 * j], v1[2 * j + 1], c1);
+        }
         TRACE_E(tslot, 7);
-        if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
+        acc = nacc;
+        acc_phase = nacc_phase;
       }
       if (!ok) break;
+      float accv[NACC];
+#pragma unroll
+      for (int j = 0; j < NACC / 2; ++j) unpack_f32x2(acc2[j], accv[2 * j], accv[2 * j + 1]);
 
       // ---- tile epilogue -----------------------------------------------------------
       // Kept short on purpose: this code runs once per tile between two main loops, and a long
       // straight-line tail (IEEE division, accurate exp) costs more in instruction fetch than in math.
+      PROF_START
       TRACE_T(tile_iter, 0);
       const float wgt = (a.doweight && valid) ? __ldg(a.sorted_weights + r) : 1.f;
       if (STAGE == 1) {
@@ -554,8 +665,10 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         }
       }
       TRACE_T(tile_iter, 3);
+      PROF_STOP(1) PROF_COUNT(4)
       ++tile_iter;
     }
+    if (threadIdx.x == 128) PROF_WRITE(2);
   }
 
   tcgen05_fence_before();
@@ -568,6 +681,14 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 }
 
 }  // namespace flymoe
+
+#ifdef FLYMOE_PROF
+extern "C" int flymoe_prof_read(long long* host_out) {
+  FLYMOE_CUDA_CHECK(cudaDeviceSynchronize());
+  FLYMOE_CUDA_CHECK(cudaMemcpyFromSymbol(host_out, flymoe::g_prof, sizeof(flymoe::g_prof)));
+  return FLYMOE_OK;
+}
+#endif
 
 #ifdef FLYMOE_TRACE
 // Copies the timeline of the last traced launch to host memory: [4 roles][256 slots][8] int64.
@@ -632,7 +753,11 @@ int launch_gemm_sm100(int stage, const GemmArgs& a, cudaStream_t stream) {
   {
     cuuint64_t dims[2] = {cuuint64_t(a.k_dim), cuuint64_t(a.a_rows)};
     cuuint64_t strides[1] = {cuuint64_t(a.k_dim)};
+#ifdef FLYMOE_EXP_SMALL_A
+    cuuint32_t box[2] = {cuuint32_t(BK), 16};
+#else
     cuuint32_t box[2] = {cuuint32_t(BK), cuuint32_t(a.tile_m)};
+#endif
     int rc = make_map(&map_a, a.a, 2, dims, strides, box);
     if (rc != FLYMOE_OK) return rc;
   }
