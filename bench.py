@@ -88,6 +88,23 @@ def run_reference_arm(args, cfg, rank: int) -> None:
     print(json.dumps(line), flush=True)
 
 
+def auto_tile_m(cfg: wl.MoEConfig, world: int = 1) -> int:
+    """Row block = sort unit: the smallest of 16/32/64/128 that covers the mean rows per expert."""
+    rows = cfg.tokens * cfg.topk / cfg.experts * 1.0
+    for m in (16, 32, 64):
+        if rows <= m:
+            return m
+    return 128
+
+
+# DRAM bytes per launch of the stage-1 kernel from ncu (dram__bytes_read.sum + dram__bytes_write.sum),
+# keyed by (workload, tile_m); sources and scaling are in profiles/.
+MEASURED_TRAFFIC = {
+    ("c4a-dsv3-prefill-uniform", 128): 8.164e9,   # 8 x the T=512/E=32 capture (same tokens per expert)
+    ("c3-dsv3-decode", 16): 6.60e9,               # full-size capture
+}
+
+
 # ------------------------------------------------------------------------------------ GPU arm
 def run_single_gpu(args, cfg) -> dict:
     from flydsl_b200 import _lib
@@ -148,7 +165,8 @@ def run_single_gpu(args, cfg) -> dict:
     fp8_peak = 2.0 * peaks["bf16_tflops"]
     roofline = {"kernel": "moe_gemm_sm100_kernel<1> (stage 1)", "bound": "hbm", "achieved": round(achieved, 1),
                 "peak": peaks["hbm_gbs"], "peak_source": peaks["source"], "unit": "GB/s",
-                "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None,
+                "frac": round(achieved / peaks["hbm_gbs"], 4),
+                "traffic": MEASURED_TRAFFIC.get((cfg.name, args.tile_m)),
                 "algorithmic_bytes_per_launch": int(s1_bytes), "ms_per_launch": round(s1_ms, 4),
                 "stage2_ms_per_launch": round(s2_ms, 4),
                 "tensor_tflops": round(s1_flops / (s1_ms * 1e-3) / 1e12, 1),
@@ -212,7 +230,8 @@ def main() -> None:
     ap.add_argument("--workload", default=None, help="c1|c2|c3|c4a|c4b|c5a|c5b (default c4a, or c5a when --gpus > 1)")
     ap.add_argument("--tokens", type=int, default=None, help="override the token count (c2 sweep)")
     ap.add_argument("--experts", type=int, default=None, help="override the expert count (small profiling cases)")
-    ap.add_argument("--tile-m", type=int, default=128)
+    ap.add_argument("--tile-m", type=int, default=0,
+                    help="sort unit = GEMM row block (16/32/64/128); 0 = pick from the rows per expert")
     ap.add_argument("--stage2-mode", default="atomic", choices=["atomic", "reduce"])
     ap.add_argument("--cpu-experts", type=int, default=24, help="experts in the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -228,6 +247,8 @@ def main() -> None:
         from dataclasses import replace
         cfg = replace(cfg, experts=args.experts, name=f"{cfg.name}-E{args.experts}")
 
+    if args.tile_m == 0:
+        args.tile_m = auto_tile_m(cfg, max(1, world))
     if args.impl == "reference":
         run_reference_arm(args, cfg, rank)
         return

@@ -3,8 +3,8 @@
 // One persistent CTA per SM walks a static sequence of (sorted row block, N tile)
 // tiles.  Warp roles (384 threads):
 //   warp 0      TMA producer: per 128-wide K block one A box (tile_m sorted rows x 128 B)
-//               and 256 weight rows x 128 B into a 4-deep shared-memory ring
-//               (128-byte swizzle, K-major).
+//               and 256 weight rows x 128 B into a 4-deep (stage 2: 3-deep) shared-memory
+//               ring (128-byte swizzle, K-major).
 //   warp 1      MMA issuer: four tcgen05.mma (kind::f8f6f4, M=128, N=256, K=32) per K
 //               block into one of two 256-column TMEM accumulator stages, started from
 //               zero for every K block; tcgen05.commit releases the smem stage and
@@ -18,9 +18,10 @@
 // output); each warpgroup takes 64 gate + 64 up columns, computes silu(gate)*up and
 // either stores f16/bf16 or requantises to e4m3 with the per-row 1x128 scale (row amax
 // exchanged between the two warpgroups through shared memory).
-// Stage 2 tile: 256 rows of W2; each warpgroup takes 128 columns, multiplies by the
-// routing weight and adds into out[token] with vector reductions (or stores per-pair
-// rows for a later top-k reduce).
+// Stage 2 tile: 256 rows of W2; each warpgroup takes 128 columns; every thread multiplies
+// its row by the routing weight, parks the 256 bytes in a private shared-memory slot and
+// adds them into out[token] with one bulk reduce (cp.reduce.async.bulk), or bulk-stores
+// per-pair rows for a later top-k reduce.
 //
 // Every wait is bounded: when one gives up it raises the CTA's abort flag and the
 // device status word, every role drains out, TMEM is released and the kernel returns.
@@ -36,10 +37,16 @@ namespace flymoe {
 constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 128;
-#ifndef FLYMOE_STAGES
-#define FLYMOE_STAGES 4
-#endif
-constexpr int kStages = FLYMOE_STAGES;
+constexpr int kMaxStages = 4;
+// Depth of the shared-memory operand ring.  Stage 2 gives one slot up for a staging area from
+// which finished output rows leave by bulk reduce/store (measured: a 3-deep ring is as fast as 4).
+template <int STAGE> struct RingDepth { static constexpr int value = STAGE == 1 ? 4 : 3; };
+// Per-epilogue-thread staging slot for finished output: stage 2 holds 256 B of 16-bit results,
+// stage 1 holds 64 e4m3 codes; 16 B of skew keep 16-byte shared-memory stores conflict-free.
+template <int STAGE> struct Staging {
+  static constexpr int stride = STAGE == 1 ? 80 : 272;
+  static constexpr int bytes = 256 * stride;
+};
 constexpr int kATileBytes = BM * BK;            // 16 KB
 constexpr int kBTileBytes = BN * BK;            // 32 KB
 constexpr int kStageBytes = kATileBytes + kBTileBytes;
@@ -50,8 +57,8 @@ constexpr int kEpilogueWarps = 8;
 constexpr unsigned long long kWaitLimitNs = 4000000000ull;   // 4 s
 
 struct __align__(16) SmemCtrl {
-  unsigned long long full[kStages];
-  unsigned long long empty[kStages];
+  unsigned long long full[kMaxStages];
+  unsigned long long empty[kMaxStages];
   unsigned long long tmem_full[kAccStages];
   unsigned long long tmem_empty[kAccStages];
   unsigned long long amax_bar[2];
@@ -59,7 +66,9 @@ struct __align__(16) SmemCtrl {
   int abort_flag;
   float amax[2][2][BM];
 };
-constexpr size_t kSmemBytes = size_t(kStages) * kStageBytes + sizeof(SmemCtrl) + 1024;
+template <int STAGE> constexpr size_t smem_bytes() {
+  return size_t(RingDepth<STAGE>::value) * kStageBytes + Staging<STAGE>::bytes + sizeof(SmemCtrl) + 1024;
+}
 
 // Optional timeline instrumentation (build with -DFLYMOE_TRACE): CTA 0 records clock64()
 // stamps of its producer thread, MMA thread and first epilogue thread for the first
@@ -119,6 +128,11 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Arrive without release ordering: for hand-offs that publish no memory (a TMEM stage whose
+// loads have already completed), so the arrive need not wait for this thread's loads in flight.
+__device__ __forceinline__ void mbar_arrive_relaxed(uint32_t bar) {
+  asm volatile("mbarrier.arrive.relaxed.cta.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t done;
@@ -244,18 +258,26 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
 constexpr uint32_t kInstrDesc = (1u << 4) | (0u << 7) | (0u << 10) | (uint32_t(BN >> 3) << 17) |
                                 (uint32_t(BM >> 4) << 24);
 
+// 256-byte bulk operations from this thread's staging slot to a contiguous global row segment.
+__device__ __forceinline__ void bulk_reduce_add_bf16_256(void* g, uint32_t s) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.noftz.bf16 [%0], [%1], 256;" ::"l"(g), "r"(s)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_reduce_add_f16_256(void* g, uint32_t s) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.noftz.f16 [%0], [%1], 256;" ::"l"(g), "r"(s)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store_256(void* g, uint32_t s) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], 256;" ::"l"(g), "r"(s) : "memory");
+}
+__device__ __forceinline__ void bulk_store_64(void* g, uint32_t s) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], 64;" ::"l"(g), "r"(s) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void red_add_v4_f32(float* p, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
-__device__ __forceinline__ void red_add_v4_bf16x2(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-  asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d)
-               : "memory");
-}
-__device__ __forceinline__ void red_add_v4_f16x2(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-  asm volatile("red.global.add.noftz.v4.f16x2 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d)
-               : "memory");
-}
-
 // ------------------------------------------------------------------------------ tiles
 struct TileSched {
   int num_mblocks, num_ntiles, total, group_m;
@@ -275,7 +297,9 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                       const GemmArgs a, const int group_m) {
   extern __shared__ uint8_t smem_dyn[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
-  SmemCtrl* ctrl = reinterpret_cast<SmemCtrl*>(smem + size_t(kStages) * kStageBytes);
+  constexpr int kStages = RingDepth<STAGE>::value;
+  uint8_t* staging = smem + size_t(kStages) * kStageBytes;
+  SmemCtrl* ctrl = reinterpret_cast<SmemCtrl*>(staging + Staging<STAGE>::bytes);
   volatile int* abort_flag = &ctrl->abort_flag;
 
   const int warp = threadIdx.x >> 5;
@@ -446,7 +470,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     int acc = 0;
     uint32_t acc_phase = 0;
     uint32_t tile_iter = 0;
-    bool ok = true, full_seen = false;
+    bool ok = true;
     int tslot = 0;
     PROF_DECL
     static_assert(kAccStages == 2, "the epilogue's stage/phase stepping assumes two accumulator stages");
@@ -486,6 +510,8 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       const float* sw0_ptr = a.scale_w + ((long long)e * wblk_per_expert + (half_ok ? blk0 : 0)) * KB;
       const int sw1_off = (blk1 - (half_ok ? blk0 : 0)) * KB;      // up-projection scales, relative to sw0_ptr
 
+      // routing weight of this row: loaded now, used after the K loop
+      const float wgt = (a.doweight && valid) ? __ldg(a.sorted_weights + r) : 1.f;
       // fp32 accumulators held as packed pairs so the scale-FMA runs as fma.rn.f32x2
       unsigned long long acc2[NACC / 2];
 #pragma unroll
@@ -495,36 +521,33 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       float s0_next = __ldg(sw0_ptr);
       float s1_next = STAGE == 1 ? __ldg(sw0_ptr + sw1_off) : 0.f;
       const float* sa_run = sa_ptr;            // running pointer: one add per K block, no multiply
-      const bool more_tiles = (t + int(gridDim.x) < sched.total) && e_next >= 0 && e_next < a.experts;
       const bool work = warp_active && half_ok;
       // stage 1: first half = gate columns, second half = up columns; stage 2: two halves of 128 columns
       const uint32_t tcol0 = tmem_base + lane_base + (STAGE == 1 ? uint32_t(wg * 64) : uint32_t(wg * 128));
       const uint32_t tcol1 = tmem_base + lane_base + (STAGE == 1 ? uint32_t(128 + wg * 64) : uint32_t(wg * 128 + 64));
+      // One K block = four 32-column chunks through two register buffers: each tcgen05.ld is in
+      // flight while the previous chunk is folded into the accumulators.
+      uint32_t v0[32], v1[32];
       for (int kb = 0; kb < KB; ++kb, ++tslot) {
         TRACE_E(tslot, 0);
         const unsigned long long c0 = pack_f32x2(sa_next * s0_next);
         const unsigned long long c1 = STAGE == 1 ? pack_f32x2(sa_next * s1_next) : c0;
-        TRACE_E(tslot, 1);
+        const uint32_t stage_off = uint32_t(acc) * BN;
         PROF_START
-        if (!full_seen &&
-            !mbar_wait(full_bar0 + uint32_t(acc) * 8u, acc_phase, abort_flag, a.status, 4)) { ok = false; break; }
+        if (!mbar_wait(full_bar0 + uint32_t(acc) * 8u, acc_phase, abort_flag, a.status, 4)) { ok = false; break; }
         PROF_STOP(0) PROF_COUNT(5)
-        if (full_seen) { PROF_COUNT(2) }
         tcgen05_fence_after();
-        TRACE_E(tslot, 2);
+        TRACE_E(tslot, 1);
+        if (work) tmem_ld_x32(tcol0 + stage_off, v0);
         if (kb + 1 < KB) {                     // next K block's scales: in flight during this block's math
           sa_run += a.sa_stride;
           sa_next = valid ? __ldg(sa_run) : 0.f;
           s0_next = __ldg(sw0_ptr + kb + 1);
           if (STAGE == 1) s1_next = __ldg(sw0_ptr + kb + 1 + sw1_off);
         }
-        const uint32_t stage_off = uint32_t(acc) * BN;
-        uint32_t v0[32], v1[32];
-        // Four 32-column chunks through two register buffers: each tcgen05.ld is in flight while the
-        // previous chunk is folded into the accumulators.
         if (work) {
-          tmem_ld_x32(tcol0 + stage_off, v0);
           tmem_ld_wait();
+          TRACE_E(tslot, 2);
           tmem_ld_x32(tcol0 + stage_off + 32, v1);
 #pragma unroll
           for (int j = 0; j < 16; ++j) ffma2(acc2[j], v0[2 * j], v0[2 * j + 1], c0);
@@ -541,22 +564,20 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           tmem_ld_wait();
           TRACE_E(tslot, 5);
         }
-        // The K block's partial sums are in registers now: hand the TMEM stage back before the
-        // last chunk's FMAs, and look (without blocking) whether the next stage is already full.
-        tcgen05_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(empty_bar0 + uint32_t(acc) * 8u);
-        const int nacc = acc ^ 1;
-        const uint32_t nacc_phase = acc_phase ^ uint32_t(acc);
-        full_seen = (kb + 1 < KB || more_tiles) && mbar_test_wait(full_bar0 + uint32_t(nacc) * 8u, nacc_phase);
+        // The K block's partial sums are in registers now (tcgen05.wait::ld has returned, so the loads
+        // have completed and need no further ordering): hand the TMEM stage back before the last
+        // chunk's FMAs.  The arrive publishes no memory, hence relaxed; tcgen05.wait::ld is warp-wide
+        // (.sync.aligned), so when lane 0 is past it every lane's loads have landed.
+        if (!work) __syncwarp();
+        if (lane == 0) mbar_arrive_relaxed(empty_bar0 + uint32_t(acc) * 8u);
         TRACE_E(tslot, 6);
         if (work) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) ffma2(acc2[48 + j], v1[2 * j], v1[2 * j + 1], c1);
         }
         TRACE_E(tslot, 7);
-        acc = nacc;
-        acc_phase = nacc_phase;
+        acc_phase ^= uint32_t(acc);
+        acc ^= 1;
       }
       if (!ok) break;
       float accv[NACC];
@@ -568,7 +589,6 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       // straight-line tail (IEEE division, accurate exp) costs more in instruction fetch than in math.
       PROF_START
       TRACE_T(tile_iter, 0);
-      const float wgt = (a.doweight && valid) ? __ldg(a.sorted_weights + r) : 1.f;
       if (STAGE == 1) {
         // accv[0..63] = gate, accv[64..127] = up, columns n*128 + wg*64 + j
         float amax = 0.f;
@@ -596,7 +616,9 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             float sc = __fdiv_rn(m, 448.0f);
             if (sc == 0.f) sc = 1.f;
             const float inv = valid ? __fdiv_rn(1.0f, sc) : 0.f;     // pad rows: every code becomes 0
-            uint8_t* op = static_cast<uint8_t*>(a.out) + orow * a.n_dim + ocol;
+            // 64 codes go through this thread's staging slot and leave as one 64-byte bulk store
+            uint8_t* op = staging + size_t(threadIdx.x - 128) * Staging<STAGE>::stride;
+            bulk_wait_read_all();
 #pragma unroll
             for (int j = 0; j < 64; j += 16) {
               uint4 pk;
@@ -607,6 +629,9 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
               if (!valid) pk = make_uint4(0, 0, 0, 0);
               *reinterpret_cast<uint4*>(op + j) = pk;
             }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            bulk_store_64(static_cast<uint8_t*>(a.out) + orow * a.n_dim + ocol, smem_u32(op));
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             if (wg == 0) a.out_scale[(long long)n * a.out_scale_stride + orow] = sc;
           }
         } else if (warp_active && valid) {
@@ -622,36 +647,23 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             *reinterpret_cast<uint4*>(op + j * 2) = pk;
           }
         }
-      } else if (warp_active && valid && half_ok) {
-        // accv[0..127]: columns n*256 + wg*128 + j
-        const long long ocol = (long long)n * BN + wg * 128;
-        if (a.accumulate) {
-          const long long o = (long long)tok * a.n_dim + ocol;
-          if (a.out_dtype == FLYMOE_F32) {
-            float* op = static_cast<float*>(a.out) + o;
+      } else if (a.out_dtype == FLYMOE_F32) {
+        if (warp_active && valid && half_ok) {
+          // fp32 output: vector reductions straight from registers (accumulate mode only)
+          float* op = static_cast<float*>(a.out) + (long long)tok * a.n_dim + (long long)n * BN + wg * 128;
 #pragma unroll
-            for (int j = 0; j < 128; j += 4)
-              red_add_v4_f32(op + j, accv[j] * wgt, accv[j + 1] * wgt, accv[j + 2] * wgt, accv[j + 3] * wgt);
-          } else {
-            uint8_t* op = static_cast<uint8_t*>(a.out) + o * 2;
-            const bool bf = a.out_dtype == FLYMOE_BF16;
-#pragma unroll
-            for (int j = 0; j < 128; j += 8) {
-              if (bf)
-                red_add_v4_bf16x2(op + j * 2, pack_bf16x2(accv[j] * wgt, accv[j + 1] * wgt),
-                                  pack_bf16x2(accv[j + 2] * wgt, accv[j + 3] * wgt),
-                                  pack_bf16x2(accv[j + 4] * wgt, accv[j + 5] * wgt),
-                                  pack_bf16x2(accv[j + 6] * wgt, accv[j + 7] * wgt));
-              else
-                red_add_v4_f16x2(op + j * 2, pack_f16x2(accv[j] * wgt, accv[j + 1] * wgt),
-                                 pack_f16x2(accv[j + 2] * wgt, accv[j + 3] * wgt),
-                                 pack_f16x2(accv[j + 4] * wgt, accv[j + 5] * wgt),
-                                 pack_f16x2(accv[j + 6] * wgt, accv[j + 7] * wgt));
-            }
-          }
-        } else {
-          const long long o = ((long long)tok * a.topk + slot) * a.n_dim + ocol;
-          uint8_t* op = static_cast<uint8_t*>(a.out) + o * 2;
+          for (int j = 0; j < 128; j += 4)
+            red_add_v4_f32(op + j, accv[j] * wgt, accv[j + 1] * wgt, accv[j + 2] * wgt, accv[j + 3] * wgt);
+        }
+      } else {
+        // 16-bit output: each thread parks its 128 results (256 B) in its own slot of the staging area
+        // and sends them off as ONE bulk reduce-add (or bulk store) of a contiguous row segment, instead
+        // of 16 scattered 16-byte atomics per thread.  The slot is private to the thread, so the only
+        // ordering needed is against the thread's own previous bulk operation.
+        uint8_t* slot_ptr = staging + size_t(threadIdx.x - 128) * Staging<STAGE>::stride;
+        bulk_wait_read_all();
+        TRACE_T(tile_iter, 1);
+        if (warp_active && valid && half_ok) {
           const bool bf = a.out_dtype == FLYMOE_BF16;
 #pragma unroll
           for (int j = 0; j < 128; j += 8) {
@@ -660,8 +672,17 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             pk.y = bf ? pack_bf16x2(accv[j + 2] * wgt, accv[j + 3] * wgt) : pack_f16x2(accv[j + 2] * wgt, accv[j + 3] * wgt);
             pk.z = bf ? pack_bf16x2(accv[j + 4] * wgt, accv[j + 5] * wgt) : pack_f16x2(accv[j + 4] * wgt, accv[j + 5] * wgt);
             pk.w = bf ? pack_bf16x2(accv[j + 6] * wgt, accv[j + 7] * wgt) : pack_f16x2(accv[j + 6] * wgt, accv[j + 7] * wgt);
-            *reinterpret_cast<uint4*>(op + j * 2) = pk;
+            *reinterpret_cast<uint4*>(slot_ptr + j * 2) = pk;
           }
+          TRACE_T(tile_iter, 2);
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          const long long orow = a.accumulate ? (long long)tok : (long long)tok * a.topk + slot;
+          uint8_t* gp = static_cast<uint8_t*>(a.out) + (orow * a.n_dim + (long long)n * BN + wg * 128) * 2;
+          const uint32_t sp = smem_u32(slot_ptr);
+          if (!a.accumulate) bulk_store_256(gp, sp);
+          else if (bf) bulk_reduce_add_bf16_256(gp, sp);
+          else bulk_reduce_add_f16_256(gp, sp);
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
       }
       TRACE_T(tile_iter, 3);
@@ -669,6 +690,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       ++tile_iter;
     }
     if (threadIdx.x == 128) PROF_WRITE(2);
+    bulk_wait_all();                           // this thread's bulk stores / reductions have landed
   }
 
   tcgen05_fence_before();
@@ -777,12 +799,12 @@ int launch_gemm_sm100(int stage, const GemmArgs& a, cudaStream_t stream) {
   if (grid <= 0) return FLYMOE_OK;
   if (stage == 1) {
     FLYMOE_CUDA_CHECK(cudaFuncSetAttribute(moe_gemm_sm100_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           int(kSmemBytes)));
-    moe_gemm_sm100_kernel<1><<<grid, kNumThreads, kSmemBytes, stream>>>(map_a, map_b, a, group_m);
+                                           int(smem_bytes<1>())));
+    moe_gemm_sm100_kernel<1><<<grid, kNumThreads, smem_bytes<1>(), stream>>>(map_a, map_b, a, group_m);
   } else {
     FLYMOE_CUDA_CHECK(cudaFuncSetAttribute(moe_gemm_sm100_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           int(kSmemBytes)));
-    moe_gemm_sm100_kernel<2><<<grid, kNumThreads, kSmemBytes, stream>>>(map_a, map_b, a, group_m);
+                                           int(smem_bytes<2>())));
+    moe_gemm_sm100_kernel<2><<<grid, kNumThreads, smem_bytes<2>(), stream>>>(map_a, map_b, a, group_m);
   }
   FLYMOE_CUDA_CHECK(cudaGetLastError());
   return FLYMOE_OK;
