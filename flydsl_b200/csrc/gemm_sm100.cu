@@ -37,6 +37,11 @@ namespace flymoe {
 constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 128;
+// Upper bound on the persistent grid (0 = one CTA per SM).  A caller that overlaps the GEMMs with
+// communication kernels leaves those kernels some SMs: a persistent CTA that cannot become resident
+// at launch would otherwise run its whole tile list after the others have finished.
+static int g_cta_limit = 0;
+
 constexpr int kMaxStages = 4;
 // Depth of the shared-memory operand ring.  Stage 2 gives one slot up for a staging area from
 // which finished output rows leave by bulk reduce/store (measured: a 3-deep ring is as fast as 4).
@@ -704,6 +709,15 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 
 }  // namespace flymoe
 
+extern "C" int flymoe_set_gemm_cta_limit(int max_ctas) {
+  if (max_ctas < 0) {
+    flymoe::set_last_error_msg("set_gemm_cta_limit: max_ctas must be >= 0");
+    return FLYMOE_ERR_INVALID_ARGUMENT;
+  }
+  flymoe::g_cta_limit = max_ctas;
+  return FLYMOE_OK;
+}
+
 #ifdef FLYMOE_PROF
 extern "C" int flymoe_prof_read(long long* host_out) {
   FLYMOE_CUDA_CHECK(cudaDeviceSynchronize());
@@ -795,7 +809,9 @@ int launch_gemm_sm100(int stage, const GemmArgs& a, cudaStream_t stream) {
   const int group_m = int(g < 1 ? 1 : (g > 16 ? 16 : g));
   const int ntiles = stage == 1 ? a.n_dim / 128 : ceil_div(a.n_dim, BN);
   const long long max_tiles = (long long)a.size_expert_ids * ntiles;
-  const int grid = int(max_tiles < sm_count() ? max_tiles : sm_count());
+  int ctas = sm_count();
+  if (g_cta_limit > 0 && g_cta_limit < ctas) ctas = g_cta_limit;
+  const int grid = int(max_tiles < ctas ? max_tiles : ctas);
   if (grid <= 0) return FLYMOE_OK;
   if (stage == 1) {
     FLYMOE_CUDA_CHECK(cudaFuncSetAttribute(moe_gemm_sm100_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -3,17 +3,21 @@ evenly over the ranks, tokens dispatched and results combined with NCCL all-to-a
 
 The reference has no dispatch/combine (its only expert-parallel hook is the
 ``expert_mask`` of the sort, kernels/moe_sorting_kernel.py:426-440); this module adds the
-partitioned case on top of the same kernels:
+partitioned case on top of the same kernels.  The rank's tokens are cut into chunks that
+are pipelined, so that the dispatch of chunk c+1 and the combine of chunk c-1 travel over
+NVLink while chunk c is in the GEMMs:
 
   1. gate the rank's own tokens over all E experts               (gating kernel)
-  2. sort the (token, slot) pairs by global expert id, unit 1     (sort kernels) — rows
+  per chunk:
+  2. sort the chunk's (token, slot) pairs by global expert id, unit 1   (sort kernels) — rows
      grouped by expert are also grouped by destination rank, and every rank's block
      arrives pre-grouped by local expert
-  3. exchange per-rank row counts                                 (all_to_all_single, tiny)
+  3. row counts per destination, exchanged for all chunks at once      (one tiny all_to_all,
+     the step's single host synchronisation)
   4. pack e4m3 rows and their fp32 scales in that order           (row-gather kernel)
-  5. dispatch rows, scales and expert ids                          (all_to_all_single x3)
+  5. dispatch rows, scales and expert ids                          (all_to_all_single x3, async)
   6. local experts: sort by local expert, stage 1, stage 2 into per-row bf16 outputs
-  7. combine: send the rows back                                  (all_to_all_single)
+  7. combine: send the rows back                                  (all_to_all_single, async)
   8. out[t] = sum_s w[t,s] * returned_row(t,s)                    (indexed reduce kernel)
 
 Remote data always lands in this GPU's memory before any kernel reads it.  The host-side
@@ -36,6 +40,18 @@ def expert_range(rank: int, world: int, experts: int) -> range:
     return range(rank * per, (rank + 1) * per)
 
 
+def chunk_bounds(tokens: int, chunks: int) -> list:
+    """Token ranges [lo, hi) of the pipeline chunks (the first chunks take the remainder)."""
+    chunks = max(1, min(chunks, max(tokens, 1)))
+    base, rem = divmod(tokens, chunks)
+    out, lo = [], 0
+    for c in range(chunks):
+        hi = lo + base + (1 if c < rem else 0)
+        out.append((lo, hi))
+        lo = hi
+    return out
+
+
 def split_counts(sorted_expert_ids: torch.Tensor, world: int, experts_per_rank: int) -> torch.Tensor:
     """Rows destined to each rank, from the ascending per-row expert ids of the unit-1 sort."""
     bounds = torch.arange(0, world + 1, device=sorted_expert_ids.device,
@@ -45,7 +61,7 @@ def split_counts(sorted_expert_ids: torch.Tensor, world: int, experts_per_rank: 
 
 
 def exchange_counts(send_counts: torch.Tensor, group=None) -> torch.Tensor:
-    """all-to-all of one int64 per peer: recv_counts[r] = rows rank r sends to this rank."""
+    """all-to-all of equal-sized int64 blocks: block r of the result is what rank r sent here."""
     recv = torch.empty_like(send_counts)
     dist.all_to_all_single(recv, send_counts, group=group)
     return recv
@@ -70,7 +86,7 @@ class DispatchPlan:
 class ExpertParallelMoE:
     """Expert-parallel layer.  ``ops`` supplies the device kernels (see ``CudaOps``)."""
 
-    def __init__(self, ops, experts: int, topk: int, model_dim: int, group=None):
+    def __init__(self, ops, experts: int, topk: int, model_dim: int, group=None, chunks: int = 1):
         self.ops = ops
         self.group = group
         self.world = dist.get_world_size(group)
@@ -78,36 +94,75 @@ class ExpertParallelMoE:
         self.experts, self.topk, self.H = experts, topk, model_dim
         self.local = expert_range(self.rank, self.world, experts)
         self.per_rank = len(self.local)
-        self.last_plan: DispatchPlan | None = None
+        self.chunks = max(1, int(chunks))
+        self.last_plans: list = []
 
-    def plan(self, sorted_expert_ids_rows: torch.Tensor, pairs: int) -> DispatchPlan:
-        send = split_counts(sorted_expert_ids_rows, self.world, self.per_rank)
-        recv = exchange_counts(send, self.group)
-        both = torch.stack([send, recv]).cpu()          # the one host synchronisation of a step
-        check_counts(both[0], both[1], pairs)
-        plan = DispatchPlan(both[0].tolist(), both[1].tolist(), int(both[0].sum()), int(both[1].sum()))
-        self.last_plan = plan
-        return plan
+    @property
+    def last_plan(self) -> DispatchPlan:
+        """Whole-step totals over the chunks of the last forward."""
+        ps = self.last_plans
+        send = [sum(p.send_counts[r] for p in ps) for r in range(self.world)]
+        recv = [sum(p.recv_counts[r] for p in ps) for r in range(self.world)]
+        return DispatchPlan(send, recv, sum(send), sum(recv))
+
+    def plan(self, eids_per_chunk: list, pairs_per_chunk: list) -> list:
+        """Per-chunk send/receive row counts; one count exchange and ONE host sync for the step."""
+        n, C = self.world, len(eids_per_chunk)
+        send = torch.stack([split_counts(e, n, self.per_rank) for e in eids_per_chunk])   # [C, n]
+        send_by_rank = send.t().contiguous().view(-1)                                      # [n * C]
+        recv_by_rank = exchange_counts(send_by_rank, self.group)
+        both = torch.stack([send_by_rank, recv_by_rank]).cpu().view(2, n, C)
+        plans = []
+        for c in range(C):
+            s, r = both[0, :, c], both[1, :, c]
+            check_counts(s, r, pairs_per_chunk[c])
+            plans.append(DispatchPlan(s.tolist(), r.tolist(), int(s.sum()), int(r.sum())))
+        self.last_plans = plans
+        return plans
 
     def forward(self, logits, xq, x_scale):
         """logits [T,E]; xq e4m3 [T,H]; x_scale f32 row-major [T,H/128] -> out [T,H]."""
-        ops, k = self.ops, self.topk
+        ops, k, g = self.ops, self.topk, self.group
         T = logits.shape[0]
-        pairs = T * k
+        bounds = chunk_bounds(T, self.chunks)
+        C = len(bounds)
         topk_w, topk_ids = ops.gate(logits)
-        s_ids, s_eids = ops.sort_by_expert(topk_ids, topk_w, T)          # unit 1: one expert id per row
-        plan = self.plan(s_eids[:pairs], pairs)
-        send_x, send_s = ops.pack(xq, x_scale, s_ids, T)
-        recv_x = ops.empty_rows(plan.rows_in, send_x)
-        recv_s = ops.empty_rows(plan.rows_in, send_s)
-        recv_e = ops.empty_rows(plan.rows_in, s_eids)
-        dist.all_to_all_single(recv_x, send_x[:pairs], plan.recv_counts, plan.send_counts, group=self.group)
-        dist.all_to_all_single(recv_s, send_s[:pairs], plan.recv_counts, plan.send_counts, group=self.group)
-        dist.all_to_all_single(recv_e, s_eids[:pairs], plan.recv_counts, plan.send_counts, group=self.group)
-        y = ops.local_experts(recv_x, recv_s, recv_e, self.local.start, plan.rows_in)
-        back = ops.empty_rows(pairs, y)
-        dist.all_to_all_single(back, y[:plan.rows_in], plan.send_counts, plan.recv_counts, group=self.group)
-        return ops.combine(back, s_ids, topk_w, T)
+        sorted_c = []
+        for c, (lo, hi) in enumerate(bounds):
+            sorted_c.append(ops.sort_by_expert(topk_ids[lo:hi], topk_w[lo:hi], hi - lo, c))
+        pairs = [(hi - lo) * k for lo, hi in bounds]
+        plans = self.plan([e[:p] for (_, e), p in zip(sorted_c, pairs)], pairs)
+
+        # dispatch of every chunk is posted up front; NCCL runs them in order on its own stream
+        recv, works = [], []
+        for c, (lo, hi) in enumerate(bounds):
+            s_ids, s_eids = sorted_c[c]
+            p, pl = pairs[c], plans[c]
+            send_x, send_s = ops.pack(xq[lo:hi], x_scale[lo:hi], s_ids, hi - lo, c)
+            rx, rs, re_ = (ops.empty_rows(pl.rows_in, t) for t in (send_x, send_s, s_eids))
+            w = [dist.all_to_all_single(rx, send_x[:p], pl.recv_counts, pl.send_counts, group=g, async_op=True),
+                 dist.all_to_all_single(rs, send_s[:p], pl.recv_counts, pl.send_counts, group=g, async_op=True),
+                 dist.all_to_all_single(re_, s_eids[:p], pl.recv_counts, pl.send_counts, group=g, async_op=True)]
+            recv.append((rx, rs, re_))
+            works.append(w)
+
+        # experts on chunk c while chunk c+1 is still arriving and chunk c-1 is already going back
+        back, back_works = [], []
+        for c in range(C):
+            for w in works[c]:
+                w.wait()
+            rx, rs, re_ = recv[c]
+            y = ops.local_experts(rx, rs, re_, self.local.start, plans[c].rows_in, c)
+            b = ops.empty_rows(pairs[c], y)
+            back_works.append(dist.all_to_all_single(b, y[:plans[c].rows_in], plans[c].send_counts,
+                                                     plans[c].recv_counts, group=g, async_op=True))
+            back.append(b)
+
+        out = None
+        for c, (lo, hi) in enumerate(bounds):
+            back_works[c].wait()
+            out = ops.combine(back[c], sorted_c[c][0], topk_w[lo:hi], lo, hi, T, c)
+        return out
 
     __call__ = forward
 
@@ -116,11 +171,15 @@ class CudaOps:
     """The device side of ``ExpertParallelMoE`` on one B200: the library's own kernels."""
 
     def __init__(self, w1q, w1_scale, w2q, w2_scale, experts: int, topk: int, tokens: int,
-                 tile_m: int = 128, headroom: float = 1.3, impl: str = "tcgen05"):
+                 tile_m: int = 128, headroom: float = 1.3, impl: str = "tcgen05", chunks: int = 1,
+                 comm_sms: int = 0):
         from . import _lib
-        from .layer import FusedMoEBlockscale
         self._lib = _lib
         self.lib = _lib.load()
+        # With a pipelined step the all-to-all kernels run beside the persistent GEMMs: leave them SMs.
+        if comm_sms > 0:
+            sms = torch.cuda.get_device_properties(w1q.device).multi_processor_count
+            _lib.check(self.lib.flymoe_set_gemm_cta_limit(max(1, sms - comm_sms)), "set_gemm_cta_limit")
         self.E, self.k, self.T = experts, topk, tokens
         self.E_local, _, self.H = w1q.shape
         self.I = w2q.shape[2]
@@ -128,25 +187,28 @@ class CudaOps:
         self.w = (w1q, w1_scale, w2q, w2_scale)
         dev = w1q.device
         self.dev = dev
-        P = tokens * topk
         i32, f32 = torch.int32, torch.float32
         self.topk_w = torch.empty((tokens, topk), dtype=f32, device=dev)
         self.topk_ids = torch.empty((tokens, topk), dtype=i32, device=dev)
         self.tei = torch.empty((tokens, topk), dtype=i32, device=dev)
-        cap = P + experts - topk                        # unit-1 sort: no padding rows
-        self.s_ids = torch.empty(cap, dtype=i32, device=dev)
-        self.s_w = torch.empty(cap, dtype=f32, device=dev)
-        self.s_eids = torch.empty(cap, dtype=i32, device=dev)
-        self.nvalid = torch.empty(2, dtype=i32, device=dev)
-        ws = int(self.lib.flymoe_moe_sorting_workspace_elems(tokens, experts, topk, 1))
-        self.ws = torch.empty(max(ws, 1), dtype=i32, device=dev)
-        self.send_x = torch.empty((P, self.H), dtype=torch.uint8, device=dev)
-        self.send_s = torch.empty((P, self.H // 128), dtype=f32, device=dev)
-        self.inverse = torch.empty(P, dtype=i32, device=dev)
         self.out = torch.empty((tokens, self.H), dtype=torch.bfloat16, device=dev)
+        bounds = chunk_bounds(tokens, chunks)
+        tc = max(hi - lo for lo, hi in bounds)            # tokens of the largest chunk
+        pc = tc * topk
+        cap = pc + experts - topk                         # unit-1 sort: no padding rows
+        ws = int(self.lib.flymoe_moe_sorting_workspace_elems(tc, experts, topk, 1))
+        self.ws = torch.empty(max(ws, 1), dtype=i32, device=dev)
+        self.chunk_bufs = []
+        for _ in bounds:                                   # buffers that must outlive their chunk's collectives
+            self.chunk_bufs.append({
+                "s_ids": torch.empty(cap, dtype=i32, device=dev), "s_w": torch.empty(cap, dtype=f32, device=dev),
+                "s_eids": torch.empty(cap, dtype=i32, device=dev), "nvalid": torch.empty(2, dtype=i32, device=dev),
+                "send_x": torch.empty((pc, self.H), dtype=torch.uint8, device=dev),
+                "send_s": torch.empty((pc, self.H // 128), dtype=f32, device=dev),
+                "inverse": torch.empty(pc, dtype=i32, device=dev), "y": None})
         self.headroom = headroom
         self.inner = None
-        self._ensure_inner(int(P * headroom))
+        self._ensure_inner(int(pc * headroom))
 
     def _ensure_inner(self, rows: int) -> None:
         from .layer import FusedMoEBlockscale
@@ -170,42 +232,46 @@ class CudaOps:
                 "topk_gating_softmax")
         return self.topk_w, self.topk_ids
 
-    def sort_by_expert(self, topk_ids, topk_w, T):
-        L = self._lib
-        L.check(self.lib.flymoe_moe_sorting(topk_ids.data_ptr(), topk_w.data_ptr(), self.s_ids.data_ptr(),
-                                            self.s_w.data_ptr(), self.s_eids.data_ptr(), self.nvalid.data_ptr(),
+    def sort_by_expert(self, topk_ids, topk_w, T, chunk: int = 0):
+        L, b = self._lib, self.chunk_bufs[chunk]
+        L.check(self.lib.flymoe_moe_sorting(topk_ids.data_ptr(), topk_w.data_ptr(), b["s_ids"].data_ptr(),
+                                            b["s_w"].data_ptr(), b["s_eids"].data_ptr(), b["nvalid"].data_ptr(),
                                             None, 0, None, self.ws.data_ptr(), self.ws.numel(), T, self.E, self.k, 1,
                                             self._stream()), "moe_sorting")
-        return self.s_ids, self.s_eids
+        return b["s_ids"], b["s_eids"]
 
-    def pack(self, xq, x_scale, s_ids, T):
-        L = self._lib
+    def pack(self, xq, x_scale, s_ids, T, chunk: int = 0):
+        L, b = self._lib, self.chunk_bufs[chunk]
         P = T * self.k
-        L.check(self.lib.flymoe_gather_rows(xq.data_ptr(), self.send_x.data_ptr(), s_ids.data_ptr(),
-                                            self.nvalid.data_ptr(), T, self.k, self.H, L.ROWS_BY_TOKEN, P,
+        L.check(self.lib.flymoe_gather_rows(xq.data_ptr(), b["send_x"].data_ptr(), s_ids.data_ptr(),
+                                            b["nvalid"].data_ptr(), T, self.k, self.H, L.ROWS_BY_TOKEN, P,
                                             self._stream()), "gather_rows")
-        L.check(self.lib.flymoe_gather_rows(x_scale.data_ptr(), self.send_s.data_ptr(), s_ids.data_ptr(),
-                                            self.nvalid.data_ptr(), T, self.k, (self.H // 128) * 4, L.ROWS_BY_TOKEN, P,
+        L.check(self.lib.flymoe_gather_rows(x_scale.data_ptr(), b["send_s"].data_ptr(), s_ids.data_ptr(),
+                                            b["nvalid"].data_ptr(), T, self.k, (self.H // 128) * 4, L.ROWS_BY_TOKEN, P,
                                             self._stream()), "gather_rows")
-        return self.send_x, self.send_s
+        return b["send_x"], b["send_s"]
 
     def empty_rows(self, rows: int, like: torch.Tensor) -> torch.Tensor:
         return torch.empty((rows,) + tuple(like.shape[1:]), dtype=like.dtype, device=like.device)
 
-    def local_experts(self, recv_x, recv_s, recv_e, first_expert: int, rows: int):
+    def local_experts(self, recv_x, recv_s, recv_e, first_expert: int, rows: int, chunk: int = 0):
         self._ensure_inner(rows)
+        b = self.chunk_bufs[chunk]
+        if b["y"] is None or b["y"].shape[0] < max(rows, 1):
+            b["y"] = torch.empty((max(int(rows * self.headroom), 1), self.H), dtype=torch.bfloat16, device=self.dev)
         if rows == 0:
-            return torch.empty((0, self.H), dtype=torch.bfloat16, device=self.dev)
+            return b["y"]
         local_ids = (recv_e - first_expert).view(rows, 1)
         return self.inner.experts_forward(local_ids, self.ones, recv_x, recv_s, rows, self._stream(),
-                                          x_scale_row_major=True)
+                                          out=b["y"], x_scale_row_major=True)
 
-    def combine(self, back, s_ids, topk_w, T):
-        L = self._lib
-        P = T * self.k
-        L.check(self.lib.flymoe_sorted_inverse(s_ids.data_ptr(), self.nvalid.data_ptr(), self.inverse.data_ptr(),
-                                               T, self.k, P, self._stream()), "sorted_inverse")
-        L.check(self.lib.flymoe_moe_reduce(back.data_ptr(), self.out.data_ptr(), None, topk_w.data_ptr(),
-                                           self.inverse.data_ptr(), T, self.k, self.H, L.BF16, self._stream()),
+    def combine(self, back, s_ids, topk_w, lo: int, hi: int, T: int, chunk: int = 0):
+        L, b = self._lib, self.chunk_bufs[chunk]
+        n = hi - lo
+        P = n * self.k
+        L.check(self.lib.flymoe_sorted_inverse(s_ids.data_ptr(), b["nvalid"].data_ptr(), b["inverse"].data_ptr(),
+                                               n, self.k, P, self._stream()), "sorted_inverse")
+        L.check(self.lib.flymoe_moe_reduce(back.data_ptr(), self.out[lo:hi].data_ptr(), None, topk_w.data_ptr(),
+                                           b["inverse"].data_ptr(), n, self.k, self.H, L.BF16, self._stream()),
                 "moe_reduce")
         return self.out

@@ -146,6 +146,12 @@ int flymoe_moe_gemm2(void* out, const void* a2, const float* scale_a, int64_t sa
                      int out_dtype, int accumulate, int a_layout, int a_scale_layout, int impl,
                      void* stream);
 
+/* Caps the persistent grid of the two GEMM stages at max_ctas CTAs (0 restores one CTA per SM).
+ * Process-wide.  For callers that run communication kernels next to the GEMMs (the
+ * expert-parallel layer); the reference has no counterpart (its grid is one CTA per tile,
+ * kernels/moe_blockscale_2stage.py:1165-1183). */
+int flymoe_set_gemm_cta_limit(int max_ctas);
+
 /* Y[t,:] = sum_s w[t,s] * X[row(t,s),:] with fp32 accumulation; row(t,s) = t*k+s, or
  * row_index[t*k+s] when row_index is given (negative entries are skipped); optional u8
  * valid_mask [T,k] and optional f32 weights [T,k] (NULL = 1).

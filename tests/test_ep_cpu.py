@@ -20,33 +20,35 @@ T, E, K, H = 37, 8, 3, 256
 
 class FakeOps:
     def __init__(self):
-        self.nvalid = None
+        self.out = torch.zeros((T, H), dtype=torch.float32)
 
     def gate(self, logits):
         w, idx, _ = orc.topk_gating_softmax(logits, K)
         return w, idx
 
-    def sort_by_expert(self, ids, w, tokens):
+    def sort_by_expert(self, ids, w, tokens, chunk=0):
         s_ids, _, s_e, nv = orc.moe_sorting(ids.numpy(), w.numpy(), E, 1)
         return torch.from_numpy(s_ids), torch.from_numpy(s_e)
 
-    def pack(self, xq, xs, s_ids, tokens):
+    def pack(self, xq, xs, s_ids, tokens, chunk=0):
         tok = (s_ids[: tokens * K] & 0xFFFFFF).long()
         return xq[tok].contiguous(), xs[tok].contiguous()
 
     def empty_rows(self, rows, like):
         return torch.empty((rows,) + tuple(like.shape[1:]), dtype=like.dtype)
 
-    def local_experts(self, rx, rs, re_, first, rows):
+    def local_experts(self, rx, rs, re_, first, rows, chunk=0):
         assert rows == 0 or (int(re_.min()) >= first and int(re_.max()) < first + E // dist.get_world_size())
         return rx.float() * rs.mean(dim=1, keepdim=True) * (re_.view(-1, 1).float() + 1.0)
 
-    def combine(self, back, s_ids, w, tokens):
-        tok = (s_ids[: tokens * K] & 0xFFFFFF).long()
-        slot = (s_ids[: tokens * K] >> 24).long()
-        out = torch.zeros((tokens, back.shape[1]), dtype=torch.float32)
-        out.index_add_(0, tok, back * w[tok, slot].view(-1, 1))
-        return out
+    def combine(self, back, s_ids, w, lo, hi, tokens, chunk=0):
+        n = hi - lo
+        tok = (s_ids[: n * K] & 0xFFFFFF).long()
+        slot = (s_ids[: n * K] >> 24).long()
+        part = torch.zeros((n, back.shape[1]), dtype=torch.float32)
+        part.index_add_(0, tok, back * w[tok, slot].view(-1, 1))
+        self.out[lo:hi] = part
+        return self.out
 
 
 def _inputs(rank):
@@ -57,12 +59,12 @@ def _inputs(rank):
     return logits, xq, xs
 
 
-def _worker(rank, world, port, q):
+def _worker(rank, world, port, chunks, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         logits, xq, xs = _inputs(rank)
-        layer = ep.ExpertParallelMoE(FakeOps(), E, K, H)
+        layer = ep.ExpertParallelMoE(FakeOps(), E, K, H, chunks=chunks)
         out = layer(logits, xq, xs)
         w, idx, _ = orc.topk_gating_softmax(logits, K)
         want = (xq.float() * xs.mean(dim=1, keepdim=True)).unsqueeze(1) * (idx.float() + 1.0).unsqueeze(-1)
@@ -86,12 +88,12 @@ def _free_port():
     return p
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_dispatch_combine_roundtrip_on_cpu_ranks(world):
+@pytest.mark.parametrize("world,chunks", [(2, 1), (2, 3), (4, 2)])
+def test_dispatch_combine_roundtrip_on_cpu_ranks(world, chunks):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, chunks, q)) for r in range(world)]
     for p in procs:
         p.start()
     res = [q.get(timeout=120) for _ in range(world)]
@@ -109,6 +111,8 @@ def test_split_counts_and_checks():
     assert ep.split_counts(eids, 4, 2).tolist() == [3, 3, 1, 2]
     assert ep.split_counts(eids, 8, 1).tolist() == [2, 1, 0, 3, 1, 0, 0, 2]
     assert list(ep.expert_range(3, 4, 256)) == list(range(192, 256))
+    assert ep.chunk_bounds(10, 3) == [(0, 4), (4, 7), (7, 10)] and ep.chunk_bounds(2, 4) == [(0, 1), (1, 2)]
+    assert ep.chunk_bounds(5, 1) == [(0, 5)]
     with pytest.raises(ValueError):
         ep.expert_range(0, 3, 256)
     good = torch.tensor([6, 3])

@@ -23,7 +23,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, routing, q):
+def _worker(rank, world, port, routing, chunks, q):
     import torch.distributed as dist
     from flydsl_b200 import _lib, workloads as wl
     from flydsl_b200.ep import CudaOps, ExpertParallelMoE, expert_range
@@ -43,8 +43,8 @@ def _worker(rank, world, port, routing, q):
         _x, xq_c, xs_c = wl.make_activations(cfg, rank=rank)
         xq, xs = xq_c.to(dev), xs_c.to(dev)
         ops = CudaOps(w1q[sl].contiguous(), w1s[sl].contiguous(), w2q[sl].contiguous(), w2s[sl].contiguous(),
-                      E, k, T, tile_m=128, headroom=1.0)
-        layer = ExpertParallelMoE(ops, E, k, H)
+                      E, k, T, tile_m=128, headroom=1.0, chunks=chunks)
+        layer = ExpertParallelMoE(ops, E, k, H, chunks=chunks)
         out = layer(logits, xq, xs).clone()
         out2 = layer(logits, xq, xs).clone()                                     # buffers are reused
         torch.cuda.synchronize()
@@ -64,14 +64,15 @@ def _worker(rank, world, port, routing, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,routing", [(2, "uniform"), (2, "zipf"), (4, "uniform"), (8, "zipf")])
-def test_expert_parallel_matches_single_gpu(world, routing):
+@pytest.mark.parametrize("world,routing,chunks", [(2, "uniform", 1), (2, "zipf", 3), (4, "uniform", 2),
+                                                  (8, "zipf", 4)])
+def test_expert_parallel_matches_single_gpu(world, routing, chunks):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs, found {torch.cuda.device_count()}")
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, routing, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, routing, chunks, q)) for r in range(world)]
     for p in procs:
         p.start()
     res = [q.get(timeout=300) for _ in range(world)]

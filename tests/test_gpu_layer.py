@@ -149,3 +149,19 @@ def test_quant_act_kernel_matches_reference_quantiser():
         rq, rs = orc.quant_act_1x128(x.float())
         assert torch.equal(q.cpu().view(torch.uint8), rq.view(torch.uint8))
         assert torch.equal(s_t.cpu().t(), rs)
+
+
+def test_host_pipeline_matches_direct_call():
+    from flydsl_b200.host_pipeline import HostPipeline
+    p = Problem(SMALL)
+    layer = make_layer(p, 128)
+    want = layer(p.d_logits, p.d_xq, p.d_xs_t).clone()
+    torch.cuda.synchronize()
+    pipe = HostPipeline(layer, SMALL.tokens, depth=2)
+    h_in = (p.logits.pin_memory(), p.xq.view(torch.uint8).pin_memory(), p.xs.t().contiguous().pin_memory())
+    outs = [torch.empty((SMALL.tokens, SMALL.model_dim), dtype=torch.bfloat16).pin_memory() for _ in range(5)]
+    for o in outs:                      # five batches through a depth-2 pipeline: slots are reused
+        pipe.submit(*h_in, o)
+    pipe.drain()
+    for o in outs:
+        assert_close(o, want, RTOL, ATOL, "host pipeline")
