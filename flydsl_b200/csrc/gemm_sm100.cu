@@ -67,6 +67,9 @@ struct __align__(16) SmemCtrl {
   unsigned long long tmem_full[kAccStages];
   unsigned long long tmem_empty[kAccStages];
   unsigned long long amax_bar[2];
+  unsigned long long stg_full;                  // epilogue warps -> store warp: slots and destinations written
+  unsigned long long stg_free;                  // store warp -> epilogue warps: slots have been read
+  unsigned long long stg_dst[256];              // per epilogue thread: global address of its row segment, 0 = none
   uint32_t tmem_base;
   int abort_flag;
   float amax[2][2][BM];
@@ -263,20 +266,17 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
 constexpr uint32_t kInstrDesc = (1u << 4) | (0u << 7) | (0u << 10) | (uint32_t(BN >> 3) << 17) |
                                 (uint32_t(BM >> 4) << 24);
 
-// 256-byte bulk operations from this thread's staging slot to a contiguous global row segment.
-__device__ __forceinline__ void bulk_reduce_add_bf16_256(void* g, uint32_t s) {
-  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.noftz.bf16 [%0], [%1], 256;" ::"l"(g), "r"(s)
-               : "memory");
+// Bulk operations from a staging slot to a contiguous global row segment (16-byte aligned, size % 16 == 0).
+__device__ __forceinline__ void bulk_reduce_add_bf16(void* g, uint32_t s, uint32_t bytes) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.noftz.bf16 [%0], [%1], %2;"
+               ::"l"(g), "r"(s), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ void bulk_reduce_add_f16_256(void* g, uint32_t s) {
-  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.noftz.f16 [%0], [%1], 256;" ::"l"(g), "r"(s)
-               : "memory");
+__device__ __forceinline__ void bulk_reduce_add_f16(void* g, uint32_t s, uint32_t bytes) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.noftz.f16 [%0], [%1], %2;"
+               ::"l"(g), "r"(s), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ void bulk_store_256(void* g, uint32_t s) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], 256;" ::"l"(g), "r"(s) : "memory");
-}
-__device__ __forceinline__ void bulk_store_64(void* g, uint32_t s) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], 64;" ::"l"(g), "r"(s) : "memory");
+__device__ __forceinline__ void bulk_store(void* g, uint32_t s, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(g), "r"(s), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
@@ -316,6 +316,8 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 #endif
 
   const int valid_rows = min(__ldg(a.num_valid_ids), a.size_expert_ids * a.tile_m);
+  // Outputs that leave through the staging slots (everything except 16-bit stage-1 and fp32 stage-2 output)
+  const bool uses_staging = STAGE == 1 ? a.out_dtype == FLYMOE_E4M3 : a.out_dtype != FLYMOE_F32;
   TileSched sched;
   sched.num_mblocks = (valid_rows + a.tile_m - 1) / a.tile_m;
   sched.num_ntiles = STAGE == 1 ? a.n_dim / 128 : (a.n_dim + BN - 1) / BN;
@@ -333,6 +335,8 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     }
     mbar_init(smem_u32(&ctrl->amax_bar[0]), kEpilogueWarps);
     mbar_init(smem_u32(&ctrl->amax_bar[1]), kEpilogueWarps);
+    mbar_init(smem_u32(&ctrl->stg_full), kEpilogueWarps);
+    mbar_init(smem_u32(&ctrl->stg_free), 1);
     ctrl->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -463,6 +467,47 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         }
       }
       PROF_WRITE(1);
+    } else if (warp == 2 && uses_staging) {
+      // ---------------------------------------------------------------- store warp
+      // Issues the bulk store / bulk reduce of every epilogue thread's staging slot, eight slots per
+      // lane, so that the ~10 cycles each of those 256 operations takes to be accepted are spent here
+      // and not by the epilogue warps between two tiles.
+      bool ok = true;
+      uint32_t it = 0;
+      int mb_next = 0, n_next = 0, e_next = -1;
+      if (int(blockIdx.x) < sched.total) {
+        sched.decode(blockIdx.x, mb_next, n_next);
+        e_next = __ldg(a.sorted_expert_ids + mb_next);
+      }
+      constexpr uint32_t kSlotBytes = STAGE == 1 ? 64u : 256u;
+      const bool bf = a.out_dtype == FLYMOE_BF16;
+      for (int t = blockIdx.x; t < sched.total && ok; t += gridDim.x) {
+        const int e = e_next;
+        if (t + int(gridDim.x) < sched.total) {
+          sched.decode(t + gridDim.x, mb_next, n_next);
+          e_next = __ldg(a.sorted_expert_ids + mb_next);
+        }
+        if (e < 0 || e >= a.experts) continue;
+        if (!mbar_wait(smem_u32(&ctrl->stg_full), it & 1, abort_flag, a.status, 6, 64)) { ok = false; break; }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int sl = i * 32 + lane;
+          const unsigned long long dst = ctrl->stg_dst[sl];
+          if (dst != 0ull) {
+            const uint32_t sp = smem_u32(staging + size_t(sl) * Staging<STAGE>::stride);
+            void* gp = reinterpret_cast<void*>(dst);
+            if (STAGE == 1 || !a.accumulate) bulk_store(gp, sp, kSlotBytes);
+            else if (bf) bulk_reduce_add_bf16(gp, sp, kSlotBytes);
+            else bulk_reduce_add_f16(gp, sp, kSlotBytes);
+          }
+        }
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        bulk_wait_read_all();                      // the slots may be overwritten from here on
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&ctrl->stg_free));
+        ++it;
+      }
+      bulk_wait_all();                             // every row segment has landed before the CTA retires
     }
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
@@ -615,6 +660,9 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           if (lane == 0) mbar_arrive(bar);
           if (!mbar_wait(bar, (tile_iter >> 1) & 1, abort_flag, a.status, 5)) { ok = false; break; }
           TRACE_T(tile_iter, 2);
+          // the store warp has finished reading the previous tile's slots
+          if (!mbar_wait(smem_u32(&ctrl->stg_free), (tile_iter & 1) ^ 1, abort_flag, a.status, 7)) { ok = false; break; }
+          unsigned long long dst_addr = 0ull;
           const bool wr = warp_active && (valid || (in_tile && a.out_layout == FLYMOE_ROWS_SORTED));
           if (wr) {
             const float m = fmaxf(ctrl->amax[buf][0][row_in_tile], ctrl->amax[buf][1][row_in_tile]);
@@ -623,7 +671,6 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             const float inv = valid ? __fdiv_rn(1.0f, sc) : 0.f;     // pad rows: every code becomes 0
             // 64 codes go through this thread's staging slot and leave as one 64-byte bulk store
             uint8_t* op = staging + size_t(threadIdx.x - 128) * Staging<STAGE>::stride;
-            bulk_wait_read_all();
 #pragma unroll
             for (int j = 0; j < 64; j += 16) {
               uint4 pk;
@@ -635,10 +682,12 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
               *reinterpret_cast<uint4*>(op + j) = pk;
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            bulk_store_64(static_cast<uint8_t*>(a.out) + orow * a.n_dim + ocol, smem_u32(op));
-            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            dst_addr = reinterpret_cast<unsigned long long>(static_cast<uint8_t*>(a.out) + orow * a.n_dim + ocol);
             if (wg == 0) a.out_scale[(long long)n * a.out_scale_stride + orow] = sc;
           }
+          ctrl->stg_dst[threadIdx.x - 128] = dst_addr;
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&ctrl->stg_full));
         } else if (warp_active && valid) {
           uint8_t* op = static_cast<uint8_t*>(a.out) + (orow * a.n_dim + ocol) * 2;
           const bool bf = a.out_dtype == FLYMOE_BF16;
@@ -662,11 +711,11 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         }
       } else {
         // 16-bit output: each thread parks its 128 results (256 B) in its own slot of the staging area
-        // and sends them off as ONE bulk reduce-add (or bulk store) of a contiguous row segment, instead
-        // of 16 scattered 16-byte atomics per thread.  The slot is private to the thread, so the only
-        // ordering needed is against the thread's own previous bulk operation.
+        // together with the global address of its row segment; the store warp sends every slot off as
+        // ONE bulk reduce-add (or bulk store), instead of 16 scattered 16-byte atomics per thread.
         uint8_t* slot_ptr = staging + size_t(threadIdx.x - 128) * Staging<STAGE>::stride;
-        bulk_wait_read_all();
+        if (!mbar_wait(smem_u32(&ctrl->stg_free), (tile_iter & 1) ^ 1, abort_flag, a.status, 7)) { ok = false; break; }
+        unsigned long long dst_addr = 0ull;
         TRACE_T(tile_iter, 1);
         if (warp_active && valid && half_ok) {
           const bool bf = a.out_dtype == FLYMOE_BF16;
@@ -682,20 +731,18 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           TRACE_T(tile_iter, 2);
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           const long long orow = a.accumulate ? (long long)tok : (long long)tok * a.topk + slot;
-          uint8_t* gp = static_cast<uint8_t*>(a.out) + (orow * a.n_dim + (long long)n * BN + wg * 128) * 2;
-          const uint32_t sp = smem_u32(slot_ptr);
-          if (!a.accumulate) bulk_store_256(gp, sp);
-          else if (bf) bulk_reduce_add_bf16_256(gp, sp);
-          else bulk_reduce_add_f16_256(gp, sp);
-          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          dst_addr = reinterpret_cast<unsigned long long>(static_cast<uint8_t*>(a.out) +
+                                                          (orow * a.n_dim + (long long)n * BN + wg * 128) * 2);
         }
+        ctrl->stg_dst[threadIdx.x - 128] = dst_addr;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&ctrl->stg_full));
       }
       TRACE_T(tile_iter, 3);
       PROF_STOP(1) PROF_COUNT(4)
       ++tile_iter;
     }
     if (threadIdx.x == 128) PROF_WRITE(2);
-    bulk_wait_all();                           // this thread's bulk stores / reductions have landed
   }
 
   tcgen05_fence_before();

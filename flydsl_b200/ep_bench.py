@@ -25,6 +25,8 @@ def run_expert_parallel(args, cfg: wl.MoEConfig):
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "29531")
+    if int(getattr(args, "nccl_max_ctas", 0)) > 0:          # bound the SMs NCCL's kernels may occupy
+        os.environ["NCCL_MAX_CTAS"] = str(int(args.nccl_max_ctas))
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
