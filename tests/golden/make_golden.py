@@ -1,9 +1,9 @@
 """Generate the golden fixtures in this directory from the reference project's own code.
 
-Run once, in a container that has the reference checkout (default
-``/root/reference``, override with ``FLYMOE_REFERENCE_DIR``):
+Run once, in a container that has the reference checkout; its location is given by the
+``FLYMOE_REFERENCE_DIR`` environment variable:
 
-    python tests/golden/make_golden.py
+    FLYMOE_REFERENCE_DIR=<path to the FlyDSL checkout> python tests/golden/make_golden.py
 
 The reference's torch oracles live in test files that import the (AMD-only)
 compiler at module level, so they cannot be imported; this script lifts the pure-torch
@@ -38,7 +38,7 @@ import torch.nn.functional as F
 
 HERE = Path(__file__).resolve().parent
 REPO = HERE.parent.parent
-REF = Path(os.environ.get("FLYMOE_REFERENCE_DIR", "/root/reference"))
+REF = Path(os.environ["FLYMOE_REFERENCE_DIR"]) if "FLYMOE_REFERENCE_DIR" in os.environ else None
 sys.path.insert(0, str(REPO))
 
 from flydsl_b200 import workloads as wl  # noqa: E402
@@ -81,6 +81,8 @@ def sha(*arrays) -> str:
 
 
 def main() -> None:
+    if REF is None or not REF.exists():
+        raise SystemExit("set FLYMOE_REFERENCE_DIR to the reference checkout")
     utils = import_file(REF / "tests" / "utils.py", "ref_tests_utils")
     bs = lift(REF / "tests" / "kernels" / "test_moe_blockscale.py",
               ["_expand_blockscale", "torch_stage1_blockscale_ref", "torch_stage2_blockscale_ref",

@@ -165,3 +165,31 @@ def test_host_pipeline_matches_direct_call():
     pipe.drain()
     for o in outs:
         assert_close(o, want, RTOL, ATOL, "host pipeline")
+
+
+@pytest.mark.parametrize("tokens,tile_m", [(1, 16), (1, 128), (3, 32), (130, 64)])
+def test_layer_few_tokens(tokens, tile_m):
+    cfg = wl.MoEConfig("few", tokens, 512, 256, 8, 2, 33)
+    p = Problem(cfg)
+    out = make_layer(p, tile_m)(p.d_logits, p.d_xq, p.d_xs_t)
+    torch.cuda.synchronize()
+    ref = orc.moe_layer(p.logits, p.xq, p.xs, p.w1q, p.w1s, p.w2q, p.w2s, cfg.topk)
+    assert_close(out[:tokens], ref["out"], RTOL, ATOL, f"layer T={tokens}")
+
+
+def test_layer_all_tokens_on_two_experts():
+    """Maximal collision: every token routed to the same two experts (many row blocks for them,
+    none for the others), and per-token order inside an expert must stay ascending."""
+    cfg = wl.MoEConfig("collide", 700, 512, 256, 8, 2, 44)
+    p = Problem(cfg)
+    logits = p.logits.clone()
+    logits[:, 5] += 50.0
+    logits[:, 2] += 40.0
+    layer = make_layer(p, 128)
+    out = layer(logits.cuda(), p.d_xq, p.d_xs_t)
+    torch.cuda.synchronize()
+    ref = orc.moe_layer(logits, p.xq, p.xs, p.w1q, p.w1s, p.w2q, p.w2s, cfg.topk)
+    assert torch.equal(layer.topk_ids[:700].cpu(), ref["topk_ids"])
+    assert set(ref["topk_ids"].unique().tolist()) == {2, 5}
+    assert int(layer.num_valid_ids[0]) == 2 * 768          # 700 rows per expert padded to 6 blocks of 128
+    assert_close(out[:700], ref["out"], RTOL, ATOL + 2.0 ** -7 * float(ref["out"].float().abs().max()), "collision layer")
