@@ -17,7 +17,7 @@ namespace flymoe {
 constexpr int kSortThreads = 256;
 constexpr int kSortWarps = kSortThreads / 32;
 constexpr int kOneBlockMaxPairs = 8192;
-constexpr int kSegPairs = 512;       // pairs per warp segment on the multi-block path
+constexpr int kSegPairs = 128;       // pairs per warp segment on the multi-block path
 constexpr int kMaxExperts = 1024;
 
 struct SortArgs {
@@ -121,7 +121,7 @@ __device__ void block_layout(const SortArgs& a, const int* tot, int* base, int* 
   int row = r_inc - rows + (warp > 0 ? scratch[warp - 1] : 0);
   int dis = d_inc - disabled + (warp > 0 ? scratch[32 + warp - 1] : 0);
   const int total_rows = scratch[nwarp - 1];
-  const int sentinel = (a.topk << 24) | a.num_tokens;
+  const int sentinel = (a.topk << 24) | a.num_tokens;   // used by the pad fill below
   for (int e = e0; e < e1; ++e) {
     const bool off = (a.expert_mask != nullptr && __ldg(a.expert_mask + e) == 0);
     base[e] = row;
@@ -129,16 +129,21 @@ __device__ void block_layout(const SortArgs& a, const int* tot, int* base, int* 
     const int b0 = row / U;
     for (int b = 0; b < nb; ++b)
       if (b0 + b < a.expert_ids_capacity) a.sorted_expert_ids[b0 + b] = e - dis;
-    for (int i = tot[e]; i < nb * U; ++i) {   // pad rows of this expert
-      a.sorted_ids[row + i] = sentinel;
-      a.sorted_weights[row + i] = 0.f;
-    }
     row += nb * U;
     dis += off ? 1 : 0;
   }
   for (int b = total_rows / U + tid; b < a.expert_ids_capacity; b += nthr) a.sorted_expert_ids[b] = -1;
   if (tid == 0) { a.num_valid_ids[0] = total_rows; a.num_valid_ids[1] = a.num_tokens; }
   __syncthreads();
+  // pad rows (sentinel id, weight 0) of every expert: one warp per expert, lanes across the pad range
+  for (int e = warp; e < E; e += nwarp) {
+    const int first = base[e] + tot[e];
+    const int last = base[e] + ((tot[e] + U - 1) / U) * U;
+    for (int i = first + lane; i < last; i += 32) {
+      a.sorted_ids[i] = sentinel;
+      a.sorted_weights[i] = 0.f;
+    }
+  }
 }
 
 __global__ void __launch_bounds__(kSortThreads) moe_sort_oneblock_kernel(SortArgs a) {
@@ -185,24 +190,42 @@ __global__ void __launch_bounds__(kSortThreads) moe_sort_count_kernel(SortArgs a
   }
 }
 
-// Step 2 (one block): exclusive prefix over segments per expert, then the expert layout.
+// Step 2 (one block of 1024 threads): exclusive prefix over segments per expert, then the expert
+// layout.  The segment axis is cut into `parts` contiguous ranges handled by different threads of
+// the same expert (parts * E <= 1024), so the serial walk per thread is nseg / parts long.
 __global__ void __launch_bounds__(1024) moe_sort_scan_kernel(SortArgs a) {
   __shared__ int tot[kMaxExperts];
   __shared__ int base[kMaxExperts];
   __shared__ int scratch[64];
+  __shared__ int part_sum[1024];
   const int E = a.num_experts;
-  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+  int parts = 1;
+  while (parts * 2 * E <= 1024 && parts * 2 <= a.nseg) parts *= 2;
+  const int per_part = (a.nseg + parts - 1) / parts;
+  const int e = threadIdx.x % E, part = threadIdx.x / E;
+  const bool active = part < parts && threadIdx.x < parts * E;
+  const int s0 = min(part * per_part, a.nseg), s1 = min(s0 + per_part, a.nseg);
+  int sum = 0;
+  if (active) {
+#pragma unroll 8
+    for (int s = s0; s < s1; ++s) sum += a.ws_counts[size_t(s) * E + e];
+    part_sum[part * E + e] = sum;
+  }
+  __syncthreads();
+  if (active) {
     int run = 0;
-    for (int s = 0; s < a.nseg; ++s) {
+    for (int q = 0; q < part; ++q) run += part_sum[q * E + e];
+    if (part == parts - 1) tot[e] = run + sum;
+#pragma unroll 4
+    for (int s = s0; s < s1; ++s) {
       const int c = a.ws_counts[size_t(s) * E + e];
       a.ws_counts[size_t(s) * E + e] = run;
       run += c;
     }
-    tot[e] = run;
   }
   __syncthreads();
   block_layout(a, tot, base, scratch);
-  for (int e = threadIdx.x; e < E; e += blockDim.x) a.ws_base[e] = base[e];
+  for (int x = threadIdx.x; x < E; x += blockDim.x) a.ws_base[x] = base[x];
 }
 
 // Step 3: scatter.

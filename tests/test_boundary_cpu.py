@@ -28,7 +28,7 @@ def test_library_exports_every_declared_symbol(lib):
 def test_workspace_size_is_host_only(lib):
     assert lib.flymoe_moe_sorting_workspace_elems(64, 256, 8, 32) == 0
     need = lib.flymoe_moe_sorting_workspace_elems(4096, 256, 8, 128)
-    assert need == (4096 * 8 // 512) * 256 + 256
+    assert need == (4096 * 8 // 128) * 256 + 256
     assert srt.moe_sorting_get_workspace_size(4096, 256, 8, 128) >= need
     assert srt.moe_sorting_get_workspace_size(16, 256, 8) == 0
 
