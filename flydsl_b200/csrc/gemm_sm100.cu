@@ -580,15 +580,20 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       uint32_t v0[32], v1[32];
       for (int kb = 0; kb < KB; ++kb, ++tslot) {
         TRACE_E(tslot, 0);
-        const unsigned long long c0 = pack_f32x2(sa_next * s0_next);
-        const unsigned long long c1 = STAGE == 1 ? pack_f32x2(sa_next * s1_next) : c0;
         const uint32_t stage_off = uint32_t(acc) * BN;
         PROF_START
         if (!mbar_wait(full_bar0 + uint32_t(acc) * 8u, acc_phase, abort_flag, a.status, 4)) { ok = false; break; }
         PROF_STOP(0) PROF_COUNT(5)
         tcgen05_fence_after();
         TRACE_E(tslot, 1);
-        if (work) tmem_ld_x32(tcol0 + stage_off, v0);
+        if (work) tmem_ld_x32(tcol0 + stage_off, v0);       // first chunk on its way before anything else
+        const unsigned long long c0 = pack_f32x2(sa_next * s0_next);
+        const unsigned long long c1 = STAGE == 1 ? pack_f32x2(sa_next * s1_next) : c0;
+        if (work) {
+          tmem_ld_wait();
+          TRACE_E(tslot, 2);
+          tmem_ld_x32(tcol0 + stage_off + 32, v1);
+        }
         if (kb + 1 < KB) {                     // next K block's scales: in flight during this block's math
           sa_run += a.sa_stride;
           sa_next = valid ? __ldg(sa_run) : 0.f;
@@ -596,9 +601,6 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           if (STAGE == 1) s1_next = __ldg(sw0_ptr + kb + 1 + sw1_off);
         }
         if (work) {
-          tmem_ld_wait();
-          TRACE_E(tslot, 2);
-          tmem_ld_x32(tcol0 + stage_off + 32, v1);
 #pragma unroll
           for (int j = 0; j < 16; ++j) ffma2(acc2[j], v0[2 * j], v0[2 * j + 1], c0);
           tmem_ld_wait();
