@@ -151,15 +151,6 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "=r"(done) : "r"(bar), "r"(parity) : "memory");
   return done;
 }
-__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-  return done;
-}
 __device__ __forceinline__ unsigned long long global_timer_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -410,7 +401,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       // ---------------------------------------------------------------- MMA issuer
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
-      bool ok = true, primed = false;
+      bool ok = true;
       int tslot = 0;
       PROF_DECL
       int mb_next = 0, n_next = 0, e_next = -1;
@@ -425,16 +416,13 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           e_next = __ldg(a.sorted_expert_ids + mb_next);
         }
         if (e < 0 || e >= a.experts) continue;
-        const bool next_tile_ok = (t + int(gridDim.x) < sched.total) && e_next >= 0 && e_next < a.experts;
         for (int kb = 0; kb < KB; ++kb, ++tslot) {
           TRACE(1, tslot, 0);
-          if (!primed) {
-            PROF_START
-            if (!mbar_wait(smem_u32(&ctrl->tmem_empty[acc]), acc_phase ^ 1, abort_flag, a.status, 2)) { ok = false; break; }
-            PROF_STOP(0) PROF_START
-            if (!mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag, a.status, 3)) { ok = false; break; }
-            PROF_STOP(1)
-          } else { PROF_COUNT(2) }
+          PROF_START
+          if (!mbar_wait(smem_u32(&ctrl->tmem_empty[acc]), acc_phase ^ 1, abort_flag, a.status, 2)) { ok = false; break; }
+          PROF_STOP(0) PROF_START
+          if (!mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag, a.status, 3)) { ok = false; break; }
+          PROF_STOP(1)
           PROF_COUNT(5) PROF_START
           TRACE(1, tslot, 2);
           tcgen05_fence_after();
@@ -443,27 +431,14 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           const uint64_t bdesc = make_smem_desc(sa + kATileBytes);
           const uint32_t d_tmem = tmem_base + uint32_t(acc) * BN;
 #pragma unroll
-          for (int k = 0; k < BK / 32 - 1; ++k)
+          for (int k = 0; k < BK / 32; ++k)
             umma_f8(d_tmem, adesc + uint64_t(k * 2), bdesc + uint64_t(k * 2), kInstrDesc, k > 0 ? 1u : 0u);
-          // While the tensor pipe works on this K block, look whether the next one's operands and
-          // accumulator stage are ready, so that its first MMA can follow this block's last at once.
-          const int nstage = stage + 1 == kStages ? 0 : stage + 1;
-          const uint32_t nphase = stage + 1 == kStages ? phase ^ 1 : phase;
-          const int nacc = acc + 1 == kAccStages ? 0 : acc + 1;
-          const uint32_t nacc_phase = acc + 1 == kAccStages ? acc_phase ^ 1 : acc_phase;
-          // Non-blocking: if either is not ready yet, the blocking wait happens at the top of the
-          // next iteration, after this block has been committed (never hold back a commit).
-          primed = (kb + 1 < KB || next_tile_ok) &&
-                   mbar_test_wait(smem_u32(&ctrl->tmem_empty[nacc]), nacc_phase ^ 1) &&
-                   mbar_test_wait(smem_u32(&ctrl->full[nstage]), nphase);
-          umma_f8(d_tmem, adesc + uint64_t((BK / 32 - 1) * 2), bdesc + uint64_t((BK / 32 - 1) * 2), kInstrDesc, 1u);
           umma_commit(smem_u32(&ctrl->empty[stage]));
           umma_commit(smem_u32(&ctrl->tmem_full[acc]));
           PROF_STOP(3)
           TRACE(1, tslot, 3);
-
-          stage = nstage; phase = nphase;
-          acc = nacc; acc_phase = nacc_phase;
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+          if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
         }
       }
       PROF_WRITE(1);
