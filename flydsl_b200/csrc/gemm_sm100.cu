@@ -550,8 +550,8 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       // stage 1: first half = gate columns, second half = up columns; stage 2: two halves of 128 columns
       const uint32_t tcol0 = tmem_base + lane_base + (STAGE == 1 ? uint32_t(wg * 64) : uint32_t(wg * 128));
       const uint32_t tcol1 = tmem_base + lane_base + (STAGE == 1 ? uint32_t(128 + wg * 64) : uint32_t(wg * 128 + 64));
-      // One K block = four 32-column chunks through two register buffers: each tcgen05.ld is in
-      // flight while the previous chunk is folded into the accumulators.
+      // One K block = four 32-column chunks through two register buffers, two tcgen05.ld in flight at
+      // a time: the thread waits twice per K block, not once per chunk.
       uint32_t v0[32], v1[32];
       for (int kb = 0; kb < KB; ++kb, ++tslot) {
         TRACE_E(tslot, 0);
@@ -561,14 +561,14 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         PROF_STOP(0) PROF_COUNT(5)
         tcgen05_fence_after();
         TRACE_E(tslot, 1);
-        if (work) tmem_ld_x32(tcol0 + stage_off, v0);       // first chunk on its way before anything else
-        const unsigned long long c0 = pack_f32x2(sa_next * s0_next);
-        const unsigned long long c1 = STAGE == 1 ? pack_f32x2(sa_next * s1_next) : c0;
-        if (work) {
-          tmem_ld_wait();
-          TRACE_E(tslot, 2);
+        if (work) {                            // both chunks of the first half on their way at once
+          tmem_ld_x32(tcol0 + stage_off, v0);
           tmem_ld_x32(tcol0 + stage_off + 32, v1);
         }
+        const unsigned long long c0 = pack_f32x2(sa_next * s0_next);
+        const unsigned long long c1 = STAGE == 1 ? pack_f32x2(sa_next * s1_next) : c0;
+        if (work) tmem_ld_wait();
+        TRACE_E(tslot, 2);
         if (kb + 1 < KB) {                     // next K block's scales: in flight during this block's math
           sa_run += a.sa_stride;
           sa_next = valid ? __ldg(sa_run) : 0.f;
@@ -576,18 +576,13 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           if (STAGE == 1) s1_next = __ldg(sw0_ptr + kb + 1 + sw1_off);
         }
         if (work) {
+          // each buffer is refilled with its chunk of the second half as soon as it has been folded in
 #pragma unroll
           for (int j = 0; j < 16; ++j) ffma2(acc2[j], v0[2 * j], v0[2 * j + 1], c0);
-          tmem_ld_wait();
-          TRACE_E(tslot, 3);
           tmem_ld_x32(tcol1 + stage_off, v0);
 #pragma unroll
           for (int j = 0; j < 16; ++j) ffma2(acc2[16 + j], v1[2 * j], v1[2 * j + 1], c0);
-          tmem_ld_wait();
-          TRACE_E(tslot, 4);
           tmem_ld_x32(tcol1 + stage_off + 32, v1);
-#pragma unroll
-          for (int j = 0; j < 16; ++j) ffma2(acc2[32 + j], v0[2 * j], v0[2 * j + 1], c1);
           tmem_ld_wait();
           TRACE_E(tslot, 5);
         }
@@ -599,6 +594,8 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         if (lane == 0) mbar_arrive_relaxed(empty_bar0 + uint32_t(acc) * 8u);
         TRACE_E(tslot, 6);
         if (work) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) ffma2(acc2[32 + j], v0[2 * j], v0[2 * j + 1], c1);
 #pragma unroll
           for (int j = 0; j < 16; ++j) ffma2(acc2[48 + j], v1[2 * j], v1[2 * j + 1], c1);
         }
