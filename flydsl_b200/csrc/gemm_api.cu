@@ -83,13 +83,13 @@ extern "C" int flymoe_moe_gemm1(void* out, float* out_scale, int64_t out_scale_s
   return FLYMOE_ERR_INVALID_ARGUMENT;
 }
 
-extern "C" int flymoe_moe_gemm2(void* out, const void* a2, const float* scale_a, int64_t sa_stride,
-                                const void* w, const float* scale_w, const int32_t* sorted_ids,
-                                const int32_t* sorted_expert_ids, const float* sorted_weights,
-                                const int32_t* num_valid_ids, int num_tokens, int model_dim,
-                                int inter_dim, int size_expert_ids, int experts, int topk, int tile_m,
-                                int doweight, int out_dtype, int accumulate, int a_layout,
-                                int a_scale_layout, int impl, void* stream) {
+static int gemm2_impl(void* out, const unsigned long long* row_dst, const void* a2, const float* scale_a,
+                      int64_t sa_stride, const void* w, const float* scale_w, const int32_t* sorted_ids,
+                      const int32_t* sorted_expert_ids, const float* sorted_weights,
+                      const int32_t* num_valid_ids, int num_tokens, int model_dim,
+                      int inter_dim, int size_expert_ids, int experts, int topk, int tile_m,
+                      int doweight, int out_dtype, int accumulate, int a_layout,
+                      int a_scale_layout, int impl, void* stream) {
   FLYMOE_REQUIRE(num_tokens >= 0 && num_tokens < (1 << 24), "gemm2: num_tokens out of range");
   FLYMOE_REQUIRE(inter_dim > 0 && inter_dim % 128 == 0, "gemm2: inter_dim must be a positive multiple of 128");
   FLYMOE_REQUIRE(model_dim > 0 && model_dim % 128 == 0, "gemm2: model_dim must be a positive multiple of 128");
@@ -101,8 +101,10 @@ extern "C" int flymoe_moe_gemm2(void* out, const void* a2, const float* scale_a,
                      (a_scale_layout == FLYMOE_ROWS_BY_PAIR || a_scale_layout == FLYMOE_ROWS_SORTED),
                  "gemm2: a_layout/a_scale_layout must be BY_PAIR or SORTED");
   if (num_tokens == 0 || size_expert_ids == 0) return FLYMOE_OK;
-  FLYMOE_REQUIRE(out && a2 && scale_a && w && scale_w && sorted_ids && sorted_expert_ids && num_valid_ids,
+  FLYMOE_REQUIRE((out || row_dst) && a2 && scale_a && w && scale_w && sorted_ids && sorted_expert_ids && num_valid_ids,
                  "gemm2: null pointer");
+  FLYMOE_REQUIRE(!row_dst || (!accumulate && out_dtype != FLYMOE_F32 && impl == FLYMOE_IMPL_TCGEN05),
+                 "gemm2: per-row destinations need accumulate == 0, a 16-bit out_dtype and the tcgen05 kernel");
   FLYMOE_REQUIRE(!doweight || sorted_weights, "gemm2: doweight needs sorted_weights");
   FLYMOE_REQUIRE(aligned16(out) && aligned16(a2) && aligned16(w), "gemm2: out/a2/w must be 16-byte aligned");
   int* status = device_status_ptr();
@@ -128,6 +130,7 @@ extern "C" int flymoe_moe_gemm2(void* out, const void* a2, const float* scale_a,
   a.out_dtype = out_dtype;
   a.out_layout = FLYMOE_ROWS_BY_PAIR;
   a.accumulate = accumulate ? 1 : 0;
+  a.row_dst = row_dst;
   a.doweight = doweight;
   a.num_tokens = num_tokens;
   a.topk = topk;
@@ -142,4 +145,30 @@ extern "C" int flymoe_moe_gemm2(void* out, const void* a2, const float* scale_a,
   if (impl == FLYMOE_IMPL_TCGEN05) return launch_gemm_sm100(2, a, s);
   set_last_error_msg("gemm2: unknown impl");
   return FLYMOE_ERR_INVALID_ARGUMENT;
+}
+
+extern "C" int flymoe_moe_gemm2(void* out, const void* a2, const float* scale_a, int64_t sa_stride,
+                                const void* w, const float* scale_w, const int32_t* sorted_ids,
+                                const int32_t* sorted_expert_ids, const float* sorted_weights,
+                                const int32_t* num_valid_ids, int num_tokens, int model_dim,
+                                int inter_dim, int size_expert_ids, int experts, int topk, int tile_m,
+                                int doweight, int out_dtype, int accumulate, int a_layout,
+                                int a_scale_layout, int impl, void* stream) {
+  return gemm2_impl(out, nullptr, a2, scale_a, sa_stride, w, scale_w, sorted_ids, sorted_expert_ids, sorted_weights,
+                    num_valid_ids, num_tokens, model_dim, inter_dim, size_expert_ids, experts, topk, tile_m, doweight,
+                    out_dtype, accumulate, a_layout, a_scale_layout, impl, stream);
+}
+
+extern "C" int flymoe_moe_gemm2_scatter_rows(const uint64_t* row_dst, const void* a2, const float* scale_a,
+                                             int64_t sa_stride, const void* w, const float* scale_w,
+                                             const int32_t* sorted_ids, const int32_t* sorted_expert_ids,
+                                             const float* sorted_weights, const int32_t* num_valid_ids,
+                                             int num_tokens, int model_dim, int inter_dim, int size_expert_ids,
+                                             int experts, int topk, int tile_m, int doweight, int out_dtype,
+                                             int a_layout, int a_scale_layout, void* stream) {
+  FLYMOE_REQUIRE(row_dst != nullptr, "gemm2_scatter_rows: row_dst is null");
+  return gemm2_impl(nullptr, reinterpret_cast<const unsigned long long*>(row_dst), a2, scale_a, sa_stride, w, scale_w,
+                    sorted_ids, sorted_expert_ids, sorted_weights, num_valid_ids, num_tokens, model_dim, inter_dim,
+                    size_expert_ids, experts, topk, tile_m, doweight, out_dtype, 0, a_layout, a_scale_layout,
+                    FLYMOE_IMPL_TCGEN05, stream);
 }

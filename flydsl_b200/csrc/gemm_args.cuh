@@ -29,6 +29,8 @@ struct GemmArgs {
   int out_dtype;               // FLYMOE_F16 / BF16 / F32 / E4M3
   int out_layout;              // stage 1: BY_PAIR or SORTED
   int accumulate;              // stage 2: atomic add into [T, n_dim] vs store into [T*k, n_dim]
+  const unsigned long long* row_dst;   // stage 2, accumulate == 0, optional: byte address of output row t*k+s
+                                       // (0 = drop the row); may point into a peer GPU's memory
   int doweight;
   // sizes
   int num_tokens, topk, experts;

@@ -287,7 +287,9 @@ struct TileSched {
   }
 };
 
-template <int STAGE>
+// ROW_DST (stage 2 only): every output row goes to a caller-given address instead of out[t*k+s].  A
+// separate instantiation, so that the common kernel's register allocation is not touched.
+template <int STAGE, bool ROW_DST = false>
 __global__ void __launch_bounds__(kNumThreads, 1)
 moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const GemmArgs a, const int group_m) {
@@ -604,6 +606,11 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         acc ^= 1;
       }
       if (!ok) break;
+      // Destination of this row when the caller gave per-row addresses: requested after the K loop (the
+      // loop runs at the register limit) and needed only once the row has been packed.
+      unsigned long long row_dst_base = 0ull;
+      if (STAGE == 2 && ROW_DST && valid)
+        row_dst_base = __ldg(a.row_dst + ((long long)tok * a.topk + slot));
       float accv[NACC];
 #pragma unroll
       for (int j = 0; j < NACC / 2; ++j) unpack_f32x2(acc2[j], accv[2 * j], accv[2 * j + 1]);
@@ -705,8 +712,15 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           TRACE_T(tile_iter, 2);
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           const long long orow = a.accumulate ? (long long)tok : (long long)tok * a.topk + slot;
-          dst_addr = reinterpret_cast<unsigned long long>(static_cast<uint8_t*>(a.out) +
-                                                          (orow * a.n_dim + (long long)n * BN + wg * 128) * 2);
+          const long long col_bytes = ((long long)n * BN + wg * 128) * 2;
+          if (ROW_DST) {
+            // rows leave for caller-given addresses (another GPU's buffer included): the bulk store
+            // carries the row segment there while the next tile is in the tensor cores
+            const unsigned long long base = row_dst_base;
+            dst_addr = base != 0ull ? base + (unsigned long long)col_bytes : 0ull;
+          } else {
+            dst_addr = reinterpret_cast<unsigned long long>(static_cast<uint8_t*>(a.out) + orow * a.n_dim * 2 + col_bytes);
+          }
         }
         ctrl->stg_dst[threadIdx.x - 128] = dst_addr;
         __syncwarp();
@@ -839,6 +853,13 @@ int launch_gemm_sm100(int stage, const GemmArgs& a, cudaStream_t stream) {
                                            int(smem_bytes<1>())));
     moe_gemm_sm100_kernel<1><<<grid, kNumThreads, smem_bytes<1>(), stream>>>(map_a, map_b, a, group_m);
   } else {
+    if (a.row_dst != nullptr) {
+      FLYMOE_CUDA_CHECK(cudaFuncSetAttribute(moe_gemm_sm100_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             int(smem_bytes<2>())));
+      moe_gemm_sm100_kernel<2, true><<<grid, kNumThreads, smem_bytes<2>(), stream>>>(map_a, map_b, a, group_m);
+      FLYMOE_CUDA_CHECK(cudaGetLastError());
+      return FLYMOE_OK;
+    }
     FLYMOE_CUDA_CHECK(cudaFuncSetAttribute(moe_gemm_sm100_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            int(smem_bytes<2>())));
     moe_gemm_sm100_kernel<2><<<grid, kNumThreads, smem_bytes<2>(), stream>>>(map_a, map_b, a, group_m);

@@ -81,6 +81,9 @@ class DispatchPlan:
     recv_counts: list
     rows_out: int
     rows_in: int
+    # peer_offsets[s]: where this rank's block starts in rank s's send order (the row index, on rank s,
+    # of the first row this rank received from s) -- the address base of the fused combine
+    peer_offsets: list | None = None
 
 
 class ExpertParallelMoE:
@@ -109,14 +112,16 @@ class ExpertParallelMoE:
         """Per-chunk send/receive row counts; one count exchange and ONE host sync for the step."""
         n, C = self.world, len(eids_per_chunk)
         send = torch.stack([split_counts(e, n, self.per_rank) for e in eids_per_chunk])   # [C, n]
-        send_by_rank = send.t().contiguous().view(-1)                                      # [n * C]
+        start = torch.cumsum(send, dim=1) - send                                           # block starts, [C, n]
+        send_by_rank = torch.stack([send.t(), start.t()], dim=2).contiguous().view(-1)     # [n * C * 2]
         recv_by_rank = exchange_counts(send_by_rank, self.group)
-        both = torch.stack([send_by_rank, recv_by_rank]).cpu().view(2, n, C)
+        both = torch.stack([send_by_rank, recv_by_rank]).cpu().view(2, n, C, 2)
         plans = []
         for c in range(C):
-            s, r = both[0, :, c], both[1, :, c]
+            s, r = both[0, :, c, 0], both[1, :, c, 0]
             check_counts(s, r, pairs_per_chunk[c])
-            plans.append(DispatchPlan(s.tolist(), r.tolist(), int(s.sum()), int(r.sum())))
+            plans.append(DispatchPlan(s.tolist(), r.tolist(), int(s.sum()), int(r.sum()),
+                                      both[1, :, c, 1].tolist()))
         self.last_plans = plans
         return plans
 
@@ -147,6 +152,20 @@ class ExpertParallelMoE:
             works.append(w)
 
         # experts on chunk c while chunk c+1 is still arriving and chunk c-1 is already going back
+        if getattr(ops, "fused_combine", False):
+            # Stage 2 stores every expert output row straight into the buffer of the rank that owns the
+            # token (peer stores from the GEMM epilogue): no combine all-to-all, only a rendezvous.
+            if C != 1:
+                raise ValueError("the fused combine runs the step as one chunk")
+            for w in works[0]:
+                w.wait()
+            rx, rs, re_ = recv[0]
+            ops.local_experts(rx, rs, re_, self.local.start, plans[0].rows_in, 0,
+                              row_dst=ops.row_destinations(plans[0], self.rank))
+            ops.peer_rendezvous()
+            lo, hi = bounds[0]
+            return ops.combine(ops.returned_rows(pairs[0]), sorted_c[0][0], topk_w[lo:hi], lo, hi, T, 0)
+
         back, back_works = [], []
         for c in range(C):
             for w in works[c]:
@@ -172,7 +191,7 @@ class CudaOps:
 
     def __init__(self, w1q, w1_scale, w2q, w2_scale, experts: int, topk: int, tokens: int,
                  tile_m: int = 128, headroom: float = 1.3, impl: str = "tcgen05", chunks: int = 1,
-                 comm_sms: int = 0):
+                 comm_sms: int = 0, fused_combine: bool = False, group=None):
         from . import _lib
         self._lib = _lib
         self.lib = _lib.load()
@@ -209,6 +228,15 @@ class CudaOps:
         self.headroom = headroom
         self.inner = None
         self._ensure_inner(int(pc * headroom))
+        # Fused combine: a [tokens * topk, H] bf16 buffer per rank that all ranks can store into.
+        self.fused_combine = bool(fused_combine)
+        self.peers = None
+        if self.fused_combine:
+            from .peer import PeerBuffers
+            if chunks != 1:
+                raise ValueError("fused_combine needs chunks == 1")
+            self.peers = PeerBuffers(tokens * topk * self.H * 2, dev, group)
+            self._rendezvous_flag = torch.zeros(1, dtype=i32, device=dev)
 
     def _ensure_inner(self, rows: int) -> None:
         from .layer import FusedMoEBlockscale
@@ -254,9 +282,34 @@ class CudaOps:
     def empty_rows(self, rows: int, like: torch.Tensor) -> torch.Tensor:
         return torch.empty((rows,) + tuple(like.shape[1:]), dtype=like.dtype, device=like.device)
 
-    def local_experts(self, recv_x, recv_s, recv_e, first_expert: int, rows: int, chunk: int = 0):
+    def row_destinations(self, plan: DispatchPlan, rank: int) -> torch.Tensor:
+        """Byte address, in the owning rank's returned-rows buffer, of every received row."""
+        row_bytes = self.H * 2
+        base, at = [], 0
+        for s, (cnt, off) in enumerate(zip(plan.recv_counts, plan.peer_offsets)):
+            base.append(self.peers.ptrs[s] + (off - at) * row_bytes)     # + j * row_bytes for received row j
+            at += cnt
+        base_d = torch.tensor(base, dtype=torch.int64, device=self.dev)
+        cnt_d = torch.tensor(plan.recv_counts, dtype=torch.int64, device=self.dev)
+        rows = plan.rows_in
+        return (torch.repeat_interleave(base_d, cnt_d, output_size=rows)
+                + torch.arange(rows, dtype=torch.int64, device=self.dev) * row_bytes)
+
+    def peer_rendezvous(self) -> None:
+        self.peers.barrier(self._rendezvous_flag)
+
+    def returned_rows(self, pairs: int) -> torch.Tensor:
+        return self.peers.local[:pairs * self.H * 2].view(torch.bfloat16).view(pairs, self.H)
+
+    def local_experts(self, recv_x, recv_s, recv_e, first_expert: int, rows: int, chunk: int = 0, row_dst=None):
         self._ensure_inner(rows)
         b = self.chunk_bufs[chunk]
+        if row_dst is not None:
+            if rows == 0:
+                return None
+            local_ids = (recv_e - first_expert).view(rows, 1)
+            return self.inner.experts_forward(local_ids, self.ones, recv_x, recv_s, rows, self._stream(),
+                                              x_scale_row_major=True, row_dst=row_dst)
         if b["y"] is None or b["y"].shape[0] < max(rows, 1):
             b["y"] = torch.empty((max(int(rows * self.headroom), 1), self.H), dtype=torch.bfloat16, device=self.dev)
         if rows == 0:

@@ -39,7 +39,9 @@ def run_expert_parallel(args, cfg: wl.MoEConfig):
         xq, xs = xq_c.to(dev), xs_c.to(dev)
         chunks = max(1, int(getattr(args, "ep_chunks", 1)))
         comm_sms = int(getattr(args, "ep_comm_sms", 0)) if chunks > 1 else 0
-        ops = CudaOps(w1q, w1s, w2q, w2s, E, k, T, tile_m=args.tile_m, chunks=chunks, comm_sms=comm_sms)
+        fused = getattr(args, "ep_combine", "nccl") == "fused"
+        ops = CudaOps(w1q, w1s, w2q, w2s, E, k, T, tile_m=args.tile_m, chunks=chunks, comm_sms=comm_sms,
+                      fused_combine=fused)
         layer = ExpertParallelMoE(ops, E, k, H, chunks=chunks)
         stream = torch.cuda.current_stream()
 
@@ -157,6 +159,8 @@ def run_expert_parallel(args, cfg: wl.MoEConfig):
                 "data": "synthetic",
                 "config": {**wl.describe(cfg), "tokens_per_gpu": T, "experts_per_gpu": len(mine),
                            "tile_m": args.tile_m, "parallelism": f"ep{world}", "pipeline_chunks": chunks, "sms_left_to_nccl": comm_sms,
+                           "combine": (f"peer stores from the stage-2 epilogue ({ops.peers.kind})" if fused
+                                       else "nccl all_to_all"),
                            "l2_policy": "inputs exceed L2 (dispatched rows and expert weights are GBs per step)"},
                 "roofline": roofline,
                 "comm": {"dispatch_bytes_rank0": int(remote * (H + H // 128 * 4 + 4)),

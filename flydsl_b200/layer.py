@@ -95,7 +95,8 @@ class FusedMoEBlockscale:
             1 if self.renormalize else 0, stream), "topk_gating_softmax")
 
     def experts_forward(self, topk_ids, topk_weights, xq, x_scale_t, tokens: int, stream: int,
-                        out: torch.Tensor | None = None, x_scale_row_major: bool = False) -> torch.Tensor:
+                        out: torch.Tensor | None = None, x_scale_row_major: bool = False,
+                        row_dst: torch.Tensor | None = None) -> torch.Tensor:
         """sort -> gather -> stage 1 -> stage 2 for already-routed tokens.
 
         topk_ids i32 [tokens, k] (ids in [0, E) of this layer's experts; ids outside
@@ -103,7 +104,9 @@ class FusedMoEBlockscale:
         x_scale_t f32 [H/128, tokens] (or row-major [tokens, H/128] with
         ``x_scale_row_major``).  stage2_mode "atomic": weighted atomic accumulation into the
         zeroed ``out``; "reduce": per-pair rows then a weighted top-k reduce (deterministic);
-        "rows" (topk == 1): the unweighted expert output of every input row.
+        "rows" (topk == 1): the unweighted expert output of every input row; with ``row_dst``
+        (int64 [tokens], byte addresses, 0 = drop) each row is stored to its own address --
+        possibly in a peer GPU's mapped memory -- instead of ``out``.
         """
         T, k, U, E, H, I = tokens, self.topk, self.tile_m, self.E, self.H, self.I
         if T > self.max_tokens:
@@ -136,6 +139,20 @@ class FusedMoEBlockscale:
         t1 = self._mark()
         accumulate = self.stage2_mode == "atomic"
         target = self.pair_out if self.stage2_mode == "reduce" else out
+        if row_dst is not None:
+            if self.stage2_mode != "rows":
+                raise ValueError("row_dst needs stage2_mode='rows'")
+            _lib.require_cuda("row_dst", row_dst, (torch.int64,), T)
+            _lib.check(lib.flymoe_moe_gemm2_scatter_rows(
+                row_dst.data_ptr(), self.a2q.data_ptr(), self.a2_scale.data_ptr(), self.cap_rows,
+                self.w2q.data_ptr(), self.w2_scale.data_ptr(), self.sorted_ids.data_ptr(),
+                self.sorted_expert_ids.data_ptr(), self.sorted_weights.data_ptr(), self.num_valid_ids.data_ptr(),
+                T, H, I, blocks, E, k, U, 0, self.out_code, _lib.ROWS_SORTED, _lib.ROWS_SORTED, stream),
+                "moe_gemm2_scatter_rows")
+            if self.timing_events is not None:
+                self.timing_events.append(("gemm1", t0, t1))
+                self.timing_events.append(("gemm2", t1, self._mark()))
+            return out
         _lib.check(lib.flymoe_moe_gemm2(
             target.data_ptr(), self.a2q.data_ptr(), self.a2_scale.data_ptr(), self.cap_rows,
             self.w2q.data_ptr(), self.w2_scale.data_ptr(), self.sorted_ids.data_ptr(),

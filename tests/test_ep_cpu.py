@@ -51,6 +51,39 @@ class FakeOps:
         return self.out
 
 
+class FakeFusedOps(FakeOps):
+    """Fused combine on CPU ranks: the peers' returned-rows buffers are one shared-memory tensor
+    [world, T*K, H]; an "address" is rank * STRIDE + row, and a peer store is a plain write there."""
+    fused_combine = True
+    STRIDE = 1 << 20
+
+    def __init__(self, shared):
+        super().__init__()
+        self.shared = shared
+
+    def row_destinations(self, plan, rank):
+        dst, at = [], 0
+        for s, (cnt, off) in enumerate(zip(plan.recv_counts, plan.peer_offsets)):
+            dst += [s * self.STRIDE + off + j for j in range(cnt)]
+            at += cnt
+        return torch.tensor(dst, dtype=torch.int64)
+
+    def local_experts(self, rx, rs, re_, first, rows, chunk=0, row_dst=None):
+        y = super().local_experts(rx, rs, re_, first, rows, chunk)
+        if row_dst is None:
+            return y
+        for j in range(rows):
+            d = int(row_dst[j])
+            self.shared[d // self.STRIDE, d % self.STRIDE] = y[j]
+        return None
+
+    def peer_rendezvous(self):
+        dist.barrier()
+
+    def returned_rows(self, pairs):
+        return self.shared[dist.get_rank(), :pairs]
+
+
 def _inputs(rank):
     g = torch.Generator().manual_seed(100 + rank)
     logits = torch.randn((T, E), generator=g)
@@ -59,13 +92,17 @@ def _inputs(rank):
     return logits, xq, xs
 
 
-def _worker(rank, world, port, chunks, q):
+def _worker(rank, world, port, chunks, q, shared=None):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         logits, xq, xs = _inputs(rank)
-        layer = ep.ExpertParallelMoE(FakeOps(), E, K, H, chunks=chunks)
+        ops = FakeOps() if shared is None else FakeFusedOps(shared)
+        layer = ep.ExpertParallelMoE(ops, E, K, H, chunks=chunks)
         out = layer(logits, xq, xs)
+        if shared is not None:                      # a second step reuses the peers' buffers
+            dist.barrier()
+            out = layer(logits, xq, xs).clone()
         w, idx, _ = orc.topk_gating_softmax(logits, K)
         want = (xq.float() * xs.mean(dim=1, keepdim=True)).unsqueeze(1) * (idx.float() + 1.0).unsqueeze(-1)
         want = (want * w.unsqueeze(-1)).sum(dim=1)
@@ -75,6 +112,9 @@ def _worker(rank, world, port, chunks, q):
         gathered = [None] * world
         dist.all_gather_object(gathered, (plan.send_counts, plan.recv_counts))
         transposed_ok = all(gathered[r][0][rank] == plan.recv_counts[r] for r in range(world))
+        if chunks == 1:                             # block starts as the sender sees them
+            offs = layer.last_plans[0].peer_offsets
+            transposed_ok = transposed_ok and all(offs[r] == sum(gathered[r][0][:rank]) for r in range(world))
         q.put((rank, bool(ok), bool(counts_ok), bool(transposed_ok), float((out - want).abs().max())))
     finally:
         dist.destroy_process_group()
@@ -94,6 +134,26 @@ def test_dispatch_combine_roundtrip_on_cpu_ranks(world, chunks):
     q = ctx.Queue()
     port = _free_port()
     procs = [ctx.Process(target=_worker, args=(r, world, port, chunks, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, ok, counts_ok, transposed_ok, err in res:
+        assert ok, f"rank {rank}: combined output differs (max abs err {err})"
+        assert counts_ok and transposed_ok
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_fused_combine_addresses_on_cpu_ranks(world):
+    """Every expert output row is written by the rank that computed it into the owner's buffer at the
+    owner's send-order position; the owner's reduce then sees exactly what the all-to-all would return."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    shared = torch.full((world, T * K, H), float("nan")).share_memory_()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, 1, q, shared)) for r in range(world)]
     for p in procs:
         p.start()
     res = [q.get(timeout=120) for _ in range(world)]

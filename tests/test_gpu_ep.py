@@ -23,7 +23,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, routing, chunks, q):
+def _worker(rank, world, port, routing, chunks, q, fused=False):
     import torch.distributed as dist
     from flydsl_b200 import _lib, workloads as wl
     from flydsl_b200.ep import CudaOps, ExpertParallelMoE, expert_range
@@ -43,7 +43,7 @@ def _worker(rank, world, port, routing, chunks, q):
         _x, xq_c, xs_c = wl.make_activations(cfg, rank=rank)
         xq, xs = xq_c.to(dev), xs_c.to(dev)
         ops = CudaOps(w1q[sl].contiguous(), w1s[sl].contiguous(), w2q[sl].contiguous(), w2s[sl].contiguous(),
-                      E, k, T, tile_m=128, headroom=1.0, chunks=chunks)
+                      E, k, T, tile_m=128, headroom=1.0, chunks=chunks, fused_combine=fused)
         layer = ExpertParallelMoE(ops, E, k, H, chunks=chunks)
         out = layer(logits, xq, xs).clone()
         out2 = layer(logits, xq, xs).clone()                                     # buffers are reused
@@ -59,7 +59,7 @@ def _worker(rank, world, port, routing, chunks, q):
         got = out[sel.to(dev)].float().cpu()
         oracle_ok = bool(((got - ref).abs() <= 2e-2 + 2e-2 * ref.abs()).all())
         q.put((rank, bool(torch.equal(out, want)), bool(torch.equal(out, out2)), oracle_ok, _lib.device_status(),
-               layer.last_plan.rows_in))
+               layer.last_plan.rows_in, ops.peers.kind if fused else "nccl"))
     finally:
         dist.destroy_process_group()
 
@@ -80,9 +80,33 @@ def test_expert_parallel_matches_single_gpu(world, routing, chunks):
         p.join(timeout=120)
         assert p.exitcode == 0
     total_rows = 0
-    for rank, same_as_single, repeatable, oracle_ok, status, rows_in in res:
+    for rank, same_as_single, repeatable, oracle_ok, status, rows_in, _kind in res:
         assert status == 0, f"rank {rank}: device-side timeout reported"
         assert same_as_single, f"rank {rank}: expert-parallel output differs from the single-GPU layer"
         assert repeatable and oracle_ok
         total_rows += rows_in
     assert total_rows == world * 300 * 4          # every dispatched row was received exactly once
+
+
+@pytest.mark.parametrize("world,routing", [(2, "uniform"), (4, "zipf"), (8, "uniform")])
+def test_fused_combine_matches_single_gpu(world, routing):
+    """Stage 2 stores the expert outputs straight into the owning ranks' buffers (peer stores from the
+    GEMM epilogue, no combine all-to-all): same bits as the single-GPU layer, twice in a row."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs, found {torch.cuda.device_count()}")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, routing, 1, q, True)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    kinds = {r[6] for r in res}
+    assert len(kinds) == 1 and kinds <= {"symmetric_memory", "cuda_ipc"}
+    for rank, same_as_single, repeatable, oracle_ok, status, rows_in, _kind in res:
+        assert status == 0, f"rank {rank}: device-side timeout reported"
+        assert same_as_single, f"rank {rank}: fused-combine output differs from the single-GPU layer"
+        assert repeatable and oracle_ok

@@ -7,6 +7,7 @@ CUDA-core implementation."""
 import pytest
 import torch
 
+from flydsl_b200 import _lib
 from flydsl_b200 import workloads as wl
 from flydsl_b200.layer import FusedMoEBlockscale, quant_act_1x128
 from oracle import moe_oracle as orc
@@ -193,3 +194,36 @@ def test_layer_all_tokens_on_two_experts():
     assert set(ref["topk_ids"].unique().tolist()) == {2, 5}
     assert int(layer.num_valid_ids[0]) == 2 * 768          # 700 rows per expert padded to 6 blocks of 128
     assert_close(out[:700], ref["out"], RTOL, ATOL + 2.0 ** -7 * float(ref["out"].float().abs().max()), "collision layer")
+
+
+def test_stage2_rows_to_caller_given_addresses():
+    """flymoe_moe_gemm2_scatter_rows: each output row goes to its own address (here a permutation of a
+    local buffer, with some rows dropped) and carries the same bits as the plain per-row output."""
+    cfg = wl.MoEConfig("rows-to", 333, 512, 256, 8, 1, 21)
+    dev = torch.device("cuda", 0)
+    w1q, w1s, w2q, w2s = wl.make_weights(cfg, device=dev)
+    T, H, E = cfg.tokens, cfg.model_dim, cfg.experts
+    _x, xq_c, xs_c = wl.make_activations(cfg)
+    xq, xs = xq_c.to(dev), xs_c.to(dev)
+    g = torch.Generator().manual_seed(5)
+    ids = torch.randint(0, E, (T, 1), generator=g, dtype=torch.int32).to(dev)
+    ones = torch.ones((T, 1), dtype=torch.float32, device=dev)
+    layer = FusedMoEBlockscale(w1q, w1s, w2q, w2s, 1, max_tokens=T, tile_m=128, stage2_mode="rows")
+    s = torch.cuda.current_stream().cuda_stream
+    plain = layer.experts_forward(ids, ones, xq, xs, T, s, x_scale_row_major=True).clone()
+    perm = torch.randperm(T, generator=g)
+    dropped = perm[:17]
+    target = torch.full((T + 3, H), -7.0, dtype=torch.bfloat16, device=dev)
+    dst = target.data_ptr() + (perm.to(torch.int64) + 3) * (H * 2)
+    dst[dropped] = 0
+    for _ in range(2):
+        layer.experts_forward(ids, ones, xq, xs, T, s, x_scale_row_major=True, row_dst=dst.to(dev))
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    kept = torch.ones(T, dtype=torch.bool)
+    kept[dropped] = False
+    got = target[3:].cpu()
+    assert torch.equal(got[perm[kept]], plain.cpu()[kept])
+    untouched = torch.ones(T, dtype=torch.bool)
+    untouched[perm[kept]] = False
+    assert bool((got[untouched] == -7.0).all()) and bool((target[:3] == -7.0).all())
