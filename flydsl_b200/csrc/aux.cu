@@ -30,6 +30,36 @@ gather_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
   }
 }
 
+// ---------------------------------------------------------------------------- dispatch
+// One warp per (token, slot) row in this rank's expert-sorted order.  The row's e4m3 bytes and its
+// fp32 scales are stored where the per-expert tables say -- normally into the operand
+// buffers of the rank that owns the expert, at the row's final position in that rank's block-padded
+// layout, so the receiver neither sorts nor gathers.  dst_*[e] is the address row 0 of THIS rank's
+// order would have; row r lands r * stride bytes further.
+__global__ void __launch_bounds__(256)
+dispatch_rows_kernel(const uint4* __restrict__ x, const float* __restrict__ x_scale,
+                     const int* __restrict__ sorted_ids, const int* __restrict__ sorted_expert_ids,
+                     const int* __restrict__ num_valid_ids, const long long* __restrict__ dst_x,
+                     const long long* __restrict__ dst_scale, int num_tokens, int topk, int row_vec,
+                     int kblocks, int experts, int max_rows) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  const int valid = min(__ldg(num_valid_ids), max_rows);
+  for (int r = blockIdx.x * warps_per_block + (threadIdx.x >> 5); r < valid;
+       r += gridDim.x * warps_per_block) {
+    const int id = __ldg(sorted_ids + r);
+    const int e = __ldg(sorted_expert_ids + r);
+    const int t = id_token(id), s = id_slot(id);
+    if (t >= num_tokens || s >= topk || e < 0 || e >= experts) continue;
+    uint4* dx = reinterpret_cast<uint4*>(__ldg(dst_x + e) + (long long)r * row_vec * 16);
+    const uint4* p = x + size_t(t) * row_vec;
+    for (int i = lane; i < row_vec; i += 32) dx[i] = __ldg(p + i);
+    float* ds = reinterpret_cast<float*>(__ldg(dst_scale + e) + (long long)r * kblocks * 4);
+    const float* ps = x_scale + size_t(t) * kblocks;
+    for (int i = lane; i < kblocks; i += 32) ds[i] = __ldg(ps + i);
+  }
+}
+
 // ---------------------------------------------------------------------------- reduce
 template <typename T> struct Vec8;
 template <> struct Vec8<__half> {
@@ -177,6 +207,26 @@ extern "C" int flymoe_gather_rows(const void* src, void* dst, const int32_t* sor
   gather_rows_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(src), static_cast<uint4*>(dst), sorted_ids, num_valid_ids, num_tokens,
       topk, row_bytes / 16, src_layout, max_rows);
+  FLYMOE_CUDA_CHECK(cudaGetLastError());
+  return FLYMOE_OK;
+}
+
+extern "C" int flymoe_dispatch_rows(const void* x, const float* x_scale, const int32_t* sorted_ids,
+                                    const int32_t* sorted_expert_ids, const int32_t* num_valid_ids,
+                                    const int64_t* dst_x, const int64_t* dst_scale, int num_tokens, int topk,
+                                    int model_dim, int experts, int max_rows, void* stream) {
+  using namespace flymoe;
+  FLYMOE_REQUIRE(x && x_scale && sorted_ids && sorted_expert_ids && num_valid_ids && dst_x && dst_scale,
+                 "dispatch_rows: null pointer");
+  FLYMOE_REQUIRE(model_dim > 0 && model_dim % 128 == 0, "dispatch_rows: model_dim must be a positive multiple of 128");
+  FLYMOE_REQUIRE(num_tokens >= 0 && topk >= 1 && experts >= 1, "dispatch_rows: bad sizes");
+  FLYMOE_REQUIRE(aligned16(x), "dispatch_rows: x must be 16-byte aligned");
+  if (max_rows <= 0) return FLYMOE_OK;
+  const int blocks = std::min(ceil_div(max_rows, 8), sm_count() * 8);
+  dispatch_rows_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x), x_scale, sorted_ids, sorted_expert_ids, num_valid_ids,
+      reinterpret_cast<const long long*>(dst_x), reinterpret_cast<const long long*>(dst_scale), num_tokens, topk,
+      model_dim / 16, model_dim / 128, experts, max_rows);
   FLYMOE_CUDA_CHECK(cudaGetLastError());
   return FLYMOE_OK;
 }

@@ -29,6 +29,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
+import numpy as np
 import torch
 import torch.distributed as dist
 
@@ -86,6 +87,61 @@ class DispatchPlan:
     peer_offsets: list | None = None
 
 
+@dataclass
+class DirectPlan:
+    """Where rows go when they are dispatched by direct stores (``plan_direct``)."""
+    counts: np.ndarray          # [world, E] rows per (source rank, global expert)
+    pos_base: np.ndarray        # [E] int64: row r of this rank's sorted order, expert e, lands at pos_base[e] + r
+    rows_in: int                # rows this rank receives
+    padded_rows: int            # its layout's extent: every local expert padded to whole row blocks
+    block_expert: np.ndarray    # [blocks] int32 local expert of each row block
+    seg_len: np.ndarray         # receiver layout as consecutive segments: length,
+    seg_src: np.ndarray         #   source rank (-1 = padding),
+    seg_src_row: np.ndarray     #   row index of the segment's first row in the source's sorted order
+    send_counts: list
+    recv_counts: list
+    max_padded_rows: int        # largest layout over all ranks (capacity check, identical on every rank)
+
+
+def plan_direct(counts: np.ndarray, rank: int, per_rank: int, unit: int) -> DirectPlan:
+    """Layout of every rank's receive buffer from the all-gathered per-expert row counts.
+
+    A rank's buffer holds its local experts in ascending order, each padded to a multiple of
+    ``unit`` rows; inside an expert the rows of source 0 come first, then source 1, ...; each
+    source's rows keep the order of its own expert-sorted list.  Every rank derives the same
+    layouts from the same matrix, so senders know final positions and receivers know who wrote
+    what, with no further exchange."""
+    counts = np.asarray(counts, dtype=np.int64)
+    world, E = counts.shape
+    src_prefix = np.cumsum(counts, axis=0) - counts                   # rows of expert e from sources < s
+    own_start = np.cumsum(counts, axis=1) - counts                    # start of expert e in source s's order
+    total = counts.sum(axis=0)                                        # [E]
+    padded = (total + unit - 1) // unit * unit
+    start = np.zeros(E, dtype=np.int64)                               # start of expert e in its owner's layout
+    extent = []
+    for d in range(world):
+        sl = slice(d * per_rank, (d + 1) * per_rank)
+        start[sl] = np.cumsum(padded[sl]) - padded[sl]
+        extent.append(int(padded[sl].sum()))
+    pos_base = start + src_prefix[rank] - own_start[rank]
+    mine = range(rank * per_rank, (rank + 1) * per_rank)
+    seg_len, seg_src, seg_src_row, block_expert = [], [], [], []
+    for e in mine:
+        for s_ in range(world):
+            if counts[s_, e] > 0:
+                seg_len.append(int(counts[s_, e])); seg_src.append(s_); seg_src_row.append(int(own_start[s_, e]))
+        if padded[e] > total[e]:
+            seg_len.append(int(padded[e] - total[e])); seg_src.append(-1); seg_src_row.append(0)
+        block_expert += [e - mine.start] * int(padded[e] // unit)
+    owner_of = np.arange(E) // per_rank
+    send_counts = [int(counts[rank, owner_of == d].sum()) for d in range(world)]
+    recv_counts = [int(counts[s_, mine.start:mine.stop].sum()) for s_ in range(world)]
+    return DirectPlan(counts, pos_base.astype(np.int64), int(total[mine.start:mine.stop].sum()), extent[rank],
+                      np.asarray(block_expert, dtype=np.int32), np.asarray(seg_len, dtype=np.int64),
+                      np.asarray(seg_src, dtype=np.int64), np.asarray(seg_src_row, dtype=np.int64),
+                      send_counts, recv_counts, max(extent))
+
+
 class ExpertParallelMoE:
     """Expert-parallel layer.  ``ops`` supplies the device kernels (see ``CudaOps``)."""
 
@@ -132,6 +188,8 @@ class ExpertParallelMoE:
         bounds = chunk_bounds(T, self.chunks)
         C = len(bounds)
         topk_w, topk_ids = ops.gate(logits)
+        if getattr(ops, "direct_dispatch", False):
+            return self._forward_direct(topk_w, topk_ids, xq, x_scale, T)
         sorted_c = []
         for c, (lo, hi) in enumerate(bounds):
             sorted_c.append(ops.sort_by_expert(topk_ids[lo:hi], topk_w[lo:hi], hi - lo, c))
@@ -183,6 +241,29 @@ class ExpertParallelMoE:
             out = ops.combine(back[c], sorted_c[c][0], topk_w[lo:hi], lo, hi, T, c)
         return out
 
+    def _forward_direct(self, topk_w, topk_ids, xq, x_scale, T):
+        """Dispatch and combine as peer stores from this library's own kernels: rows travel straight
+        into the owners' GEMM operand buffers at their final sorted positions, expert outputs travel
+        straight back from stage 2's epilogue.  NCCL carries only the per-expert row counts and the
+        two rendezvous of the step."""
+        ops, k, g = self.ops, self.topk, self.group
+        P = T * k
+        s_ids, s_eids = ops.sort_by_expert(topk_ids, topk_w, T, 0)
+        mine = ops.expert_counts(s_eids, P)                                   # int64 [E]
+        gathered = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(gathered, mine, group=g)
+        counts = torch.stack(gathered).cpu().numpy()                          # the step's host synchronisation
+        if int(counts[self.rank].sum()) != P:
+            raise RuntimeError(f"dispatch plan covers {int(counts[self.rank].sum())} rows, expected {P}")
+        dp = plan_direct(counts, self.rank, self.per_rank, ops.tile_m)
+        self.last_plans = [DispatchPlan(dp.send_counts, dp.recv_counts, P, dp.rows_in)]
+        ops.check_direct_capacity(dp)
+        ops.dispatch_direct(xq, x_scale, s_ids, s_eids, dp, T)
+        ops.peer_rendezvous()                                                 # every rank's rows have landed
+        ops.local_experts_direct(dp)
+        ops.peer_rendezvous()                                                 # every rank's outputs are back
+        return ops.combine(ops.returned_rows(P), s_ids, topk_w, 0, T, T, 0)
+
     __call__ = forward
 
 
@@ -191,7 +272,7 @@ class CudaOps:
 
     def __init__(self, w1q, w1_scale, w2q, w2_scale, experts: int, topk: int, tokens: int,
                  tile_m: int = 128, headroom: float = 1.3, impl: str = "tcgen05", chunks: int = 1,
-                 comm_sms: int = 0, fused_combine: bool = False, group=None):
+                 comm_sms: int = 0, fused_combine: bool = False, direct_dispatch: bool = False, group=None):
         from . import _lib
         self._lib = _lib
         self.lib = _lib.load()
@@ -229,13 +310,20 @@ class CudaOps:
         self.inner = None
         self._ensure_inner(int(pc * headroom))
         # Fused combine: a [tokens * topk, H] bf16 buffer per rank that all ranks can store into.
-        self.fused_combine = bool(fused_combine)
+        # Direct dispatch: in front of it, the stage-1 operand rows and their scales of this rank.
+        self.direct_dispatch = bool(direct_dispatch)
+        self.fused_combine = bool(fused_combine) or self.direct_dispatch
         self.peers = None
         if self.fused_combine:
             from .peer import PeerBuffers
             if chunks != 1:
-                raise ValueError("fused_combine needs chunks == 1")
-            self.peers = PeerBuffers(tokens * topk * self.H * 2, dev, group)
+                raise ValueError("fused_combine / direct_dispatch need chunks == 1")
+            al = lambda n: (n + 255) // 256 * 256
+            rows = self.inner.cap_rows if self.direct_dispatch else 0
+            self._off_xs = 0
+            self._off_xsc = al(rows * self.H)
+            self._off_back = self._off_xsc + al(rows * (self.H // 128) * 4)
+            self.peers = PeerBuffers(self._off_back + tokens * topk * self.H * 2, dev, group)
             self._rendezvous_flag = torch.zeros(1, dtype=i32, device=dev)
 
     def _ensure_inner(self, rows: int) -> None:
@@ -287,7 +375,7 @@ class CudaOps:
         row_bytes = self.H * 2
         base, at = [], 0
         for s, (cnt, off) in enumerate(zip(plan.recv_counts, plan.peer_offsets)):
-            base.append(self.peers.ptrs[s] + (off - at) * row_bytes)     # + j * row_bytes for received row j
+            base.append(self.peers.ptrs[s] + self._off_back + (off - at) * row_bytes)   # + j * row_bytes for row j
             at += cnt
         base_d = torch.tensor(base, dtype=torch.int64, device=self.dev)
         cnt_d = torch.tensor(plan.recv_counts, dtype=torch.int64, device=self.dev)
@@ -299,7 +387,54 @@ class CudaOps:
         self.peers.barrier(self._rendezvous_flag)
 
     def returned_rows(self, pairs: int) -> torch.Tensor:
-        return self.peers.local[:pairs * self.H * 2].view(torch.bfloat16).view(pairs, self.H)
+        back = self.peers.local[self._off_back:self._off_back + pairs * self.H * 2]
+        return back.view(torch.bfloat16).view(pairs, self.H)
+
+    # ---- direct dispatch --------------------------------------------------------------------
+    def expert_counts(self, s_eids: torch.Tensor, pairs: int) -> torch.Tensor:
+        """Rows per global expert from the ascending per-row expert ids of the unit-1 sort."""
+        bounds = torch.arange(0, self.E + 1, device=s_eids.device, dtype=s_eids.dtype)
+        pos = torch.searchsorted(s_eids[:pairs].contiguous(), bounds)
+        return (pos[1:] - pos[:-1]).to(torch.int64)
+
+    def check_direct_capacity(self, dp: DirectPlan) -> None:
+        if dp.max_padded_rows > self.inner.cap_rows:       # same verdict on every rank: all hold the same matrix
+            raise RuntimeError(f"a rank would receive {dp.max_padded_rows} padded rows, buffers hold "
+                               f"{self.inner.cap_rows}; raise headroom")
+
+    def dispatch_direct(self, xq, x_scale, s_ids, s_eids, dp: DirectPlan, T: int) -> None:
+        L, b = self._lib, self.chunk_bufs[0]
+        per = self.E_local
+        owner = np.arange(self.E) // per
+        ptrs = np.asarray(self.peers.ptrs, dtype=np.int64)[owner]
+        kb4 = (self.H // 128) * 4
+        tables = np.stack([ptrs + self._off_xs + dp.pos_base * self.H, ptrs + self._off_xsc + dp.pos_base * kb4])
+        tab = torch.from_numpy(tables).to(self.dev)
+        self._tables = tab                                   # alive until the kernel has run
+        L.check(self.lib.flymoe_dispatch_rows(xq.data_ptr(), x_scale.data_ptr(), s_ids.data_ptr(), s_eids.data_ptr(),
+                                              b["nvalid"].data_ptr(), tab[0].data_ptr(), tab[1].data_ptr(), T, self.k,
+                                              self.H, self.E, T * self.k, self._stream()), "dispatch_rows")
+
+    def local_experts_direct(self, dp: DirectPlan) -> None:
+        inner, dev = self.inner, self.dev
+        rows, blocks = dp.padded_rows, int(dp.block_expert.shape[0])
+        if rows == 0:
+            return
+        row_bytes = self.H * 2
+        seg_pos = np.cumsum(dp.seg_len) - dp.seg_len
+        src = np.maximum(dp.seg_src, 0)
+        base = np.asarray(self.peers.ptrs, dtype=np.int64)[src] + self._off_back + (dp.seg_src_row - seg_pos) * row_bytes
+        seg = torch.from_numpy(np.stack([dp.seg_len, (dp.seg_src >= 0).astype(np.int64), base])).to(dev)
+        which = torch.repeat_interleave(torch.arange(seg.shape[1], device=dev), seg[0], output_size=rows)
+        pos = torch.arange(rows, dtype=torch.int64, device=dev)
+        pad_id = (1 << 24) | rows
+        inner.sorted_ids[:rows] = torch.where(seg[1][which] != 0, pos, pad_id).to(torch.int32)
+        inner.sorted_expert_ids[:blocks] = torch.from_numpy(dp.block_expert).to(dev)
+        inner.num_valid_ids.fill_(rows)
+        row_dst = seg[2][which] + pos * row_bytes
+        base_ptr = self.peers.local.data_ptr()
+        inner.experts_forward_sorted(base_ptr + self._off_xs, base_ptr + self._off_xsc, rows, blocks,
+                                     self._stream(), row_dst)
 
     def local_experts(self, recv_x, recv_s, recv_e, first_expert: int, rows: int, chunk: int = 0, row_dst=None):
         self._ensure_inner(rows)

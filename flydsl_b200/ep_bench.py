@@ -39,9 +39,12 @@ def run_expert_parallel(args, cfg: wl.MoEConfig):
         xq, xs = xq_c.to(dev), xs_c.to(dev)
         chunks = max(1, int(getattr(args, "ep_chunks", 1)))
         comm_sms = int(getattr(args, "ep_comm_sms", 0)) if chunks > 1 else 0
-        fused = getattr(args, "ep_combine", "nccl") == "fused"
+        mode = getattr(args, "ep_combine", "nccl")
+        fused, direct = mode in ("fused", "direct"), mode == "direct"
+        # direct dispatch writes into fixed peer-visible buffers: size them for the routing's imbalance
+        headroom = 1.3 if cfg.routing == "uniform" else 3.0
         ops = CudaOps(w1q, w1s, w2q, w2s, E, k, T, tile_m=args.tile_m, chunks=chunks, comm_sms=comm_sms,
-                      fused_combine=fused)
+                      fused_combine=fused, direct_dispatch=direct, headroom=headroom)
         layer = ExpertParallelMoE(ops, E, k, H, chunks=chunks)
         stream = torch.cuda.current_stream()
 
@@ -136,6 +139,13 @@ def run_expert_parallel(args, cfg: wl.MoEConfig):
         if _lib.device_status() != 0:
             raise RuntimeError("a kernel reported a device-side timeout during the timed region")
 
+        # this library's kernels per step: gate, unit-1 sort, pack (2 row gathers) or the dispatch kernel,
+        # the local experts (their own sort + gather unless the rows arrive sorted), inverse (2) + reduce
+        sort1 = 1 if (T // chunks) * k <= 8192 else 3
+        if direct:
+            launches = 1 + sort1 + 1 + 2 + 3
+        else:
+            launches = 1 + chunks * (sort1 + 2 + ops.inner.experts_kernel_launches(rows_in // chunks) + 3)
         if rank != 0:
             return None
         peaks = load_peaks()
@@ -159,6 +169,8 @@ def run_expert_parallel(args, cfg: wl.MoEConfig):
                 "data": "synthetic",
                 "config": {**wl.describe(cfg), "tokens_per_gpu": T, "experts_per_gpu": len(mine),
                            "tile_m": args.tile_m, "parallelism": f"ep{world}", "pipeline_chunks": chunks, "sms_left_to_nccl": comm_sms,
+                           "dispatch": (f"peer stores into the owners' sorted operand buffers ({ops.peers.kind})"
+                                        if direct else "nccl all_to_all"),
                            "combine": (f"peer stores from the stage-2 epilogue ({ops.peers.kind})" if fused
                                        else "nccl all_to_all"),
                            "l2_policy": "inputs exceed L2 (dispatched rows and expert weights are GBs per step)"},
@@ -170,7 +182,6 @@ def run_expert_parallel(args, cfg: wl.MoEConfig):
                         "h2d_bytes_per_step": int(world * (h_logits.numel() * 4 + h_xq.numel() + h_xs.numel() * 4)),
                         "d2h_bytes_per_step": int(world * h_out.numel() * 2)},
                 "clocks": clocks,
-                "gpu_launches": args.steps * (1 + chunks * ((1 if (T // chunks) * k <= 8192 else 3) + 2
-                                                            + ops.inner.experts_kernel_launches(rows_in // chunks) + 3))}
+                "gpu_launches": args.steps * launches}
     finally:
         dist.destroy_process_group()

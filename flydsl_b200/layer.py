@@ -169,6 +169,41 @@ class FusedMoEBlockscale:
                 self.out_code, stream), "moe_reduce")
         return out
 
+    def experts_forward_sorted(self, xs_ptr: int, x_scale_ptr: int, rows: int, blocks: int, stream: int,
+                               row_dst: torch.Tensor) -> None:
+        """Stage 1 and stage 2 over rows that already sit in sorted, block-padded order.
+
+        ``xs_ptr``: e4m3 [rows, H]; ``x_scale_ptr``: f32 row-major [rows, H/128]; the caller has
+        filled ``self.sorted_ids[:rows]`` (row index, or a pad id), ``self.sorted_expert_ids[:blocks]``
+        and ``self.num_valid_ids[0] = rows``.  Every valid row's output goes to ``row_dst[row]``
+        (int64 byte addresses).  Used by the expert-parallel layer, whose dispatch kernel writes
+        the rows into this layout on the receiving GPU."""
+        if self.stage2_mode != "rows":
+            raise ValueError("experts_forward_sorted needs stage2_mode='rows'")
+        if rows > self.cap_rows or blocks > self.blocks or blocks * self.tile_m != rows:
+            raise ValueError(f"rows={rows} / blocks={blocks} do not fit this layer (cap_rows={self.cap_rows})")
+        if rows == 0:
+            return
+        _lib.require_cuda("row_dst", row_dst, (torch.int64,), rows)
+        lib, E, H, I, U = self.lib, self.E, self.H, self.I, self.tile_m
+        t0 = self._mark()
+        _lib.check(lib.flymoe_moe_gemm1(
+            self.a2q.data_ptr(), self.a2_scale.data_ptr(), self.cap_rows, xs_ptr, x_scale_ptr, 1, H // 128,
+            self.w1q.data_ptr(), self.w1_scale.data_ptr(), self.sorted_ids.data_ptr(),
+            self.sorted_expert_ids.data_ptr(), self.sorted_weights.data_ptr(), self.num_valid_ids.data_ptr(),
+            rows, I, H, blocks, E, 1, U, 0, _lib.E4M3, _lib.ROWS_SORTED, _lib.ROWS_SORTED, _lib.ROWS_SORTED,
+            self.impl, stream), "moe_gemm1")
+        t1 = self._mark()
+        _lib.check(lib.flymoe_moe_gemm2_scatter_rows(
+            row_dst.data_ptr(), self.a2q.data_ptr(), self.a2_scale.data_ptr(), self.cap_rows,
+            self.w2q.data_ptr(), self.w2_scale.data_ptr(), self.sorted_ids.data_ptr(),
+            self.sorted_expert_ids.data_ptr(), self.sorted_weights.data_ptr(), self.num_valid_ids.data_ptr(),
+            rows, H, I, blocks, E, 1, U, 0, self.out_code, _lib.ROWS_SORTED, _lib.ROWS_SORTED, stream),
+            "moe_gemm2_scatter_rows")
+        if self.timing_events is not None:
+            self.timing_events.append(("gemm1", t0, t1))
+            self.timing_events.append(("gemm2", t1, self._mark()))
+
     # ---------------------------------------------------------------- whole layer
     def forward(self, logits: torch.Tensor, xq: torch.Tensor, x_scale_t: torch.Tensor,
                 out: torch.Tensor | None = None, stream=None) -> torch.Tensor:

@@ -164,6 +164,21 @@ int flymoe_moe_gemm2_scatter_rows(const uint64_t* row_dst, const void* a2, const
                                   int doweight, int out_dtype, int a_layout, int a_scale_layout,
                                   void* stream);
 
+/* Expert-parallel dispatch by direct stores.  For every (token, slot) row r of this rank's
+ * expert-sorted order (sorted_ids / sorted_expert_ids of a unit-1 sort, one expert id per
+ * row): the token's e4m3 row (model_dim bytes) is stored to dst_x[e] + r*model_dim and its
+ * model_dim/128 fp32 scales (x_scale row-major [T, model_dim/128]) to
+ * dst_scale[e] + r*(model_dim/128)*4, e being the row's expert.  The two tables hold one
+ * byte address per expert, usually in the memory of the GPU that owns the expert (mapped
+ * into this process, peer access enabled), chosen so that a row lands at its final position
+ * of the receiver's block-padded sorted layout; dst_x addresses must be 16-byte aligned.
+ * Rows with ids outside [0, T) x [0, topk) or experts outside [0, experts) are skipped.
+ * The reference has no counterpart (no dispatch/combine). */
+int flymoe_dispatch_rows(const void* x, const float* x_scale, const int32_t* sorted_ids,
+                         const int32_t* sorted_expert_ids, const int32_t* num_valid_ids,
+                         const int64_t* dst_x, const int64_t* dst_scale, int num_tokens, int topk,
+                         int model_dim, int experts, int max_rows, void* stream);
+
 /* Lets kernels launched on the current device address memory of peer_device that is mapped
  * into this process (needed once per peer before flymoe_moe_gemm2_scatter_rows is given
  * addresses there, unless the mapping mechanism already did it).  Already-enabled is

@@ -84,6 +84,44 @@ class FakeFusedOps(FakeOps):
         return self.shared[dist.get_rank(), :pairs]
 
 
+class FakeDirectOps(FakeFusedOps):
+    """Direct dispatch on CPU ranks: the peers' operand buffers are shared-memory tensors too, rows are
+    written at the positions ``plan_direct`` assigns and read back through its segment list."""
+    direct_dispatch = True
+    tile_m = 4
+    CAP = 256
+
+    def __init__(self, shared, xs_shared, xsc_shared):
+        super().__init__(shared)
+        self.xs_shared, self.xsc_shared = xs_shared, xsc_shared
+
+    def expert_counts(self, s_eids, pairs):
+        return torch.bincount(s_eids[:pairs].long(), minlength=E).to(torch.int64)
+
+    def check_direct_capacity(self, dp):
+        assert dp.max_padded_rows <= self.CAP
+
+    def dispatch_direct(self, xq, xs, s_ids, s_eids, dp, tokens):
+        per = E // dist.get_world_size()
+        for i in range(tokens * K):
+            e, tok = int(s_eids[i]), int(s_ids[i]) & 0xFFFFFF
+            pos = int(dp.pos_base[e]) + i
+            self.xs_shared[e // per, pos] = xq[tok]
+            self.xsc_shared[e // per, pos] = xs[tok]
+
+    def local_experts_direct(self, dp):
+        rank, per = dist.get_rank(), E // dist.get_world_size()
+        assert dp.padded_rows == len(dp.block_expert) * self.tile_m
+        pos = 0
+        for n, src, row in zip(dp.seg_len.tolist(), dp.seg_src.tolist(), dp.seg_src_row.tolist()):
+            for j in range(n):
+                if src >= 0:
+                    e = rank * per + int(dp.block_expert[(pos + j) // self.tile_m])
+                    y = self.xs_shared[rank, pos + j].float() * self.xsc_shared[rank, pos + j].mean() * (e + 1.0)
+                    self.shared[src, row + j] = y
+            pos += n
+
+
 def _inputs(rank):
     g = torch.Generator().manual_seed(100 + rank)
     logits = torch.randn((T, E), generator=g)
@@ -92,12 +130,13 @@ def _inputs(rank):
     return logits, xq, xs
 
 
-def _worker(rank, world, port, chunks, q, shared=None):
+def _worker(rank, world, port, chunks, q, shared=None, direct=None):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         logits, xq, xs = _inputs(rank)
-        ops = FakeOps() if shared is None else FakeFusedOps(shared)
+        ops = (FakeOps() if shared is None else FakeFusedOps(shared) if direct is None
+               else FakeDirectOps(shared, *direct))
         layer = ep.ExpertParallelMoE(ops, E, K, H, chunks=chunks)
         out = layer(logits, xq, xs)
         if shared is not None:                      # a second step reuses the peers' buffers
@@ -112,7 +151,7 @@ def _worker(rank, world, port, chunks, q, shared=None):
         gathered = [None] * world
         dist.all_gather_object(gathered, (plan.send_counts, plan.recv_counts))
         transposed_ok = all(gathered[r][0][rank] == plan.recv_counts[r] for r in range(world))
-        if chunks == 1:                             # block starts as the sender sees them
+        if chunks == 1 and direct is None:          # block starts as the sender sees them
             offs = layer.last_plans[0].peer_offsets
             transposed_ok = transposed_ok and all(offs[r] == sum(gathered[r][0][:rank]) for r in range(world))
         q.put((rank, bool(ok), bool(counts_ok), bool(transposed_ok), float((out - want).abs().max())))
@@ -163,6 +202,60 @@ def test_fused_combine_addresses_on_cpu_ranks(world):
     for rank, ok, counts_ok, transposed_ok, err in res:
         assert ok, f"rank {rank}: combined output differs (max abs err {err})"
         assert counts_ok and transposed_ok
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_direct_dispatch_layout_on_cpu_ranks(world):
+    """Rows stored by their senders at plan_direct's positions are found by the receivers' segment
+    lists, grouped by expert in whole row blocks; outputs return to the owners' send-order slots."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    shared = torch.full((world, T * K, H), float("nan")).share_memory_()
+    xs_sh = torch.zeros((world, FakeDirectOps.CAP, H), dtype=torch.uint8).share_memory_()
+    xsc_sh = torch.zeros((world, FakeDirectOps.CAP, H // 128)).share_memory_()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, 1, q, shared, (xs_sh, xsc_sh))) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, ok, counts_ok, transposed_ok, err in res:
+        assert ok, f"rank {rank}: combined output differs (max abs err {err})"
+        assert counts_ok and transposed_ok
+
+
+def test_plan_direct_positions_and_segments():
+    """Pure bookkeeping: emulate every rank's stores and check every receiver's view of them."""
+    rng = np.random.default_rng(0)
+    world, experts, unit = 4, 16, 8
+    per = experts // world
+    lists = [np.sort(rng.integers(0, experts, size=int(rng.integers(20, 60)))) for _ in range(world)]
+    lists[2] = lists[2][lists[2] != 5]                     # an expert nobody on rank 2 uses
+    counts = np.stack([np.bincount(l, minlength=experts) for l in lists])
+    counts[:, 9] = 0                                       # an expert with no rows at all takes no block
+    lists = [l[l != 9] for l in lists]
+    plans = [ep.plan_direct(counts, r, per, unit) for r in range(world)]
+    bufs = [np.full((plans[d].padded_rows, 2), -1, dtype=np.int64) for d in range(world)]
+    for r in range(world):
+        for i, e in enumerate(lists[r]):
+            pos = plans[r].pos_base[e] + i
+            assert (bufs[e // per][pos] == -1).all(), "two rows at one position"
+            bufs[e // per][pos] = (r, i)
+    for d, p in enumerate(plans):
+        pos = 0
+        for n, src, row in zip(p.seg_len, p.seg_src, p.seg_src_row):
+            for j in range(n):
+                assert tuple(bufs[d][pos + j]) == ((-1, -1) if src < 0 else (src, row + j))
+            pos += n
+        assert pos == p.padded_rows == len(p.block_expert) * unit == max(pos, 0)
+        assert p.rows_in == int((bufs[d][:, 0] >= 0).sum()) == sum(p.recv_counts)
+        for b, el in enumerate(p.block_expert):
+            for s_, i in bufs[d][b * unit:(b + 1) * unit]:
+                assert s_ < 0 or lists[s_][i] == d * per + el
+        assert p.max_padded_rows == max(q.padded_rows for q in plans)
+        assert all(plans[s_].send_counts[d] == p.recv_counts[s_] for s_ in range(world))
 
 
 def test_split_counts_and_checks():

@@ -15,6 +15,15 @@ import torch.multiprocessing as mp
 pytestmark = pytest.mark.gpu
 
 
+def _collect(q, world):
+    res = []
+    for _ in range(world):
+        item = q.get(timeout=300)
+        assert item[0] != "error", f"rank {item[1]} failed: {item[2]}"
+        res.append(item)
+    return res
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -23,45 +32,54 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, routing, chunks, q, fused=False):
+def _worker(rank, world, port, routing, chunks, q, fused=False, direct=False):
     import torch.distributed as dist
-    from flydsl_b200 import _lib, workloads as wl
-    from flydsl_b200.ep import CudaOps, ExpertParallelMoE, expert_range
-    from flydsl_b200.layer import FusedMoEBlockscale
-    from oracle import moe_oracle as orc
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dev = torch.device("cuda", rank)
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
-        cfg = wl.MoEConfig("ep-test", 300, 512, 256, 16, 4, 11, routing)
-        T, k, H, E = cfg.tokens, cfg.topk, cfg.model_dim, cfg.experts
-        w1q, w1s, w2q, w2s = wl.make_weights(cfg, device=dev)                    # all experts (for the check)
-        mine = expert_range(rank, world, E)
-        sl = slice(mine.start, mine.stop)
-        logits = wl.make_logits(cfg, rank=rank).to(dev)
-        _x, xq_c, xs_c = wl.make_activations(cfg, rank=rank)
-        xq, xs = xq_c.to(dev), xs_c.to(dev)
-        ops = CudaOps(w1q[sl].contiguous(), w1s[sl].contiguous(), w2q[sl].contiguous(), w2s[sl].contiguous(),
-                      E, k, T, tile_m=128, headroom=1.0, chunks=chunks, fused_combine=fused)
-        layer = ExpertParallelMoE(ops, E, k, H, chunks=chunks)
-        out = layer(logits, xq, xs).clone()
-        out2 = layer(logits, xq, xs).clone()                                     # buffers are reused
-        torch.cuda.synchronize()
-        single = FusedMoEBlockscale(w1q, w1s, w2q, w2s, k, max_tokens=T, tile_m=128, stage2_mode="reduce")
-        want = single(logits, xq, xs.t().contiguous())
-        torch.cuda.synchronize()
-        sel = torch.tensor([0, 7, 299])
-        tw, ids, _ = orc.topk_gating_softmax(logits.cpu(), k)
-        o1 = orc.stage1(xq_c[sel], xs_c[sel], w1q.cpu(), w1s.cpu(), ids[sel], cfg.inter_dim)
-        a2q, a2s = orc.requant(o1)
-        ref = orc.stage2(a2q, a2s, w2q.cpu(), w2s.cpu(), ids[sel], tw[sel], H)
-        got = out[sel.to(dev)].float().cpu()
-        oracle_ok = bool(((got - ref).abs() <= 2e-2 + 2e-2 * ref.abs()).all())
-        q.put((rank, bool(torch.equal(out, want)), bool(torch.equal(out, out2)), oracle_ok, _lib.device_status(),
-               layer.last_plan.rows_in, ops.peers.kind if fused else "nccl"))
+        _run(rank, world, routing, chunks, q, fused, direct, dev)
+    except Exception as exc:                      # noqa: BLE001 - the parent fails at once instead of timing out
+        q.put(("error", rank, repr(exc)))
+        raise
     finally:
         dist.destroy_process_group()
+
+
+def _run(rank, world, routing, chunks, q, fused, direct, dev):
+    import torch.distributed as dist
+    from flydsl_b200 import _lib, workloads as wl
+    from flydsl_b200.ep import CudaOps, ExpertParallelMoE, expert_range
+    from flydsl_b200.layer import FusedMoEBlockscale
+    from oracle import moe_oracle as orc
+    cfg = wl.MoEConfig("ep-test", 300, 512, 256, 16, 4, 11, routing)
+    T, k, H, E = cfg.tokens, cfg.topk, cfg.model_dim, cfg.experts
+    w1q, w1s, w2q, w2s = wl.make_weights(cfg, device=dev)                    # all experts (for the check)
+    mine = expert_range(rank, world, E)
+    sl = slice(mine.start, mine.stop)
+    logits = wl.make_logits(cfg, rank=rank).to(dev)
+    _x, xq_c, xs_c = wl.make_activations(cfg, rank=rank)
+    xq, xs = xq_c.to(dev), xs_c.to(dev)
+    ops = CudaOps(w1q[sl].contiguous(), w1s[sl].contiguous(), w2q[sl].contiguous(), w2s[sl].contiguous(),
+                  E, k, T, tile_m=128, headroom=float(world) if direct else 1.0, chunks=chunks,
+                  fused_combine=fused, direct_dispatch=direct)
+    layer = ExpertParallelMoE(ops, E, k, H, chunks=chunks)
+    out = layer(logits, xq, xs).clone()
+    out2 = layer(logits, xq, xs).clone()                                     # buffers are reused
+    torch.cuda.synchronize()
+    single = FusedMoEBlockscale(w1q, w1s, w2q, w2s, k, max_tokens=T, tile_m=128, stage2_mode="reduce")
+    want = single(logits, xq, xs.t().contiguous())
+    torch.cuda.synchronize()
+    sel = torch.tensor([0, 7, 299])
+    tw, ids, _ = orc.topk_gating_softmax(logits.cpu(), k)
+    o1 = orc.stage1(xq_c[sel], xs_c[sel], w1q.cpu(), w1s.cpu(), ids[sel], cfg.inter_dim)
+    a2q, a2s = orc.requant(o1)
+    ref = orc.stage2(a2q, a2s, w2q.cpu(), w2s.cpu(), ids[sel], tw[sel], H)
+    got = out[sel.to(dev)].float().cpu()
+    oracle_ok = bool(((got - ref).abs() <= 2e-2 + 2e-2 * ref.abs()).all())
+    q.put((rank, bool(torch.equal(out, want)), bool(torch.equal(out, out2)), oracle_ok, _lib.device_status(),
+           layer.last_plan.rows_in, ops.peers.kind if fused else "nccl"))
 
 
 @pytest.mark.parametrize("world,routing,chunks", [(2, "uniform", 1), (2, "zipf", 3), (4, "uniform", 2),
@@ -75,7 +93,7 @@ def test_expert_parallel_matches_single_gpu(world, routing, chunks):
     procs = [ctx.Process(target=_worker, args=(r, world, port, routing, chunks, q)) for r in range(world)]
     for p in procs:
         p.start()
-    res = [q.get(timeout=300) for _ in range(world)]
+    res = _collect(q, world)
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
@@ -88,19 +106,22 @@ def test_expert_parallel_matches_single_gpu(world, routing, chunks):
     assert total_rows == world * 300 * 4          # every dispatched row was received exactly once
 
 
-@pytest.mark.parametrize("world,routing", [(2, "uniform"), (4, "zipf"), (8, "uniform")])
-def test_fused_combine_matches_single_gpu(world, routing):
+@pytest.mark.parametrize("world,routing,direct", [(2, "uniform", False), (2, "zipf", True), (4, "zipf", False),
+                                                  (4, "uniform", True), (8, "uniform", False), (8, "zipf", True)])
+def test_fused_combine_matches_single_gpu(world, routing, direct):
     """Stage 2 stores the expert outputs straight into the owning ranks' buffers (peer stores from the
-    GEMM epilogue, no combine all-to-all): same bits as the single-GPU layer, twice in a row."""
+    GEMM epilogue, no combine all-to-all); with ``direct`` the dispatch, too, is peer stores, into the
+    owners' stage-1 operand buffers at final sorted positions.  Same bits as the single-GPU layer,
+    twice in a row."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs, found {torch.cuda.device_count()}")
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, routing, 1, q, True)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, routing, 1, q, True, direct)) for r in range(world)]
     for p in procs:
         p.start()
-    res = [q.get(timeout=300) for _ in range(world)]
+    res = _collect(q, world)
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
