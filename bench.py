@@ -230,7 +230,7 @@ def main() -> None:
                     help="sort unit = GEMM row block (16/32/64/128); 0 = pick from the rows per expert")
     ap.add_argument("--stage2-mode", default="atomic", choices=["atomic", "reduce"])
     ap.add_argument("--ep-chunks", type=int, default=1, help="pipeline chunks of the expert-parallel layer")
-    ap.add_argument("--ep-combine", choices=("nccl", "fused", "direct"), default="nccl",
+    ap.add_argument("--ep-combine", choices=("auto", "nccl", "fused", "direct"), default="auto",
                     help="expert-parallel transport: NCCL all-to-all both ways; 'fused' = combine as peer stores "
                          "from stage 2's epilogue; 'direct' = dispatch as peer stores into the owners' operand buffers too")
     ap.add_argument("--ep-comm-sms", type=int, default=0, help="SMs the pipelined EP step leaves to NCCL")

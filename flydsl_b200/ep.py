@@ -1,27 +1,42 @@
 """Expert-parallel FP8 block-scaled MoE layer: one process per GPU, experts sharded
-evenly over the ranks, tokens dispatched and results combined with NCCL all-to-all.
+evenly over the ranks.
 
 The reference has no dispatch/combine (its only expert-parallel hook is the
 ``expert_mask`` of the sort, kernels/moe_sorting_kernel.py:426-440); this module adds the
-partitioned case on top of the same kernels.  The rank's tokens are cut into chunks that
-are pipelined, so that the dispatch of chunk c+1 and the combine of chunk c-1 travel over
-NVLink while chunk c is in the GEMMs:
+partitioned case on top of the same kernels.  Three transports, same arithmetic per
+(token, slot) pair, bit-identical results:
 
+``direct_dispatch`` (the fast path, needs peer-mapped buffers, ``flydsl_b200.peer``):
   1. gate the rank's own tokens over all E experts               (gating kernel)
-  per chunk:
-  2. sort the chunk's (token, slot) pairs by global expert id, unit 1   (sort kernels) — rows
-     grouped by expert are also grouped by destination rank, and every rank's block
-     arrives pre-grouped by local expert
+  2. sort the (token, slot) pairs by global expert id, unit 1     (sort kernels)
+  3. rows per expert, all-gathered; every rank derives every rank's receive layout
+     (``plan_direct``) -- the step's single host synchronisation
+  4. dispatch: each row and its scales are stored straight into the owning rank's stage-1
+     operand buffer, at its final position of that rank's expert-sorted, block-padded
+     layout                                                        (``flymoe_dispatch_rows``, peer stores)
+  5. rendezvous; stage 1; stage 2, whose epilogue stores every output row straight into the
+     token owner's buffer                                          (``flymoe_moe_gemm2_scatter_rows``)
+  6. rendezvous; out[t] = sum_s w[t,s] * returned_row(t,s)        (indexed reduce kernel)
+  The receiver neither sorts nor gathers, and NCCL carries only the counts and the two
+  rendezvous (one-element all-reduces).
+
+``fused_combine``: dispatch by NCCL all-to-all (steps 2-5 of the list below), outputs return
+  as in 5./6. above.
+
+NCCL both ways (default without peer buffers; can be cut into pipelined chunks):
+  2. sort by global expert id, unit 1 -- rows grouped by expert are also grouped by
+     destination rank, and every rank's block arrives pre-grouped by local expert
   3. row counts per destination, exchanged for all chunks at once      (one tiny all_to_all,
      the step's single host synchronisation)
   4. pack e4m3 rows and their fp32 scales in that order           (row-gather kernel)
   5. dispatch rows, scales and expert ids                          (all_to_all_single x3, async)
   6. local experts: sort by local expert, stage 1, stage 2 into per-row bf16 outputs
   7. combine: send the rows back                                  (all_to_all_single, async)
-  8. out[t] = sum_s w[t,s] * returned_row(t,s)                    (indexed reduce kernel)
+  8. the indexed reduce.
 
-Remote data always lands in this GPU's memory before any kernel reads it.  The host-side
-bookkeeping (``split_counts``, ``exchange_counts``, the step order in ``forward``) is
+Remote data always lands in this GPU's memory before any kernel reads it: kernels only ever
+*store* to a peer, never load from one or wait on one.  The host-side bookkeeping
+(``split_counts``, ``exchange_counts``, ``plan_direct``, the step order in ``forward``) is
 device-agnostic so it can be exercised with gloo on CPU ranks through the ``ops`` seam.
 """
 
@@ -124,22 +139,18 @@ def plan_direct(counts: np.ndarray, rank: int, per_rank: int, unit: int) -> Dire
         start[sl] = np.cumsum(padded[sl]) - padded[sl]
         extent.append(int(padded[sl].sum()))
     pos_base = start + src_prefix[rank] - own_start[rank]
-    mine = range(rank * per_rank, (rank + 1) * per_rank)
-    seg_len, seg_src, seg_src_row, block_expert = [], [], [], []
-    for e in mine:
-        for s_ in range(world):
-            if counts[s_, e] > 0:
-                seg_len.append(int(counts[s_, e])); seg_src.append(s_); seg_src_row.append(int(own_start[s_, e]))
-        if padded[e] > total[e]:
-            seg_len.append(int(padded[e] - total[e])); seg_src.append(-1); seg_src_row.append(0)
-        block_expert += [e - mine.start] * int(padded[e] // unit)
-    owner_of = np.arange(E) // per_rank
-    send_counts = [int(counts[rank, owner_of == d].sum()) for d in range(world)]
-    recv_counts = [int(counts[s_, mine.start:mine.stop].sum()) for s_ in range(world)]
-    return DirectPlan(counts, pos_base.astype(np.int64), int(total[mine.start:mine.stop].sum()), extent[rank],
-                      np.asarray(block_expert, dtype=np.int32), np.asarray(seg_len, dtype=np.int64),
-                      np.asarray(seg_src, dtype=np.int64), np.asarray(seg_src_row, dtype=np.int64),
-                      send_counts, recv_counts, max(extent))
+    lo, hi = rank * per_rank, (rank + 1) * per_rank
+    # this rank's layout as segments: per local expert one segment per source, then the padding
+    seg_len = np.concatenate([counts[:, lo:hi].T, (padded - total)[lo:hi, None]], axis=1).reshape(-1)
+    seg_src = np.tile(np.concatenate([np.arange(world), [-1]]), per_rank)
+    seg_src_row = np.concatenate([own_start[:, lo:hi].T, np.zeros((per_rank, 1), dtype=np.int64)], axis=1).reshape(-1)
+    keep = seg_len > 0
+    block_expert = np.repeat(np.arange(per_rank, dtype=np.int32), padded[lo:hi] // unit)
+    send_counts = counts[rank].reshape(world, per_rank).sum(axis=1).tolist()
+    recv_counts = counts[:, lo:hi].sum(axis=1).tolist()
+    return DirectPlan(counts, pos_base.astype(np.int64), int(total[lo:hi].sum()), extent[rank], block_expert,
+                      seg_len[keep].astype(np.int64), seg_src[keep].astype(np.int64),
+                      seg_src_row[keep].astype(np.int64), send_counts, recv_counts, max(extent))
 
 
 class ExpertParallelMoE:

@@ -8,6 +8,7 @@ device (CUDA events between barriers), the maximum over ranks is reported.
 from __future__ import annotations
 
 import os
+import sys
 
 import torch
 import torch.distributed as dist
@@ -39,12 +40,25 @@ def run_expert_parallel(args, cfg: wl.MoEConfig):
         xq, xs = xq_c.to(dev), xs_c.to(dev)
         chunks = max(1, int(getattr(args, "ep_chunks", 1)))
         comm_sms = int(getattr(args, "ep_comm_sms", 0)) if chunks > 1 else 0
-        mode = getattr(args, "ep_combine", "nccl")
-        fused, direct = mode in ("fused", "direct"), mode == "direct"
+        mode = getattr(args, "ep_combine", "auto")
+        if chunks > 1 and mode == "auto":
+            mode = "nccl"                                    # the chunked pipeline is an NCCL path
         # direct dispatch writes into fixed peer-visible buffers: size them for the routing's imbalance
         headroom = 1.3 if cfg.routing == "uniform" else 3.0
-        ops = CudaOps(w1q, w1s, w2q, w2s, E, k, T, tile_m=args.tile_m, chunks=chunks, comm_sms=comm_sms,
-                      fused_combine=fused, direct_dispatch=direct, headroom=headroom)
+
+        def make_ops(m):
+            return CudaOps(w1q, w1s, w2q, w2s, E, k, T, tile_m=args.tile_m, chunks=chunks, comm_sms=comm_sms,
+                           fused_combine=m in ("fused", "direct"), direct_dispatch=m in ("direct", "auto"),
+                           headroom=headroom)
+        try:
+            ops = make_ops(mode)
+        except RuntimeError as exc:                          # no peer mapping here: same outcome on every rank
+            if mode != "auto":
+                raise
+            if rank == 0:
+                print(f"[bench] peer buffers unavailable ({exc}); using the NCCL all-to-all path", file=sys.stderr)
+            mode, ops = "nccl", make_ops("nccl")
+        fused, direct = ops.fused_combine, ops.direct_dispatch
         layer = ExpertParallelMoE(ops, E, k, H, chunks=chunks)
         stream = torch.cuda.current_stream()
 
@@ -163,6 +177,19 @@ def run_expert_parallel(args, cfg: wl.MoEConfig):
                     "traffic": None, "ms_per_step_all_chunks": round(s1_ms, 4),
                     "stage2_ms_per_step_all_chunks": round(s2_ms, 4),
                     "rows_received_rank0": rows_in}
+        fused_roofline = None
+        if fused and s2_ms == s2_ms:
+            # stage 2 + combine in one kernel: bounded by the slower of its math at the FP8 peak and its
+            # peer stores at the measured per-direction NVLink rate of this pool (770 GB/s)
+            s2_flops = 2.0 * rows_in * H * I
+            link_bytes = float(rows_in - nplan.recv_counts[rank]) * H * 2
+            t_tensor, t_link = s2_flops / (fp8_peak * 1e12), link_bytes / 770e9
+            target = max(t_tensor, t_link)
+            fused_roofline = {"kernel": "moe_gemm_sm100_kernel<2, true> (stage 2 + combine, rank 0)",
+                              "bound": "nvlink" if t_link > t_tensor else "tensor",
+                              "tensor_ms": round(t_tensor * 1e3, 4), "nvlink_ms": round(t_link * 1e3, 4),
+                              "nvlink_peak_gbs": 770.0, "nvlink_bytes": int(link_bytes),
+                              "measured_ms": round(s2_ms, 4), "frac": round(target * 1e3 / s2_ms, 4)}
         return {"metric": METRIC, "value": round(flops / (ms * 1e-3) / 1e12, 2), "unit": UNIT, "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate and scales)",
@@ -175,7 +202,8 @@ def run_expert_parallel(args, cfg: wl.MoEConfig):
                                        else "nccl all_to_all"),
                            "l2_policy": "inputs exceed L2 (dispatched rows and expert weights are GBs per step)"},
                 "roofline": roofline,
-                "comm": {"dispatch_bytes_rank0": int(remote * (H + H // 128 * 4 + 4)),
+                "fused_stage2_roofline": fused_roofline,
+                "comm": {"dispatch_bytes_rank0": int(remote * (H + H // 128 * 4 + (0 if direct else 4))),
                          "combine_bytes_rank0": int(remote * H * 2), "load_imbalance_max_over_mean": round(imbalance, 3)},
                 "cpu_baseline": None,
                 "e2e": {"value": round(flops / (e2e_ms * 1e-3) / 1e12, 2), "unit": UNIT, "ms_per_step": round(e2e_ms, 4),
