@@ -73,15 +73,25 @@ def cpu_baseline(cfg: wl.MoEConfig, n_sample_experts: int, device_weights=None, 
 def run_reference_arm(args, cfg, rank: int) -> None:
     if rank != 0:
         return
+    # Each step is one bounded sample (~1.5 s of CPU work).  W warm-up samples and up to K timed ones are
+    # run, but no more than fit into about a minute, so that large K still ends within minutes.
+    budget_s, t_begin = 60.0, time.perf_counter()
+    warm = 0
+    for _ in range(min(max(args.warmup, 0), 2)):
+        cpu_baseline(cfg, args.cpu_experts)
+        warm += 1
     vals = []
     last = None
-    for _ in range(max(1, min(args.steps, 3))):
+    for _ in range(max(1, args.steps)):
         last = cpu_baseline(cfg, args.cpu_experts)
         vals.append(last["value"])
+        if time.perf_counter() - t_begin > budget_s:
+            break
     v = statistics.median(vals)
     last["value"] = v
     line = {"metric": METRIC, "value": v, "unit": UNIT, "impl": "reference", "n_gpus": args.gpus,
-            "steps": len(vals), "warmup": 0, "ms_per_step": last["seconds"] * 1e3, "higher_is_better": True,
+            "steps": len(vals), "steps_requested": args.steps, "warmup": warm,
+            "ms_per_step": last["seconds"] * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32 (CPU dequantised fp8)", "data": "synthetic",
             "config": wl.describe(cfg), "cpu_baseline": last,
             "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
