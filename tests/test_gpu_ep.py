@@ -106,13 +106,15 @@ def test_expert_parallel_matches_single_gpu(world, routing, chunks):
     assert total_rows == world * 300 * 4          # every dispatched row was received exactly once
 
 
-@pytest.mark.parametrize("world,routing,direct", [(2, "uniform", False), (2, "zipf", True), (4, "zipf", False),
+@pytest.mark.parametrize("world,routing,direct", [(1, "zipf", False), (1, "uniform", True),
+                                                  (2, "uniform", False), (2, "zipf", True), (4, "zipf", False),
                                                   (4, "uniform", True), (8, "uniform", False), (8, "zipf", True)])
 def test_fused_combine_matches_single_gpu(world, routing, direct):
     """Stage 2 stores the expert outputs straight into the owning ranks' buffers (peer stores from the
     GEMM epilogue, no combine all-to-all); with ``direct`` the dispatch, too, is peer stores, into the
     owners' stage-1 operand buffers at final sorted positions.  Same bits as the single-GPU layer,
-    twice in a row."""
+    twice in a row.  The one-rank cases run the same kernels and bookkeeping with every row staying
+    on the GPU, so a single-GPU box covers them too."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs, found {torch.cuda.device_count()}")
     ctx = mp.get_context("spawn")
