@@ -49,7 +49,6 @@ _SIGNATURES = {
                                               c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                               c_int, c_int, _P]),
     "flymoe_dispatch_rows": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P]),
-    "flymoe_enable_peer_access": (c_int, [c_int]),
     "flymoe_set_gemm_cta_limit": (c_int, [c_int]),
     "flymoe_moe_reduce": (c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P]),
     "flymoe_sorted_inverse": (c_int, [_P, _P, _P, c_int, c_int, c_int, _P]),

@@ -77,23 +77,4 @@ int flymoe_device_status(int* status_out) {
   return FLYMOE_OK;
 }
 
-int flymoe_enable_peer_access(int peer_device) {
-  int dev = 0;
-  FLYMOE_CUDA_CHECK(cudaGetDevice(&dev));
-  if (peer_device == dev) return FLYMOE_OK;
-  int can = 0;
-  FLYMOE_CUDA_CHECK(cudaDeviceCanAccessPeer(&can, dev, peer_device));
-  if (!can) {
-    flymoe::set_last_error_msg("flymoe_enable_peer_access: the current device cannot address that peer");
-    return FLYMOE_ERR_INVALID_ARGUMENT;
-  }
-  cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
-  if (e == cudaErrorPeerAccessAlreadyEnabled) {
-    (void)cudaGetLastError();               // not an error: someone in this process enabled it before
-    return FLYMOE_OK;
-  }
-  FLYMOE_CUDA_CHECK(e);
-  return FLYMOE_OK;
-}
-
 }  // extern "C"

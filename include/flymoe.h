@@ -149,7 +149,7 @@ int flymoe_moe_gemm2(void* out, const void* a2, const float* scale_a, int64_t sa
 /* Stage 2 with a caller-given destination per output row: row_dst[t*topk+s] is the byte
  * address the H out_dtype (F16/BF16) values of that (token, slot) row are stored to, 0 drops
  * the row.  Addresses must be 16-byte aligned and may lie in another GPU's memory that is
- * mapped into this process (peer access enabled): in the expert-parallel layer each rank
+ * mapped into this process with peer access: in the expert-parallel layer each rank
  * stores its expert outputs straight into the buffers of the ranks that own the tokens, so
  * the combine transfer rides on stage 2's epilogue instead of a separate all-to-all.
  * No accumulation, no routing weight unless doweight; tensor-core kernel only.  The
@@ -178,12 +178,6 @@ int flymoe_dispatch_rows(const void* x, const float* x_scale, const int32_t* sor
                          const int32_t* sorted_expert_ids, const int32_t* num_valid_ids,
                          const int64_t* dst_x, const int64_t* dst_scale, int num_tokens, int topk,
                          int model_dim, int experts, int max_rows, void* stream);
-
-/* Lets kernels launched on the current device address memory of peer_device that is mapped
- * into this process (needed once per peer before flymoe_moe_gemm2_scatter_rows is given
- * addresses there, unless the mapping mechanism already did it).  Already-enabled is
- * success.  No reference counterpart. */
-int flymoe_enable_peer_access(int peer_device);
 
 /* Caps the persistent grid of the two GEMM stages at max_ctas CTAs (0 restores one CTA per SM).
  * Process-wide.  For callers that run communication kernels next to the GEMMs (the

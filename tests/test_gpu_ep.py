@@ -128,7 +128,7 @@ def test_fused_combine_matches_single_gpu(world, routing, direct):
         p.join(timeout=120)
         assert p.exitcode == 0
     kinds = {r[6] for r in res}
-    assert len(kinds) == 1 and kinds <= {"symmetric_memory", "cuda_ipc"}
+    assert kinds == {"symmetric_memory"}
     for rank, same_as_single, repeatable, oracle_ok, status, rows_in, _kind in res:
         assert status == 0, f"rank {rank}: device-side timeout reported"
         assert same_as_single, f"rank {rank}: fused-combine output differs from the single-GPU layer"
