@@ -40,7 +40,8 @@ __global__ void __launch_bounds__(256)
 dispatch_rows_kernel(const uint4* __restrict__ x, const float* __restrict__ x_scale,
                      const int* __restrict__ sorted_ids, const int* __restrict__ sorted_expert_ids,
                      const int* __restrict__ num_valid_ids, const long long* __restrict__ dst_x,
-                     const long long* __restrict__ dst_scale, int num_tokens, int topk, int row_vec,
+                     const long long* __restrict__ dst_scale, const long long* __restrict__ pos_base,
+                     long long pos_limit, int* __restrict__ status, int num_tokens, int topk, int row_vec,
                      int kblocks, int experts, int max_rows) {
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
@@ -51,6 +52,10 @@ dispatch_rows_kernel(const uint4* __restrict__ x, const float* __restrict__ x_sc
     const int e = __ldg(sorted_expert_ids + r);
     const int t = id_token(id), s = id_slot(id);
     if (t >= num_tokens || s >= topk || e < 0 || e >= experts) continue;
+    if (pos_base != nullptr && __ldg(pos_base + e) + r >= pos_limit) {   // would fall outside the receiver's buffer
+      if (lane == 0) atomicOr(status, 2);
+      continue;
+    }
     uint4* dx = reinterpret_cast<uint4*>(__ldg(dst_x + e) + (long long)r * row_vec * 16);
     const uint4* p = x + size_t(t) * row_vec;
     for (int i = lane; i < row_vec; i += 32) dx[i] = __ldg(p + i);
@@ -213,8 +218,9 @@ extern "C" int flymoe_gather_rows(const void* src, void* dst, const int32_t* sor
 
 extern "C" int flymoe_dispatch_rows(const void* x, const float* x_scale, const int32_t* sorted_ids,
                                     const int32_t* sorted_expert_ids, const int32_t* num_valid_ids,
-                                    const int64_t* dst_x, const int64_t* dst_scale, int num_tokens, int topk,
-                                    int model_dim, int experts, int max_rows, void* stream) {
+                                    const int64_t* dst_x, const int64_t* dst_scale, const int64_t* pos_base,
+                                    int64_t pos_limit, int num_tokens, int topk, int model_dim, int experts,
+                                    int max_rows, void* stream) {
   using namespace flymoe;
   FLYMOE_REQUIRE(x && x_scale && sorted_ids && sorted_expert_ids && num_valid_ids && dst_x && dst_scale,
                  "dispatch_rows: null pointer");
@@ -222,10 +228,13 @@ extern "C" int flymoe_dispatch_rows(const void* x, const float* x_scale, const i
   FLYMOE_REQUIRE(num_tokens >= 0 && topk >= 1 && experts >= 1, "dispatch_rows: bad sizes");
   FLYMOE_REQUIRE(aligned16(x), "dispatch_rows: x must be 16-byte aligned");
   if (max_rows <= 0) return FLYMOE_OK;
+  int* status = device_status_ptr();
+  FLYMOE_REQUIRE(status != nullptr, "dispatch_rows: no CUDA device");
   const int blocks = std::min(ceil_div(max_rows, 8), sm_count() * 8);
   dispatch_rows_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(x), x_scale, sorted_ids, sorted_expert_ids, num_valid_ids,
-      reinterpret_cast<const long long*>(dst_x), reinterpret_cast<const long long*>(dst_scale), num_tokens, topk,
+      reinterpret_cast<const long long*>(dst_x), reinterpret_cast<const long long*>(dst_scale),
+      reinterpret_cast<const long long*>(pos_base), static_cast<long long>(pos_limit), status, num_tokens, topk,
       model_dim / 16, model_dim / 128, experts, max_rows);
   FLYMOE_CUDA_CHECK(cudaGetLastError());
   return FLYMOE_OK;

@@ -18,7 +18,10 @@ partitioned case on top of the same kernels.  Three transports, same arithmetic 
      token owner's buffer                                          (``flymoe_moe_gemm2_scatter_rows``)
   6. rendezvous; out[t] = sum_s w[t,s] * returned_row(t,s)        (indexed reduce kernel)
   The receiver neither sorts nor gathers, and NCCL carries only the counts and the two
-  rendezvous (one-element all-reduces).
+  rendezvous (one-element all-reduces).  With ``device_plan`` step 3 is tensor operations on the
+  GPU (``plan_direct_tensors``) and the step has no host synchronisation at all; rows that would
+  not fit the receiver's buffer are then dropped and flagged in the device status word instead
+  of raising.
 
 ``fused_combine``: dispatch by NCCL all-to-all (steps 2-5 of the list below), outputs return
   as in 5./6. above.
@@ -153,6 +156,43 @@ def plan_direct(counts: np.ndarray, rank: int, per_rank: int, unit: int) -> Dire
                       seg_src_row[keep].astype(np.int64), send_counts, recv_counts, max(extent))
 
 
+def plan_direct_tensors(counts: torch.Tensor, rank: int, per_rank: int, unit: int, cap_rows: int) -> dict:
+    """``plan_direct`` as tensor operations on the device that holds ``counts`` -- no host round trip.
+
+    Returns pos_base [E]; for this rank's layout the per-row arrays of length ``cap_rows``: ``src``
+    (source rank, -1 = padding or beyond the layout), ``src_row`` (row in the source's sorted order);
+    ``block_expert`` [cap_rows // unit] (local expert of each row block, clamped beyond the layout);
+    ``padded_rows`` / ``rows_in`` / ``max_padded_rows`` as 0-dim tensors."""
+    world, E = counts.shape
+    dev = counts.device
+    src_prefix = torch.cumsum(counts, dim=0) - counts
+    own_start = torch.cumsum(counts, dim=1) - counts
+    total = counts.sum(dim=0)
+    padded = (total + unit - 1) // unit * unit
+    pad2 = padded.view(world, per_rank)
+    start = (torch.cumsum(pad2, dim=1) - pad2).reshape(-1)
+    extent = pad2.sum(dim=1)                                              # [world]
+    pos_base = start + src_prefix[rank] - own_start[rank]
+    lo, hi = rank * per_rank, (rank + 1) * per_rank
+    # segments of this rank's layout, in layout order: per local expert one per source, then the padding
+    seg_len = torch.cat([counts[:, lo:hi].t(), (padded - total)[lo:hi, None]], dim=1).reshape(-1)
+    seg_src = torch.cat([torch.arange(world, device=dev), torch.tensor([-1], device=dev)]).repeat(per_rank)
+    seg_row = torch.cat([own_start[:, lo:hi].t(), torch.zeros((per_rank, 1), dtype=counts.dtype, device=dev)],
+                        dim=1).reshape(-1)
+    seg_end = torch.cumsum(seg_len, dim=0)
+    pos = torch.arange(cap_rows, dtype=torch.int64, device=dev)
+    which = torch.searchsorted(seg_end, pos, right=True)                  # zero-length segments are skipped
+    inside = which < seg_len.numel()
+    which = which.clamp(max=seg_len.numel() - 1)
+    src = torch.where(inside, seg_src[which], -1)
+    src_row = seg_row[which] + (pos - (seg_end - seg_len)[which])
+    blk_end = torch.cumsum(padded[lo:hi] // unit, dim=0)                  # row blocks per local expert
+    blocks = torch.arange(cap_rows // unit, dtype=torch.int64, device=dev)
+    block_expert = torch.searchsorted(blk_end, blocks, right=True).clamp(max=per_rank - 1)
+    return {"pos_base": pos_base, "src": src, "src_row": src_row, "block_expert": block_expert.to(torch.int32),
+            "padded_rows": extent[rank], "rows_in": total[lo:hi].sum(), "max_padded_rows": extent.max()}
+
+
 class ExpertParallelMoE:
     """Expert-parallel layer.  ``ops`` supplies the device kernels (see ``CudaOps``)."""
 
@@ -171,6 +211,9 @@ class ExpertParallelMoE:
     def last_plan(self) -> DispatchPlan:
         """Whole-step totals over the chunks of the last forward."""
         ps = self.last_plans
+        if not ps and getattr(self, "_counts_dev", None) is not None:         # device-planned step: fetch on demand
+            dp = plan_direct(self._counts_dev.cpu().numpy(), self.rank, self.per_rank, self.ops.tile_m)
+            ps = [DispatchPlan(dp.send_counts, dp.recv_counts, sum(dp.send_counts), dp.rows_in)]
         send = [sum(p.send_counts[r] for p in ps) for r in range(self.world)]
         recv = [sum(p.recv_counts[r] for p in ps) for r in range(self.world)]
         return DispatchPlan(send, recv, sum(send), sum(recv))
@@ -263,6 +306,12 @@ class ExpertParallelMoE:
         mine = ops.expert_counts(s_eids, P)                                   # int64 [E]
         gathered = [torch.empty_like(mine) for _ in range(self.world)]
         dist.all_gather(gathered, mine, group=g)
+        if getattr(ops, "device_plan", False):
+            # the whole plan stays on the device: no host synchronisation in the step
+            self._counts_dev = torch.stack(gathered)
+            self.last_plans = []
+            ops.run_direct_on_device(xq, x_scale, s_ids, s_eids, self._counts_dev, self.rank, T)
+            return ops.combine(ops.returned_rows(P), s_ids, topk_w, 0, T, T, 0)
         counts = torch.stack(gathered).cpu().numpy()                          # the step's host synchronisation
         if int(counts[self.rank].sum()) != P:
             raise RuntimeError(f"dispatch plan covers {int(counts[self.rank].sum())} rows, expected {P}")
@@ -283,7 +332,8 @@ class CudaOps:
 
     def __init__(self, w1q, w1_scale, w2q, w2_scale, experts: int, topk: int, tokens: int,
                  tile_m: int = 128, headroom: float = 1.3, impl: str = "tcgen05", chunks: int = 1,
-                 comm_sms: int = 0, fused_combine: bool = False, direct_dispatch: bool = False, group=None):
+                 comm_sms: int = 0, fused_combine: bool = False, direct_dispatch: bool = False,
+                 device_plan: bool = False, group=None):
         from . import _lib
         self._lib = _lib
         self.lib = _lib.load()
@@ -323,6 +373,7 @@ class CudaOps:
         # Fused combine: a [tokens * topk, H] bf16 buffer per rank that all ranks can store into.
         # Direct dispatch: in front of it, the stage-1 operand rows and their scales of this rank.
         self.direct_dispatch = bool(direct_dispatch)
+        self.device_plan = bool(device_plan) and self.direct_dispatch
         self.fused_combine = bool(fused_combine) or self.direct_dispatch
         self.peers = None
         if self.fused_combine:
@@ -423,8 +474,42 @@ class CudaOps:
         tab = torch.from_numpy(tables).to(self.dev)
         self._tables = tab                                   # alive until the kernel has run
         L.check(self.lib.flymoe_dispatch_rows(xq.data_ptr(), x_scale.data_ptr(), s_ids.data_ptr(), s_eids.data_ptr(),
-                                              b["nvalid"].data_ptr(), tab[0].data_ptr(), tab[1].data_ptr(), T, self.k,
-                                              self.H, self.E, T * self.k, self._stream()), "dispatch_rows")
+                                              b["nvalid"].data_ptr(), tab[0].data_ptr(), tab[1].data_ptr(), None, 0,
+                                              T, self.k, self.H, self.E, T * self.k, self._stream()), "dispatch_rows")
+
+    def run_direct_on_device(self, xq, x_scale, s_ids, s_eids, counts, rank: int, T: int) -> None:
+        """Dispatch, local experts and the two rendezvous with the plan computed by tensor operations on
+        the GPU.  Launch sizes use the buffers' capacity; the kernels read the real extents from device
+        memory.  A step that does not fit the capacity drops the rows that would fall outside and raises
+        the device status word (``flymoe_device_status``) instead of an exception."""
+        L, b, inner, dev = self._lib, self.chunk_bufs[0], self.inner, self.dev
+        cap, U, H = inner.cap_rows, self.tile_m, self.H
+        pl = plan_direct_tensors(counts, rank, self.E_local, U, cap)
+        if not hasattr(self, "_owner_ptrs"):
+            owner = torch.arange(self.E, device=dev) // self.E_local
+            ptrs = torch.tensor(self.peers.ptrs, dtype=torch.int64, device=dev)
+            self._owner_ptrs, self._peer_ptrs = ptrs[owner], ptrs
+        kb4 = (H // 128) * 4
+        tab = torch.stack([self._owner_ptrs + self._off_xs + pl["pos_base"] * H,
+                           self._owner_ptrs + self._off_xsc + pl["pos_base"] * kb4, pl["pos_base"]])
+        self._tables = tab
+        L.check(self.lib.flymoe_dispatch_rows(xq.data_ptr(), x_scale.data_ptr(), s_ids.data_ptr(), s_eids.data_ptr(),
+                                              b["nvalid"].data_ptr(), tab[0].data_ptr(), tab[1].data_ptr(),
+                                              tab[2].data_ptr(), cap, T, self.k, H, self.E, T * self.k,
+                                              self._stream()), "dispatch_rows")
+        self.peer_rendezvous()
+        rows = torch.clamp(pl["padded_rows"], max=cap)
+        pos = torch.arange(cap, dtype=torch.int64, device=dev)
+        valid = (pl["src"] >= 0) & (pos < rows)
+        inner.sorted_ids[:cap] = torch.where(valid, pos, (1 << 24) | cap).to(torch.int32)
+        inner.sorted_expert_ids[:cap // U] = pl["block_expert"]
+        inner.num_valid_ids[:] = rows.to(torch.int32)
+        row_dst = torch.where(valid, self._peer_ptrs[pl["src"].clamp(min=0)] + self._off_back
+                              + pl["src_row"] * (H * 2), 0)
+        base_ptr = self.peers.local.data_ptr()
+        inner.experts_forward_sorted(base_ptr + self._off_xs, base_ptr + self._off_xsc, cap, cap // U,
+                                     self._stream(), row_dst)
+        self.peer_rendezvous()
 
     def local_experts_direct(self, dp: DirectPlan) -> None:
         inner, dev = self.inner, self.dev

@@ -173,11 +173,16 @@ int flymoe_moe_gemm2_scatter_rows(const uint64_t* row_dst, const void* a2, const
  * into this process, peer access enabled), chosen so that a row lands at its final position
  * of the receiver's block-padded sorted layout; dst_x addresses must be 16-byte aligned.
  * Rows with ids outside [0, T) x [0, topk) or experts outside [0, experts) are skipped.
+ * Optional bound for callers that size nothing on the host: with pos_base != NULL, row r
+ * of expert e is dropped -- and bit 1 of the device status word raised
+ * (flymoe_device_status) -- when pos_base[e] + r >= pos_limit, i.e. when it would fall
+ * outside the receiver's buffer of pos_limit rows.
  * The reference has no counterpart (no dispatch/combine). */
 int flymoe_dispatch_rows(const void* x, const float* x_scale, const int32_t* sorted_ids,
                          const int32_t* sorted_expert_ids, const int32_t* num_valid_ids,
-                         const int64_t* dst_x, const int64_t* dst_scale, int num_tokens, int topk,
-                         int model_dim, int experts, int max_rows, void* stream);
+                         const int64_t* dst_x, const int64_t* dst_scale, const int64_t* pos_base,
+                         int64_t pos_limit, int num_tokens, int topk, int model_dim, int experts,
+                         int max_rows, void* stream);
 
 /* Caps the persistent grid of the two GEMM stages at max_ctas CTAs (0 restores one CTA per SM).
  * Process-wide.  For callers that run communication kernels next to the GEMMs (the

@@ -44,7 +44,7 @@ def test_c_abi_rejects_bad_arguments_without_launching(lib):
     rc = lib.flymoe_quant_act_1x128(None, 2, None, None, 0, 4, 100, None)
     assert rc == -1
     # the expert-parallel entry points
-    rc = lib.flymoe_dispatch_rows(None, None, None, None, None, None, None, 4, 2, 256, 8, 8, None)
+    rc = lib.flymoe_dispatch_rows(None, None, None, None, None, None, None, None, 0, 4, 2, 256, 8, 8, None)
     assert rc == -1 and b"null pointer" in lib.flymoe_last_error()
     rc = lib.flymoe_moe_gemm2_scatter_rows(None, None, None, 0, None, None, None, None, None, None,
                                            4, 256, 128, 1, 2, 1, 128, 0, 2, 2, 2, None)

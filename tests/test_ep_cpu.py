@@ -122,6 +122,28 @@ class FakeDirectOps(FakeFusedOps):
             pos += n
 
 
+class FakeDevicePlanOps(FakeDirectOps):
+    """The step without a host round trip: the plan is ``plan_direct_tensors`` output."""
+    device_plan = True
+
+    def run_direct_on_device(self, xq, xs, s_ids, s_eids, counts, rank, tokens):
+        per = E // dist.get_world_size()
+        pl = ep.plan_direct_tensors(counts, rank, per, self.tile_m, self.CAP)
+        for i in range(tokens * K):
+            e, tok = int(s_eids[i]), int(s_ids[i]) & 0xFFFFFF
+            pos = int(pl["pos_base"][e]) + i
+            self.xs_shared[e // per, pos] = xq[tok]
+            self.xsc_shared[e // per, pos] = xs[tok]
+        dist.barrier()
+        for pos in range(int(pl["padded_rows"])):
+            src = int(pl["src"][pos])
+            if src >= 0:
+                e = rank * per + int(pl["block_expert"][pos // self.tile_m])
+                y = self.xs_shared[rank, pos].float() * self.xsc_shared[rank, pos].mean() * (e + 1.0)
+                self.shared[src, int(pl["src_row"][pos])] = y
+        dist.barrier()
+
+
 def _inputs(rank):
     g = torch.Generator().manual_seed(100 + rank)
     logits = torch.randn((T, E), generator=g)
@@ -136,7 +158,7 @@ def _worker(rank, world, port, chunks, q, shared=None, direct=None):
     try:
         logits, xq, xs = _inputs(rank)
         ops = (FakeOps() if shared is None else FakeFusedOps(shared) if direct is None
-               else FakeDirectOps(shared, *direct))
+               else (FakeDevicePlanOps if len(direct) == 3 else FakeDirectOps)(shared, *direct[:2]))
         layer = ep.ExpertParallelMoE(ops, E, K, H, chunks=chunks)
         out = layer(logits, xq, xs)
         if shared is not None:                      # a second step reuses the peers' buffers
@@ -204,8 +226,8 @@ def test_fused_combine_addresses_on_cpu_ranks(world):
         assert counts_ok and transposed_ok
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_direct_dispatch_layout_on_cpu_ranks(world):
+@pytest.mark.parametrize("world,device_plan", [(2, False), (4, False), (2, True), (4, True)])
+def test_direct_dispatch_layout_on_cpu_ranks(world, device_plan):
     """Rows stored by their senders at plan_direct's positions are found by the receivers' segment
     lists, grouped by expert in whole row blocks; outputs return to the owners' send-order slots."""
     ctx = mp.get_context("spawn")
@@ -214,7 +236,8 @@ def test_direct_dispatch_layout_on_cpu_ranks(world):
     shared = torch.full((world, T * K, H), float("nan")).share_memory_()
     xs_sh = torch.zeros((world, FakeDirectOps.CAP, H), dtype=torch.uint8).share_memory_()
     xsc_sh = torch.zeros((world, FakeDirectOps.CAP, H // 128)).share_memory_()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, 1, q, shared, (xs_sh, xsc_sh))) for r in range(world)]
+    extra = (xs_sh, xsc_sh, True) if device_plan else (xs_sh, xsc_sh)
+    procs = [ctx.Process(target=_worker, args=(r, world, port, 1, q, shared, extra)) for r in range(world)]
     for p in procs:
         p.start()
     res = [q.get(timeout=120) for _ in range(world)]
@@ -256,6 +279,17 @@ def test_plan_direct_positions_and_segments():
                 assert s_ < 0 or lists[s_][i] == d * per + el
         assert p.max_padded_rows == max(q.padded_rows for q in plans)
         assert all(plans[s_].send_counts[d] == p.recv_counts[s_] for s_ in range(world))
+        # the tensor-operation planner (what runs on the GPU without a host round trip) agrees row by row
+        cap = p.max_padded_rows + 3 * unit
+        t = ep.plan_direct_tensors(torch.from_numpy(counts), d, per, unit, cap)
+        assert t["pos_base"].tolist() == p.pos_base.tolist()
+        assert int(t["padded_rows"]) == p.padded_rows and int(t["rows_in"]) == p.rows_in
+        assert int(t["max_padded_rows"]) == p.max_padded_rows
+        want_src = np.concatenate([bufs[d][:, 0], np.full(cap - p.padded_rows, -1)])
+        assert t["src"].tolist() == want_src.tolist()
+        real = want_src >= 0
+        assert t["src_row"].numpy()[real].tolist() == bufs[d][:, 1][real[:p.padded_rows]].tolist()
+        assert t["block_expert"][:len(p.block_expert)].tolist() == p.block_expert.tolist()
 
 
 def test_split_counts_and_checks():

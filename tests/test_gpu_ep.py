@@ -63,7 +63,7 @@ def _run(rank, world, routing, chunks, q, fused, direct, dev):
     xq, xs = xq_c.to(dev), xs_c.to(dev)
     ops = CudaOps(w1q[sl].contiguous(), w1s[sl].contiguous(), w2q[sl].contiguous(), w2s[sl].contiguous(),
                   E, k, T, tile_m=128, headroom=float(world) if direct else 1.0, chunks=chunks,
-                  fused_combine=fused, direct_dispatch=direct)
+                  fused_combine=fused, direct_dispatch=direct, device_plan=world in (1, 4))
     layer = ExpertParallelMoE(ops, E, k, H, chunks=chunks)
     out = layer(logits, xq, xs).clone()
     out2 = layer(logits, xq, xs).clone()                                     # buffers are reused
@@ -114,7 +114,8 @@ def test_fused_combine_matches_single_gpu(world, routing, direct):
     GEMM epilogue, no combine all-to-all); with ``direct`` the dispatch, too, is peer stores, into the
     owners' stage-1 operand buffers at final sorted positions.  Same bits as the single-GPU layer,
     twice in a row.  The one-rank cases run the same kernels and bookkeeping with every row staying
-    on the GPU, so a single-GPU box covers them too."""
+    on the GPU, so a single-GPU box covers them too.  The 1- and 4-rank direct cases plan on the device
+    (no host round trip in the step), the others on the host (capacity checked with an exception)."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs, found {torch.cuda.device_count()}")
     ctx = mp.get_context("spawn")
