@@ -53,7 +53,7 @@ dispatch_rows_kernel(const uint4* __restrict__ x, const float* __restrict__ x_sc
     const int t = id_token(id), s = id_slot(id);
     if (t >= num_tokens || s >= topk || e < 0 || e >= experts) continue;
     if (pos_base != nullptr && __ldg(pos_base + e) + r >= pos_limit) {   // would fall outside the receiver's buffer
-      if (lane == 0) atomicOr(status, 2);
+      if (lane == 0) atomicCAS(status, 0, 16);
       continue;
     }
     uint4* dx = reinterpret_cast<uint4*>(__ldg(dst_x + e) + (long long)r * row_vec * 16);

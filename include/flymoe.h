@@ -174,7 +174,7 @@ int flymoe_moe_gemm2_scatter_rows(const uint64_t* row_dst, const void* a2, const
  * of the receiver's block-padded sorted layout; dst_x addresses must be 16-byte aligned.
  * Rows with ids outside [0, T) x [0, topk) or experts outside [0, experts) are skipped.
  * Optional bound for callers that size nothing on the host: with pos_base != NULL, row r
- * of expert e is dropped -- and bit 1 of the device status word raised
+ * of expert e is dropped -- and the device status word set to 16
  * (flymoe_device_status) -- when pos_base[e] + r >= pos_limit, i.e. when it would fall
  * outside the receiver's buffer of pos_limit rows.
  * The reference has no counterpart (no dispatch/combine). */
