@@ -360,12 +360,13 @@ class CudaOps:
         ws = int(self.lib.flymoe_moe_sorting_workspace_elems(tc, experts, topk, 1))
         self.ws = torch.empty(max(ws, 1), dtype=i32, device=dev)
         self.chunk_bufs = []
+        packed = 0 if direct_dispatch else pc              # direct dispatch stores rows at the receiver: no send buffers
         for _ in bounds:                                   # buffers that must outlive their chunk's collectives
             self.chunk_bufs.append({
                 "s_ids": torch.empty(cap, dtype=i32, device=dev), "s_w": torch.empty(cap, dtype=f32, device=dev),
                 "s_eids": torch.empty(cap, dtype=i32, device=dev), "nvalid": torch.empty(2, dtype=i32, device=dev),
-                "send_x": torch.empty((pc, self.H), dtype=torch.uint8, device=dev),
-                "send_s": torch.empty((pc, self.H // 128), dtype=f32, device=dev),
+                "send_x": torch.empty((packed, self.H), dtype=torch.uint8, device=dev),
+                "send_s": torch.empty((packed, self.H // 128), dtype=f32, device=dev),
                 "inverse": torch.empty(pc, dtype=i32, device=dev), "y": None})
         self.headroom = headroom
         self.inner = None
