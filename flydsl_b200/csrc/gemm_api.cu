@@ -172,3 +172,83 @@ extern "C" int flymoe_moe_gemm2_scatter_rows(const uint64_t* row_dst, const void
                     size_expert_ids, experts, topk, tile_m, doweight, out_dtype, 0, a_layout, a_scale_layout,
                     FLYMOE_IMPL_TCGEN05, stream);
 }
+
+// ---------------------------------------------------------------------------------------------
+// Dense block-scaled GEMM: the stage-2 kernel with one expert, identity routing and plain stores.
+namespace flymoe {
+__global__ void dense_routing_kernel(int* __restrict__ sorted_ids, int* __restrict__ sorted_expert_ids,
+                                     int* __restrict__ num_valid_ids, int m, int rows_padded, int blocks) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < rows_padded) sorted_ids[i] = i < m ? i : ((1 << 24) | m);   // slot 0 of "token" i; pad id beyond M
+  if (i < blocks) sorted_expert_ids[i] = 0;
+  if (i == 0) { num_valid_ids[0] = rows_padded; num_valid_ids[1] = m; }
+}
+}  // namespace flymoe
+
+extern "C" int64_t flymoe_blockscale_gemm_workspace_elems(int m, int tile_m) {
+  if (m <= 0 || tile_m <= 0) return 0;
+  const int64_t blocks = (int64_t(m) + tile_m - 1) / tile_m;
+  return blocks * tile_m + blocks + 2;
+}
+
+extern "C" int flymoe_blockscale_gemm(void* c, const void* a, const float* scale_a, int64_t sa_stride,
+                                      const void* b, const float* scale_b, int32_t* workspace,
+                                      int64_t workspace_elems, int m, int n, int k, int tile_m, int out_dtype,
+                                      void* stream) {
+  using namespace flymoe;
+  FLYMOE_REQUIRE(m >= 0 && m < (1 << 24), "blockscale_gemm: M out of range");
+  FLYMOE_REQUIRE(n > 0 && n % 128 == 0, "blockscale_gemm: N must be a positive multiple of 128");
+  FLYMOE_REQUIRE(k > 0 && k % 128 == 0, "blockscale_gemm: K must be a positive multiple of 128");
+  FLYMOE_REQUIRE(tile_m == 16 || tile_m == 32 || tile_m == 64 || tile_m == 128,
+                 "blockscale_gemm: tile_m must be 16, 32, 64 or 128");
+  FLYMOE_REQUIRE(out_dtype == FLYMOE_F16 || out_dtype == FLYMOE_BF16, "blockscale_gemm: out_dtype must be F16 or BF16");
+  if (m == 0) return FLYMOE_OK;
+  FLYMOE_REQUIRE(c && a && scale_a && b && scale_b && workspace, "blockscale_gemm: null pointer");
+  FLYMOE_REQUIRE(aligned16(c) && aligned16(a) && aligned16(b), "blockscale_gemm: c/a/b must be 16-byte aligned");
+  FLYMOE_REQUIRE(sa_stride >= m, "blockscale_gemm: sa_stride smaller than M");
+  FLYMOE_REQUIRE(workspace_elems >= flymoe_blockscale_gemm_workspace_elems(m, tile_m),
+                 "blockscale_gemm: workspace too small");
+  int* status = device_status_ptr();
+  FLYMOE_REQUIRE(status != nullptr, "blockscale_gemm: no CUDA device");
+  const int blocks = (m + tile_m - 1) / tile_m;
+  const int rows_padded = blocks * tile_m;
+  int* sorted_ids = workspace;
+  int* sorted_expert_ids = workspace + rows_padded;
+  int* num_valid_ids = sorted_expert_ids + blocks;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  dense_routing_kernel<<<(rows_padded + 255) / 256, 256, 0, s>>>(sorted_ids, sorted_expert_ids, num_valid_ids, m,
+                                                                 rows_padded, blocks);
+  FLYMOE_CUDA_CHECK(cudaGetLastError());
+
+  GemmArgs g;
+  g.a = static_cast<const uint8_t*>(a);
+  g.scale_a = scale_a;
+  g.sa_stride = sa_stride;
+  g.sa_row_stride = 1;
+  g.a_layout = FLYMOE_ROWS_SORTED;
+  g.a_scale_layout = FLYMOE_ROWS_SORTED;
+  g.a_rows = m;                       // rows beyond M are filled with zeros by the TMA unit, never read from memory
+  g.w = static_cast<const uint8_t*>(b);
+  g.scale_w = scale_b;
+  g.sorted_ids = sorted_ids;
+  g.sorted_expert_ids = sorted_expert_ids;
+  g.sorted_weights = nullptr;
+  g.num_valid_ids = num_valid_ids;
+  g.out = c;
+  g.out_scale = nullptr;
+  g.out_scale_stride = 0;
+  g.out_dtype = out_dtype;
+  g.out_layout = FLYMOE_ROWS_BY_PAIR;
+  g.accumulate = 0;
+  g.row_dst = nullptr;
+  g.doweight = 0;
+  g.num_tokens = m;
+  g.topk = 1;
+  g.experts = 1;
+  g.n_dim = n;
+  g.k_dim = k;
+  g.size_expert_ids = blocks;
+  g.tile_m = tile_m;
+  g.status = status;
+  return launch_gemm_sm100(2, g, s);
+}

@@ -34,6 +34,7 @@ from __future__ import annotations
 
 import functools
 import logging
+import weakref
 from collections import OrderedDict
 
 import torch
@@ -74,13 +75,16 @@ def shuffle_weight(w: torch.Tensor, rows: int, cols: int, stream=None) -> torch.
 def _plain_weight(w: torch.Tensor, rows: int, cols: int, layout: str, stream) -> torch.Tensor:
     if layout == "plain":
         return w
+    # An entry is only valid for the allocation it was made from: a freed weight's address is reused
+    # by the allocator, so the storage object itself (weakly referenced) is part of the check.
+    storage = w.untyped_storage()
     key = (w.data_ptr(), w.numel(), w.device.index, rows, cols)
     hit = _plain_cache.get(key)
-    if hit is not None and hit[0] == w._version:
+    if hit is not None and hit[0] == w._version and hit[2]() is storage:
         _plain_cache.move_to_end(key)
         return hit[1]
     plain = unshuffle_weight(w, rows, cols, stream)
-    _plain_cache[key] = (w._version, plain)
+    _plain_cache[key] = (w._version, plain, weakref.ref(storage))
     while len(_plain_cache) > _PLAIN_CACHE_MAX:
         _plain_cache.popitem(last=False)
     return plain

@@ -184,6 +184,20 @@ int flymoe_dispatch_rows(const void* x, const float* x_scale, const int32_t* sor
                          int64_t pos_limit, int num_tokens, int topk, int model_dim, int experts,
                          int max_rows, void* stream);
 
+/* Dense block-scaled FP8 GEMM  c[M,N] = (a . b^T) with per-1x128 activation scales and
+ * per-128x128 weight scales -- the stage-2 kernel run with one expert and identity routing.
+ * Replaces kernels/blockscale_preshuffle_gemm.py:32-45 (builder) and the launcher :865-901.
+ * a e4m3 [M,K]; scale_a f32 [K/128, sa_stride] (the reference's transposed layout,
+ * sa_stride >= M); b e4m3 [N,K] row-major; scale_b f32 [N/128, K/128]; c [M,N] of out_dtype
+ * (F16/BF16).  N and K must be multiples of 128 (the reference also accepts N = 64 mod 128).
+ * workspace: flymoe_blockscale_gemm_workspace_elems(M, tile_m) int32, rewritten by every
+ * call (the routing arrays of the grouped kernel); tile_m 16/32/64/128. */
+int64_t flymoe_blockscale_gemm_workspace_elems(int m, int tile_m);
+int flymoe_blockscale_gemm(void* c, const void* a, const float* scale_a, int64_t sa_stride,
+                           const void* b, const float* scale_b, int32_t* workspace,
+                           int64_t workspace_elems, int m, int n, int k, int tile_m, int out_dtype,
+                           void* stream);
+
 /* Caps the persistent grid of the two GEMM stages at max_ctas CTAs (0 restores one CTA per SM).
  * Process-wide.  For callers that run communication kernels next to the GEMMs (the
  * expert-parallel layer); the reference has no counterpart (its grid is one CTA per tile,

@@ -25,6 +25,7 @@ Reference locations each function follows (paths inside the reference project):
 * requant         tests/kernels/test_moe_blockscale.py:447-452
 * stage 2         tests/kernels/test_moe_blockscale.py:115-150
 * top-k reduce    tests/kernels/test_moe_reduce.py:88-93
+* dense GEMM      tests/kernels/test_blockscale_preshuffle_gemm.py:101-125
 
 Differences from the reference text, all value-preserving: weights are
 dequantised one expert at a time (the reference expands every expert to fp32
@@ -244,6 +245,18 @@ def moe_layer(logits, xq, x_scale, w1q, w1_scale, w2q, w2_scale, topk: int,
     o2 = stage2(a2q, a2s, w2q, w2_scale, idx, w, H)
     return {"topk_weights": w, "topk_ids": idx, "tei": tei, "out1": o1,
             "a2q": a2q, "a2_scale": a2s, "out": o2.to(out_dtype), "out_f32": o2}
+
+
+# --------------------------------------------------------------------------- dense GEMM
+def blockscale_gemm(xq: torch.Tensor, x_scale: torch.Tensor, wq: torch.Tensor, w_scale: torch.Tensor,
+                    dtype=torch.float32) -> torch.Tensor:
+    """c = (xq * x_scale per 1x128) . (wq * w_scale per 128x128)^T in fp32, cast to ``dtype``.
+
+    xq e4m3 [M, K]; x_scale f32 [M, K/128]; wq e4m3 [N, K]; w_scale f32 [ceil(N/128), K/128]."""
+    x = _dequant_a(xq, x_scale)
+    n, k = wq.shape
+    w = wq.float() * w_scale.repeat_interleave(128, dim=0)[:n].repeat_interleave(128, dim=1)[:, :k]
+    return F.linear(x, w).to(dtype)
 
 
 # --------------------------------------------------------------------------- comparisons

@@ -189,6 +189,23 @@ def main() -> None:
 
     run_moe(wl.MoEConfig("mini", 16, 256, 128, 4, 2, 7), True, "moe_mini.npz")
     run_moe(wl.CONFIGS["c1"], False, "moe_c1.npz")
+
+    # ------------------------------------------------------------------ dense block-scaled GEMM
+    dense = lift(REF / "tests" / "kernels" / "test_blockscale_preshuffle_gemm.py", ["run_torch_blockscale"],
+                 {"torch": torch, "F": F, "BLOCK_SHAPE": (128, 128)})["run_torch_blockscale"]
+    out = {}
+    for i, (M, N, K) in enumerate([(5, 256, 384), (33, 384, 256), (1, 128, 128)]):
+        g = torch.Generator().manual_seed(40 + i)
+        # the reference test's own input recipe (test_blockscale_preshuffle_gemm.py:208-212)
+        x = (torch.rand((M, K), generator=g, dtype=torch.float32) / 10).to(torch.float16).to(FP8)
+        w = (torch.rand((N, K), generator=g, dtype=torch.float32) / 10).to(torch.float16).to(FP8)
+        x_scale = torch.rand((M, K // 128), generator=g, dtype=torch.float32)
+        w_scale = torch.rand((N // 128, K // 128), generator=g, dtype=torch.float32)
+        c = dense(x, w, x_scale, w_scale, dtype=torch.float32)
+        out.update({f"x{i}": u8(x), f"w{i}": u8(w), f"x_scale{i}": x_scale.numpy(), f"w_scale{i}": w_scale.numpy(),
+                    f"c{i}": c.numpy()})
+    out["n_cases"] = np.array([3], dtype=np.int32)
+    np.savez_compressed(HERE / "blockscale_gemm.npz", **out)
     for f in sorted(HERE.glob("*.npz")):
         print(f.name, f.stat().st_size)
 

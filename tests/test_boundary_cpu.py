@@ -8,6 +8,7 @@ import torch
 
 from flydsl_b200 import _lib
 from flydsl_b200.kernels import moe_blockscale_2stage as bs
+from flydsl_b200.kernels.blockscale_preshuffle_gemm import compile_blockscale_preshuffle_gemm
 from flydsl_b200.kernels import moe_sorting_kernel as srt
 from flydsl_b200.kernels import topk_gating_softmax_kernel as gat
 
@@ -103,3 +104,19 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "nope.so")
     with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
         _lib.load()
+
+
+def test_dense_blockscale_gemm_argument_rules():
+    kw = dict(M=64, K=2304, tile_m=64, tile_n=128, tile_k=128)
+    with pytest.raises(ValueError, match="multiple of 128"):
+        compile_blockscale_preshuffle_gemm(N=2112, **kw)           # the reference's N = 64 mod 128 case
+    with pytest.raises(ValueError, match="out_dtype"):
+        compile_blockscale_preshuffle_gemm(N=7168, out_dtype="f32", **kw)
+    with pytest.raises(ValueError, match="divisible by tile_k"):
+        compile_blockscale_preshuffle_gemm(N=7168, **{**kw, "tile_k": 256, "K": 2304 + 128})
+    exe = compile_blockscale_preshuffle_gemm(N=7168, **kw)
+    z = torch.zeros(16)
+    with pytest.raises(ValueError, match="CUDA tensor"):
+        exe(z, z, z, z, z, 4, 7168)
+    with pytest.raises(ValueError, match="built for N"):
+        exe(z, z, z, z, z, 4, 1024)

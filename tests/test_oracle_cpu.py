@@ -98,6 +98,18 @@ def test_moe_c1_matches_reference():
     _check_moe("moe_c1.npz", wl.CONFIGS["c1"], False)
 
 
+def test_dense_blockscale_gemm_matches_reference():
+    """oracle.blockscale_gemm against run_torch_blockscale of the reference's own test
+    (tests/kernels/test_blockscale_preshuffle_gemm.py:101-125), on that test's input recipe."""
+    g = hp.load("blockscale_gemm.npz")
+    for i in range(int(g["n_cases"][0])):
+        c = orc.blockscale_gemm(hp.fp8_from_u8(g[f"x{i}"]), torch.from_numpy(g[f"x_scale{i}"]),
+                                hp.fp8_from_u8(g[f"w{i}"]), torch.from_numpy(g[f"w_scale{i}"]))
+        want = torch.from_numpy(g[f"c{i}"])
+        assert c.shape == want.shape
+        assert torch.allclose(c, want, rtol=1e-5, atol=1e-6), float((c - want).abs().max())
+
+
 def test_ulp_distance():
     a = torch.tensor([0.0, 1.0, -1.0, 448.0]).to(hp.FP8)
     b = torch.tensor([0.0, 1.125, -0.9375, 416.0]).to(hp.FP8)
