@@ -227,13 +227,73 @@ def run_single_gpu(args, cfg) -> dict:
             "gpu_launches": args.steps * layer.kernel_launches(T)}
 
 
+def run_dense_gemm(args) -> dict:
+    """`--workload gemm`: the dense block-scaled FP8 GEMM (kernels.blockscale_preshuffle_gemm) on one
+    GPU.  Weight copies rotate so that every launch streams weights that are not in L2."""
+    from flydsl_b200 import _lib
+    from flydsl_b200.kernels.blockscale_preshuffle_gemm import compile_blockscale_preshuffle_gemm
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks = load_peaks()
+    M, N, K = args.tokens or 4096, args.gemm_n, args.gemm_k
+    tile_m = args.tile_m if args.tile_m else (16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128)
+    g = torch.Generator().manual_seed(5)
+    x = (torch.rand((M, K), generator=g) / 10).to(torch.float16).to(torch.float8_e4m3fn).to(dev)
+    sa = torch.rand((K // 128, M), generator=g).to(dev)
+    copies = max(2, int(2 * 126e6 // (N * K)) + 1)                       # > 2 x L2 of weights in rotation
+    ws = [(torch.rand((N, K), generator=g) / 10).to(torch.float16).to(torch.float8_e4m3fn).to(dev)
+          for _ in range(copies)]
+    sb = torch.rand((N // 128, K // 128), generator=g).to(dev)
+    c = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    exe = compile_blockscale_preshuffle_gemm(M=M, N=N, K=K, tile_m=tile_m, tile_n=128, tile_k=128, w_layout="plain")
+    stream = torch.cuda.current_stream()
+    for i in range(args.warmup):
+        exe(c, x, ws[i % copies], sa, sb, M, N, stream)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(physical_gpu_index(0))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(args.steps):
+        exe(c, x, ws[i % copies], sa, sb, M, N, stream)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    if _lib.device_status() != 0:
+        raise RuntimeError("a kernel reported a device-side timeout")
+    ms = e0.elapsed_time(e1) / args.steps
+    flops = 2.0 * M * N * K
+    nbytes = M * K + N * K + M * N * 2 + (M * (K // 128) + (N // 128) * (K // 128)) * 4
+    tf, gbs = flops / (ms * 1e-3) / 1e12, nbytes / (ms * 1e-3) / 1e9
+    fp8_peak = 2.0 * peaks["bf16_tflops"]
+    t_tensor, t_hbm = flops / (fp8_peak * 1e12), nbytes / (peaks["hbm_gbs"] * 1e9)
+    bound = "tensor" if t_tensor >= t_hbm else "hbm"
+    return {"metric": "fp8_blockscale_gemm_tflops", "value": round(tf, 2), "unit": UNIT, "n_gpus": 1,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate and scales)",
+            "data": "synthetic",
+            "config": {"workload": f"dense-gemm-M{M}-N{N}-K{K}", "tile_m": tile_m,
+                       "l2_policy": f"{copies} weight copies in rotation ({copies * N * K / 1e6:.0f} MB > 2 x L2)"},
+            "roofline": {"kernel": "moe_gemm_sm100_kernel<2> (one expert, identity routing)", "bound": bound,
+                         "achieved": round(tf if bound == "tensor" else gbs, 1),
+                         "peak": fp8_peak if bound == "tensor" else peaks["hbm_gbs"],
+                         "peak_source": peaks["source"] + (": 2 x burst cuBLAS bf16" if bound == "tensor" else ""),
+                         "unit": "TFLOP/s" if bound == "tensor" else "GB/s",
+                         "frac": round(max(t_tensor, t_hbm) * 1e3 / ms, 4), "traffic": None,
+                         "algorithmic_bytes_per_launch": int(nbytes), "gbs": round(gbs, 1)},
+            "cpu_baseline": None, "e2e": None, "clocks": clocks, "gpu_launches": 2 * args.steps}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, help="c1|c2|c3|c4a|c4b|c5a|c5b (default c4a, or c5a when --gpus > 1)")
+    ap.add_argument("--workload", default=None,
+                    help="c1|c2|c3|c4a|c4b|c5a|c5b (default c4a, or c5a when --gpus > 1); 'gemm' = the dense "
+                         "block-scaled GEMM with M = --tokens, --gemm-n, --gemm-k")
+    ap.add_argument("--gemm-n", type=int, default=7168)
+    ap.add_argument("--gemm-k", type=int, default=2304)
     ap.add_argument("--tokens", type=int, default=None, help="override the token count (c2 sweep)")
     ap.add_argument("--experts", type=int, default=None, help="override the expert count (small profiling cases)")
     ap.add_argument("--tile-m", type=int, default=0,
@@ -252,6 +312,10 @@ def main() -> None:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     name = args.workload or ("c4a" if args.gpus == 1 else "c5a")
+    if name == "gemm":
+        if rank == 0:
+            print(json.dumps(run_dense_gemm(args)), flush=True)
+        return
     cfg = wl.CONFIGS[name]
     if args.tokens is not None:
         cfg = cfg.with_tokens(args.tokens)
