@@ -197,7 +197,7 @@ extern "C" int flymoe_blockscale_gemm(void* c, const void* a, const float* scale
                                       void* stream) {
   using namespace flymoe;
   FLYMOE_REQUIRE(m >= 0 && m < (1 << 24), "blockscale_gemm: M out of range");
-  FLYMOE_REQUIRE(n > 0 && n % 128 == 0, "blockscale_gemm: N must be a positive multiple of 128");
+  FLYMOE_REQUIRE(n > 0 && n % 64 == 0, "blockscale_gemm: N must be a positive multiple of 64");
   FLYMOE_REQUIRE(k > 0 && k % 128 == 0, "blockscale_gemm: K must be a positive multiple of 128");
   FLYMOE_REQUIRE(tile_m == 16 || tile_m == 32 || tile_m == 64 || tile_m == 128,
                  "blockscale_gemm: tile_m must be 16, 32, 64 or 128");

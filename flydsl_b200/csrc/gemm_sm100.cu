@@ -459,13 +459,15 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       constexpr uint32_t kSlotBytes = STAGE == 1 ? 64u : 256u;
       const bool bf = a.out_dtype == FLYMOE_BF16;
       for (int t = blockIdx.x; t < sched.total && ok; t += gridDim.x) {
-        const int e = e_next;
+        const int e = e_next, n = n_next;
         if (t + int(gridDim.x) < sched.total) {
           sched.decode(t + gridDim.x, mb_next, n_next);
           e_next = __ldg(a.sorted_expert_ids + mb_next);
         }
         if (e < 0 || e >= a.experts) continue;
         if (!mbar_wait(smem_u32(&ctrl->stg_full), it & 1, abort_flag, a.status, 6, 64)) { ok = false; break; }
+        // stage 2 with n_dim = 64 mod 128 (dense GEMM only): the tile's last segment holds 64 columns
+        const int cols_left = STAGE == 2 ? a.n_dim - n * BN : 0;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const int sl = i * 32 + lane;
@@ -473,9 +475,10 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           if (dst != 0ull) {
             const uint32_t sp = smem_u32(staging + size_t(sl) * Staging<STAGE>::stride);
             void* gp = reinterpret_cast<void*>(dst);
-            if (STAGE == 1 || !a.accumulate) bulk_store(gp, sp, kSlotBytes);
-            else if (bf) bulk_reduce_add_bf16(gp, sp, kSlotBytes);
-            else bulk_reduce_add_f16(gp, sp, kSlotBytes);
+            const uint32_t bytes = (STAGE == 2 && cols_left - (sl >> 7) * 128 < 128) ? kSlotBytes / 2 : kSlotBytes;
+            if (STAGE == 1 || !a.accumulate) bulk_store(gp, sp, bytes);
+            else if (bf) bulk_reduce_add_bf16(gp, sp, bytes);
+            else bulk_reduce_add_f16(gp, sp, bytes);
           }
         }
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");

@@ -7,12 +7,11 @@ Mirrors ``kernels/blockscale_preshuffle_gemm.py`` of the reference:
 Data contract (the reference's): ``a`` e4m3 [M, K]; ``scale_a`` fp32 stored transposed
 [K/128, M]; ``b`` e4m3 [N, K] in the 16x16 preshuffle order (tests/utils.py:76-96; converted to
 row-major once per weight tensor and cached) or row-major with ``w_layout="plain"``; ``scale_b``
-fp32 [N/128, K/128]; ``c`` [M, N] bf16/fp16.  ``c = sum_kb (a_kb . b_kb^T) * scale_a[kb, m] *
+fp32 [ceil(N/128), K/128]; ``c`` [M, N] bf16/fp16.  ``c = sum_kb (a_kb . b_kb^T) * scale_a[kb, m] *
 scale_b[n/128, kb]`` -- the arithmetic of MoE stage 2 without grouping, and it runs on the same
 tcgen05 kernel (one expert, identity routing).
 
-Differences: N must be a multiple of 128 (the reference also takes N = 64 mod 128, e.g. 2112);
-``tile_m`` must be 16/32/64/128 and is the only tile parameter that changes anything --
+Differences: N must be a multiple of 64 (covers the reference's 2112-column case); ``tile_m`` must be 16/32/64/128 and is the only tile parameter that changes anything --
 ``tile_n`` / ``tile_k`` are checked like the reference does and otherwise ignored, as are the AMD
 knobs ``use_cshuffle_epilog``, ``waves_per_eu`` and ``use_async_copy``.
 """
@@ -56,8 +55,8 @@ def compile_blockscale_preshuffle_gemm(*, M: int, N: int, K: int, tile_m: int, t
         raise ValueError(f"tile_k_bytes must be divisible by 64, got {tile_k}")
     if scale_block_k != 128:
         raise ValueError(f"scale_block_k must be 128, got {scale_block_k}")
-    if N % 128 != 0:
-        raise ValueError(f"N ({N}) must be a multiple of 128 on this implementation")
+    if N % 64 != 0:
+        raise ValueError(f"N ({N}) must be a multiple of 64 on this implementation")
     if tile_m not in (16, 32, 64, 128):
         raise ValueError(f"tile_m must be one of (16, 32, 64, 128), got {tile_m}")
     if w_layout not in ("preshuffle16x16", "plain"):
@@ -76,7 +75,7 @@ def compile_blockscale_preshuffle_gemm(*, M: int, N: int, K: int, tile_m: int, t
         _lib.require_cuda("arg_a", arg_a, _FP8_DTYPES, m * K)
         _lib.require_cuda("arg_b", arg_b, _FP8_DTYPES, N * K)
         _lib.require_cuda("arg_scale_a", arg_scale_a, (torch.float32,), (K // 128) * m)
-        _lib.require_cuda("arg_scale_b", arg_scale_b, (torch.float32,), (N // 128) * (K // 128))
+        _lib.require_cuda("arg_scale_b", arg_scale_b, (torch.float32,), ((N + 127) // 128) * (K // 128))
         s = _lib.stream_handle(stream)
         b_plain = _plain_weight(arg_b, N, K, w_layout, stream)
         ws = _workspace(arg_a.device, int(lib.flymoe_blockscale_gemm_workspace_elems(m, tile_m)))

@@ -188,8 +188,8 @@ int flymoe_dispatch_rows(const void* x, const float* x_scale, const int32_t* sor
  * per-128x128 weight scales -- the stage-2 kernel run with one expert and identity routing.
  * Replaces kernels/blockscale_preshuffle_gemm.py:32-45 (builder) and the launcher :865-901.
  * a e4m3 [M,K]; scale_a f32 [K/128, sa_stride] (the reference's transposed layout,
- * sa_stride >= M); b e4m3 [N,K] row-major; scale_b f32 [N/128, K/128]; c [M,N] of out_dtype
- * (F16/BF16).  N and K must be multiples of 128 (the reference also accepts N = 64 mod 128).
+ * sa_stride >= M); b e4m3 [N,K] row-major; scale_b f32 [ceil(N/128), K/128]; c [M,N] of
+ * out_dtype (F16/BF16).  K must be a multiple of 128, N a multiple of 64.
  * workspace: flymoe_blockscale_gemm_workspace_elems(M, tile_m) int32, rewritten by every
  * call (the routing arrays of the grouped kernel); tile_m 16/32/64/128. */
 int64_t flymoe_blockscale_gemm_workspace_elems(int m, int tile_m);

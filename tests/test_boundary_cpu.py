@@ -108,8 +108,9 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
 
 def test_dense_blockscale_gemm_argument_rules():
     kw = dict(M=64, K=2304, tile_m=64, tile_n=128, tile_k=128)
-    with pytest.raises(ValueError, match="multiple of 128"):
-        compile_blockscale_preshuffle_gemm(N=2112, **kw)           # the reference's N = 64 mod 128 case
+    with pytest.raises(ValueError, match="multiple of 64"):
+        compile_blockscale_preshuffle_gemm(N=2080, **kw)
+    compile_blockscale_preshuffle_gemm(N=2112, **kw)               # the reference's N = 64 mod 128 case builds
     with pytest.raises(ValueError, match="out_dtype"):
         compile_blockscale_preshuffle_gemm(N=7168, out_dtype="f32", **kw)
     with pytest.raises(ValueError, match="divisible by tile_k"):

@@ -2,7 +2,8 @@
 
 Shapes and input recipe follow the reference's own test
 (tests/kernels/test_blockscale_preshuffle_gemm.py:128-152, :208-212): DeepSeek-V3 projection sizes
-with M from 1 to 1024, including M below the row block and M that is not a multiple of it.  Bar:
+with M from 1 to 1024, including M below the row block and M that is not a multiple of it, and the
+2112-column weight whose last scale block holds 64 columns.  Bar:
 the reference's rtol 1e-2 / atol 1e-2 on the 16-bit output."""
 import pytest
 import torch
@@ -25,11 +26,11 @@ def _case(M, N, K, seed):
     x = (torch.rand((M, K), generator=g) / 10).to(torch.float16).to(FP8)
     w = (torch.rand((N, K), generator=g) / 10).to(torch.float16).to(FP8)
     x_scale = torch.rand((M, K // 128), generator=g)
-    w_scale = torch.rand((N // 128, K // 128), generator=g)
+    w_scale = torch.rand(((N + 127) // 128, K // 128), generator=g)
     return x, w, x_scale, w_scale
 
 
-@pytest.mark.parametrize("N,K", [(7168, 2304), (3072, 1536), (1280, 7168), (1408, 512)])
+@pytest.mark.parametrize("N,K", [(7168, 2304), (2112, 7168), (3072, 1536), (1280, 7168), (1408, 512), (192, 256)])
 @pytest.mark.parametrize("M", [1, 7, 16, 33, 64, 256, 1024])
 def test_dense_blockscale_gemm_matches_oracle(M, N, K):
     dev = torch.device("cuda", 0)
