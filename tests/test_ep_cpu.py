@@ -189,7 +189,7 @@ def _free_port():
     return p
 
 
-@pytest.mark.parametrize("world,chunks", [(2, 1), (2, 3), (4, 2)])
+@pytest.mark.parametrize("world,chunks", [(2, 1), (2, 3), (4, 2), (8, 1)])
 def test_dispatch_combine_roundtrip_on_cpu_ranks(world, chunks):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
@@ -226,7 +226,7 @@ def test_fused_combine_addresses_on_cpu_ranks(world):
         assert counts_ok and transposed_ok
 
 
-@pytest.mark.parametrize("world,device_plan", [(2, False), (4, False), (2, True), (4, True)])
+@pytest.mark.parametrize("world,device_plan", [(2, False), (4, False), (2, True), (4, True), (8, True)])
 def test_direct_dispatch_layout_on_cpu_ranks(world, device_plan):
     """Rows stored by their senders at plan_direct's positions are found by the receivers' segment
     lists, grouped by expert in whole row blocks; outputs return to the owners' send-order slots."""
