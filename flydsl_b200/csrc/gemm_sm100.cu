@@ -9,6 +9,9 @@
 //               block into one of two 256-column TMEM accumulator stages, started from
 //               zero for every K block; tcgen05.commit releases the smem stage and
 //               publishes the TMEM stage.
+//   warp 2      store warp: sends the finished rows that the epilogue threads parked in
+//               shared-memory slots to global memory as bulk stores / bulk reductions
+//               (one per slot), so their issue cost is off the epilogue's path.
 //   warps 4-11  epilogue, two warpgroups: tcgen05.ld the fp32 partial sums of the K
 //               block and fold them into register accumulators with the product of the
 //               row's activation scale and the weight block's scale (the scales are
@@ -20,8 +23,10 @@
 // exchanged between the two warpgroups through shared memory).
 // Stage 2 tile: 256 rows of W2; each warpgroup takes 128 columns; every thread multiplies
 // its row by the routing weight, parks the 256 bytes in a private shared-memory slot and
-// adds them into out[token] with one bulk reduce (cp.reduce.async.bulk), or bulk-stores
-// per-pair rows for a later top-k reduce.
+// the store warp adds them into out[token] with one bulk reduce (cp.reduce.async.bulk),
+// bulk-stores per-pair rows for a later top-k reduce, or (ROW_DST instantiation) stores
+// each row to a caller-given address, which may be in a peer GPU's memory.  The same
+// kernel with one expert and identity routing is the dense block-scaled GEMM.
 //
 // Every wait is bounded: when one gives up it raises the CTA's abort flag and the
 // device status word, every role drains out, TMEM is released and the kernel returns.
