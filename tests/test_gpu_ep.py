@@ -62,8 +62,8 @@ def _run(rank, world, routing, chunks, q, fused, direct, dev):
     _x, xq_c, xs_c = wl.make_activations(cfg, rank=rank)
     xq, xs = xq_c.to(dev), xs_c.to(dev)
     ops = CudaOps(w1q[sl].contiguous(), w1s[sl].contiguous(), w2q[sl].contiguous(), w2s[sl].contiguous(),
-                  E, k, T, tile_m=128, headroom=float(world) if direct else 1.0, chunks=chunks,
-                  fused_combine=fused, direct_dispatch=direct, device_plan=world in (1, 4))
+                  E, k, T, tile_m=128, headroom=float(max(world, 2)) if direct else 1.0, chunks=chunks,
+                  fused_combine=fused, direct_dispatch=bool(direct), device_plan=direct == "device")
     layer = ExpertParallelMoE(ops, E, k, H, chunks=chunks)
     out = layer(logits, xq, xs).clone()
     out2 = layer(logits, xq, xs).clone()                                     # buffers are reused
@@ -106,16 +106,18 @@ def test_expert_parallel_matches_single_gpu(world, routing, chunks):
     assert total_rows == world * 300 * 4          # every dispatched row was received exactly once
 
 
-@pytest.mark.parametrize("world,routing,direct", [(1, "zipf", False), (1, "uniform", True),
-                                                  (2, "uniform", False), (2, "zipf", True), (4, "zipf", False),
-                                                  (4, "uniform", True), (8, "uniform", False), (8, "zipf", True)])
+@pytest.mark.parametrize("world,routing,direct", [(1, "zipf", False), (1, "uniform", "host"), (1, "zipf", "device"),
+                                                  (2, "uniform", False), (2, "zipf", "host"), (4, "zipf", False),
+                                                  (4, "uniform", "device"), (8, "uniform", False),
+                                                  (8, "zipf", "host")])
 def test_fused_combine_matches_single_gpu(world, routing, direct):
     """Stage 2 stores the expert outputs straight into the owning ranks' buffers (peer stores from the
     GEMM epilogue, no combine all-to-all); with ``direct`` the dispatch, too, is peer stores, into the
     owners' stage-1 operand buffers at final sorted positions.  Same bits as the single-GPU layer,
     twice in a row.  The one-rank cases run the same kernels and bookkeeping with every row staying
-    on the GPU, so a single-GPU box covers them too.  The 1- and 4-rank direct cases plan on the device
-    (no host round trip in the step), the others on the host (capacity checked with an exception)."""
+    on the GPU, so a single-GPU box covers them too.  ``direct`` = "host" plans the step on the host
+    (capacity checked with an exception), "device" with tensor operations on the GPU (no host round
+    trip in the step)."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs, found {torch.cuda.device_count()}")
     ctx = mp.get_context("spawn")
