@@ -18,12 +18,14 @@ LIB_NAME = "libflymoe_sm100.so"
 # FLYMOE_LIB overrides the path (e.g. an instrumented build of the same sources).
 LIB_PATH = Path(os.environ.get("FLYMOE_LIB", Path(__file__).resolve().parent / LIB_NAME))
 
-F32, F16, BF16, E4M3 = 0, 1, 2, 3
+F32, F16, BF16, E4M3, I8 = 0, 1, 2, 3, 4
+SCALE_BLOCK128, SCALE_PER_TOKEN = 0, 1
+STATUS_DISPATCH_OVERFLOW, STATUS_ROW_DST_MISALIGNED, STATUS_SELFTEST_TIMEOUT = 16, 17, 99
 ROWS_BY_TOKEN, ROWS_BY_PAIR, ROWS_SORTED = 0, 1, 2
 IMPL_TCGEN05, IMPL_SIMT = 0, 1
 
 DTYPE_CODE = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16,
-              torch.float8_e4m3fn: E4M3, torch.uint8: E4M3}
+              torch.float8_e4m3fn: E4M3, torch.uint8: E4M3, torch.int8: I8}
 
 _P = c_void_p
 _SIGNATURES = {
@@ -45,6 +47,13 @@ _SIGNATURES = {
     "flymoe_moe_gemm2": (c_int, [_P, _P, _P, c_int64, _P, _P, _P, _P, _P, _P,
                                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                  c_int, c_int, c_int, c_int, _P]),
+    "flymoe_moe_gemm1_pertoken": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P,
+                                          c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                          c_int, c_int, c_int, c_int, c_int, _P]),
+    "flymoe_moe_gemm2_pertoken": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P,
+                                          c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                          c_int, c_int, c_int, c_int, c_int, _P]),
+    "flymoe_selftest_bounded_wait": (c_int, [c_int64, _P]),
     "flymoe_moe_gemm2_scatter_rows": (c_int, [_P, _P, _P, c_int64, _P, _P, _P, _P, _P, _P,
                                               c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                               c_int, c_int, _P]),

@@ -14,24 +14,27 @@ static long long layout_rows(int layout, int num_tokens, int topk, int size_expe
   return (long long)size_expert_ids * tile_m;
 }
 
-extern "C" int flymoe_moe_gemm1(void* out, float* out_scale, int64_t out_scale_stride, const void* x,
-                                const float* scale_x, int64_t sx_stride, int64_t sx_row_stride, const void* w,
-                                const float* scale_w, const int32_t* sorted_ids,
-                                const int32_t* sorted_expert_ids, const float* sorted_weights,
-                                const int32_t* num_valid_ids, int num_tokens, int inter_dim,
-                                int model_dim, int size_expert_ids, int experts, int topk, int tile_m,
-                                int doweight, int out_dtype, int x_layout, int x_scale_layout,
-                                int out_layout, int impl, void* stream) {
+static int gemm1_impl(void* out, float* out_scale, int64_t out_scale_stride, const void* x, const float* scale_x,
+                      int64_t sx_stride, int64_t sx_row_stride, const void* w, const float* scale_w,
+                      const int32_t* sorted_ids, const int32_t* sorted_expert_ids, const float* sorted_weights,
+                      const int32_t* num_valid_ids, int num_tokens, int inter_dim, int model_dim,
+                      int size_expert_ids, int experts, int topk, int tile_m, int doweight, int out_dtype,
+                      int x_layout, int x_scale_layout, int out_layout, int impl, int scaling, int in_dtype,
+                      void* stream) {
+  const bool per_token = scaling == FLYMOE_SCALE_PER_TOKEN;
   FLYMOE_REQUIRE(num_tokens >= 0 && num_tokens < (1 << 24), "gemm1: num_tokens out of range");
   FLYMOE_REQUIRE(inter_dim > 0 && inter_dim % 128 == 0, "gemm1: inter_dim must be a positive multiple of 128");
   FLYMOE_REQUIRE(model_dim > 0 && model_dim % 128 == 0, "gemm1: model_dim must be a positive multiple of 128");
   FLYMOE_REQUIRE(experts >= 1 && topk >= 1 && topk <= 255, "gemm1: experts/topk out of range");
   FLYMOE_REQUIRE(tile_m >= 1 && size_expert_ids >= 0, "gemm1: tile_m/size_expert_ids out of range");
-  FLYMOE_REQUIRE(out_dtype == FLYMOE_F16 || out_dtype == FLYMOE_BF16 || out_dtype == FLYMOE_E4M3,
-                 "gemm1: out_dtype must be F16, BF16 or E4M3");
-  FLYMOE_REQUIRE(layout_ok(x_layout) && x_layout != FLYMOE_ROWS_BY_PAIR, "gemm1: x_layout must be BY_TOKEN or SORTED");
-  FLYMOE_REQUIRE(layout_ok(x_scale_layout) && x_scale_layout != FLYMOE_ROWS_BY_PAIR,
-                 "gemm1: x_scale_layout must be BY_TOKEN or SORTED");
+  FLYMOE_REQUIRE(out_dtype == FLYMOE_F16 || out_dtype == FLYMOE_BF16 || (out_dtype == FLYMOE_E4M3 && !per_token),
+                 "gemm1: out_dtype must be F16, BF16 or (block-scaled only) E4M3");
+  FLYMOE_REQUIRE(in_dtype == FLYMOE_E4M3 || (in_dtype == FLYMOE_I8 && per_token),
+                 "gemm1: in_dtype must be E4M3 or (per-token scaling only) I8");
+  FLYMOE_REQUIRE(layout_ok(x_layout) && (x_layout != FLYMOE_ROWS_BY_PAIR || per_token),
+                 "gemm1: x_layout must be BY_TOKEN or SORTED (BY_PAIR with per-token scaling)");
+  FLYMOE_REQUIRE(layout_ok(x_scale_layout) && (x_scale_layout != FLYMOE_ROWS_BY_PAIR || per_token),
+                 "gemm1: x_scale_layout must be BY_TOKEN or SORTED (BY_PAIR with per-token scaling)");
   FLYMOE_REQUIRE(out_layout == FLYMOE_ROWS_BY_PAIR || out_layout == FLYMOE_ROWS_SORTED,
                  "gemm1: out_layout must be BY_PAIR or SORTED");
   if (num_tokens == 0 || size_expert_ids == 0) return FLYMOE_OK;
@@ -40,9 +43,10 @@ extern "C" int flymoe_moe_gemm1(void* out, float* out_scale, int64_t out_scale_s
   FLYMOE_REQUIRE(!doweight || sorted_weights, "gemm1: doweight needs sorted_weights");
   FLYMOE_REQUIRE(out_dtype != FLYMOE_E4M3 || out_scale, "gemm1: e4m3 output needs out_scale");
   FLYMOE_REQUIRE(aligned16(out) && aligned16(x) && aligned16(w), "gemm1: out/x/w must be 16-byte aligned");
+  FLYMOE_REQUIRE(!per_token || aligned16(scale_w), "gemm1: per-row weight scales must be 16-byte aligned");
   const long long srows = layout_rows(x_scale_layout, num_tokens, topk, size_expert_ids, tile_m);
   FLYMOE_REQUIRE(sx_row_stride >= 1 && sx_stride >= 1, "gemm1: scale strides must be positive");
-  FLYMOE_REQUIRE(sx_row_stride != 1 || sx_stride >= srows || x_scale_layout == FLYMOE_ROWS_SORTED,
+  FLYMOE_REQUIRE(per_token || sx_row_stride != 1 || sx_stride >= srows || x_scale_layout == FLYMOE_ROWS_SORTED,
                  "gemm1: sx_stride smaller than row count");
   int* status = device_status_ptr();
   FLYMOE_REQUIRE(status != nullptr, "gemm1: no CUDA device");
@@ -67,7 +71,10 @@ extern "C" int flymoe_moe_gemm1(void* out, float* out_scale, int64_t out_scale_s
   a.out_dtype = out_dtype;
   a.out_layout = out_layout;
   a.accumulate = 0;
+  a.row_dst = nullptr;
   a.doweight = doweight;
+  a.scaling = scaling;
+  a.in_dtype = in_dtype;
   a.num_tokens = num_tokens;
   a.topk = topk;
   a.experts = experts;
@@ -83,13 +90,40 @@ extern "C" int flymoe_moe_gemm1(void* out, float* out_scale, int64_t out_scale_s
   return FLYMOE_ERR_INVALID_ARGUMENT;
 }
 
+extern "C" int flymoe_moe_gemm1(void* out, float* out_scale, int64_t out_scale_stride, const void* x,
+                                const float* scale_x, int64_t sx_stride, int64_t sx_row_stride, const void* w,
+                                const float* scale_w, const int32_t* sorted_ids,
+                                const int32_t* sorted_expert_ids, const float* sorted_weights,
+                                const int32_t* num_valid_ids, int num_tokens, int inter_dim,
+                                int model_dim, int size_expert_ids, int experts, int topk, int tile_m,
+                                int doweight, int out_dtype, int x_layout, int x_scale_layout,
+                                int out_layout, int impl, void* stream) {
+  return gemm1_impl(out, out_scale, out_scale_stride, x, scale_x, sx_stride, sx_row_stride, w, scale_w, sorted_ids,
+                    sorted_expert_ids, sorted_weights, num_valid_ids, num_tokens, inter_dim, model_dim,
+                    size_expert_ids, experts, topk, tile_m, doweight, out_dtype, x_layout, x_scale_layout,
+                    out_layout, impl, FLYMOE_SCALE_BLOCK128, FLYMOE_E4M3, stream);
+}
+
+extern "C" int flymoe_moe_gemm1_pertoken(void* out, const void* x, const float* scale_x, const void* w,
+                                         const float* scale_w, const int32_t* sorted_ids,
+                                         const int32_t* sorted_expert_ids, const float* sorted_weights,
+                                         const int32_t* num_valid_ids, int num_tokens, int inter_dim,
+                                         int model_dim, int size_expert_ids, int experts, int topk, int tile_m,
+                                         int doweight, int in_dtype, int out_dtype, int x_layout,
+                                         int x_scale_layout, int out_layout, int impl, void* stream) {
+  return gemm1_impl(out, nullptr, 0, x, scale_x, 1, 1, w, scale_w, sorted_ids, sorted_expert_ids, sorted_weights,
+                    num_valid_ids, num_tokens, inter_dim, model_dim, size_expert_ids, experts, topk, tile_m, doweight,
+                    out_dtype, x_layout, x_scale_layout, out_layout, impl, FLYMOE_SCALE_PER_TOKEN, in_dtype, stream);
+}
+
 static int gemm2_impl(void* out, const unsigned long long* row_dst, const void* a2, const float* scale_a,
                       int64_t sa_stride, const void* w, const float* scale_w, const int32_t* sorted_ids,
                       const int32_t* sorted_expert_ids, const float* sorted_weights,
                       const int32_t* num_valid_ids, int num_tokens, int model_dim,
                       int inter_dim, int size_expert_ids, int experts, int topk, int tile_m,
                       int doweight, int out_dtype, int accumulate, int a_layout,
-                      int a_scale_layout, int impl, void* stream) {
+                      int a_scale_layout, int impl, int scaling, int in_dtype, void* stream) {
+  const bool per_token = scaling == FLYMOE_SCALE_PER_TOKEN;
   FLYMOE_REQUIRE(num_tokens >= 0 && num_tokens < (1 << 24), "gemm2: num_tokens out of range");
   FLYMOE_REQUIRE(inter_dim > 0 && inter_dim % 128 == 0, "gemm2: inter_dim must be a positive multiple of 128");
   FLYMOE_REQUIRE(model_dim > 0 && model_dim % 128 == 0, "gemm2: model_dim must be a positive multiple of 128");
@@ -97,16 +131,19 @@ static int gemm2_impl(void* out, const unsigned long long* row_dst, const void* 
   FLYMOE_REQUIRE(tile_m >= 1 && size_expert_ids >= 0, "gemm2: tile_m/size_expert_ids out of range");
   FLYMOE_REQUIRE(out_dtype == FLYMOE_F16 || out_dtype == FLYMOE_BF16 || (out_dtype == FLYMOE_F32 && accumulate),
                  "gemm2: out_dtype must be F16 or BF16 (F32 only with accumulate)");
+  FLYMOE_REQUIRE(in_dtype == FLYMOE_E4M3 || (in_dtype == FLYMOE_I8 && per_token),
+                 "gemm2: in_dtype must be E4M3 or (per-token scaling only) I8");
   FLYMOE_REQUIRE((a_layout == FLYMOE_ROWS_BY_PAIR || a_layout == FLYMOE_ROWS_SORTED) &&
                      (a_scale_layout == FLYMOE_ROWS_BY_PAIR || a_scale_layout == FLYMOE_ROWS_SORTED),
                  "gemm2: a_layout/a_scale_layout must be BY_PAIR or SORTED");
   if (num_tokens == 0 || size_expert_ids == 0) return FLYMOE_OK;
   FLYMOE_REQUIRE((out || row_dst) && a2 && scale_a && w && scale_w && sorted_ids && sorted_expert_ids && num_valid_ids,
                  "gemm2: null pointer");
-  FLYMOE_REQUIRE(!row_dst || (!accumulate && out_dtype != FLYMOE_F32 && impl == FLYMOE_IMPL_TCGEN05),
-                 "gemm2: per-row destinations need accumulate == 0, a 16-bit out_dtype and the tcgen05 kernel");
+  FLYMOE_REQUIRE(!row_dst || (!accumulate && out_dtype != FLYMOE_F32 && impl == FLYMOE_IMPL_TCGEN05 && !per_token),
+                 "gemm2: per-row destinations need accumulate == 0, a 16-bit out_dtype and the block-scaled tcgen05 kernel");
   FLYMOE_REQUIRE(!doweight || sorted_weights, "gemm2: doweight needs sorted_weights");
   FLYMOE_REQUIRE(aligned16(out) && aligned16(a2) && aligned16(w), "gemm2: out/a2/w must be 16-byte aligned");
+  FLYMOE_REQUIRE(!per_token || aligned16(scale_w), "gemm2: per-row weight scales must be 16-byte aligned");
   int* status = device_status_ptr();
   FLYMOE_REQUIRE(status != nullptr, "gemm2: no CUDA device");
 
@@ -132,6 +169,8 @@ static int gemm2_impl(void* out, const unsigned long long* row_dst, const void* 
   a.accumulate = accumulate ? 1 : 0;
   a.row_dst = row_dst;
   a.doweight = doweight;
+  a.scaling = scaling;
+  a.in_dtype = in_dtype;
   a.num_tokens = num_tokens;
   a.topk = topk;
   a.experts = experts;
@@ -156,7 +195,19 @@ extern "C" int flymoe_moe_gemm2(void* out, const void* a2, const float* scale_a,
                                 int a_scale_layout, int impl, void* stream) {
   return gemm2_impl(out, nullptr, a2, scale_a, sa_stride, w, scale_w, sorted_ids, sorted_expert_ids, sorted_weights,
                     num_valid_ids, num_tokens, model_dim, inter_dim, size_expert_ids, experts, topk, tile_m, doweight,
-                    out_dtype, accumulate, a_layout, a_scale_layout, impl, stream);
+                    out_dtype, accumulate, a_layout, a_scale_layout, impl, FLYMOE_SCALE_BLOCK128, FLYMOE_E4M3, stream);
+}
+
+extern "C" int flymoe_moe_gemm2_pertoken(void* out, const void* a2, const float* scale_a, const void* w,
+                                         const float* scale_w, const int32_t* sorted_ids,
+                                         const int32_t* sorted_expert_ids, const float* sorted_weights,
+                                         const int32_t* num_valid_ids, int num_tokens, int model_dim,
+                                         int inter_dim, int size_expert_ids, int experts, int topk, int tile_m,
+                                         int doweight, int in_dtype, int out_dtype, int accumulate, int a_layout,
+                                         int a_scale_layout, int impl, void* stream) {
+  return gemm2_impl(out, nullptr, a2, scale_a, 1, w, scale_w, sorted_ids, sorted_expert_ids, sorted_weights,
+                    num_valid_ids, num_tokens, model_dim, inter_dim, size_expert_ids, experts, topk, tile_m, doweight,
+                    out_dtype, accumulate, a_layout, a_scale_layout, impl, FLYMOE_SCALE_PER_TOKEN, in_dtype, stream);
 }
 
 extern "C" int flymoe_moe_gemm2_scatter_rows(const uint64_t* row_dst, const void* a2, const float* scale_a,
@@ -170,7 +221,7 @@ extern "C" int flymoe_moe_gemm2_scatter_rows(const uint64_t* row_dst, const void
   return gemm2_impl(nullptr, reinterpret_cast<const unsigned long long*>(row_dst), a2, scale_a, sa_stride, w, scale_w,
                     sorted_ids, sorted_expert_ids, sorted_weights, num_valid_ids, num_tokens, model_dim, inter_dim,
                     size_expert_ids, experts, topk, tile_m, doweight, out_dtype, 0, a_layout, a_scale_layout,
-                    FLYMOE_IMPL_TCGEN05, stream);
+                    FLYMOE_IMPL_TCGEN05, FLYMOE_SCALE_BLOCK128, FLYMOE_E4M3, stream);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -242,6 +293,8 @@ extern "C" int flymoe_blockscale_gemm(void* c, const void* a, const float* scale
   g.accumulate = 0;
   g.row_dst = nullptr;
   g.doweight = 0;
+  g.scaling = FLYMOE_SCALE_BLOCK128;
+  g.in_dtype = FLYMOE_E4M3;
   g.num_tokens = m;
   g.topk = 1;
   g.experts = 1;

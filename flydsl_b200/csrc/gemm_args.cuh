@@ -32,6 +32,10 @@ struct GemmArgs {
   const unsigned long long* row_dst;   // stage 2, accumulate == 0, optional: byte address of output row t*k+s
                                        // (0 = drop the row); may point into a peer GPU's memory
   int doweight;
+  // FLYMOE_SCALE_BLOCK128: scale_a [k_dim/128, rows] (strided as above), scale_w [experts, wrows/128, k_dim/128];
+  // FLYMOE_SCALE_PER_TOKEN: scale_a [rows] (one per activation row), scale_w [experts, wrows] (one per weight row)
+  int scaling;
+  int in_dtype;                // FLYMOE_E4M3, or FLYMOE_I8 (per-token scaling only)
   // sizes
   int num_tokens, topk, experts;
   int n_dim;                   // stage 1: inter_dim; stage 2: model_dim

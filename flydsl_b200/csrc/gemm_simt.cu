@@ -10,10 +10,10 @@ namespace flymoe {
 constexpr int kSimtRows = 8;      // sorted rows processed per pass
 constexpr int kSimtCols = 128;    // output columns per block (= threads)
 
-__device__ __forceinline__ void cvt16(const uint4& v, float* f) {
+__device__ __forceinline__ void cvt16(const uint4& v, float* f, bool int8_ops) {
   const uint8_t* b = reinterpret_cast<const uint8_t*>(&v);
 #pragma unroll
-  for (int i = 0; i < 16; ++i) f[i] = fp8_e4m3_to_float(b[i]);
+  for (int i = 0; i < 16; ++i) f[i] = int8_ops ? float(int(static_cast<int8_t>(b[i]))) : fp8_e4m3_to_float(b[i]);
 }
 
 __device__ __forceinline__ long long src_row(int layout, int r, int t, int s, int topk) {
@@ -48,8 +48,11 @@ moe_gemm_simt_kernel(GemmArgs a) {
   const uint8_t* w0 = a.w + ((long long)e * wrows_per_expert + (col_ok ? col : 0)) * K;
   const uint8_t* w1 = STAGE == 1 ? w0 + (long long)a.n_dim * K : w0;
   const int nblk_per_expert = int(wrows_per_expert / 128);
+  const bool per_token = a.scaling == FLYMOE_SCALE_PER_TOKEN;   // one scale per activation row / weight row
+  const bool int8_ops = a.in_dtype == FLYMOE_I8;
   const float* sw0 = a.scale_w + ((long long)e * nblk_per_expert + (col_ok ? col : 0) / 128) * KB;
   const float* sw1 = STAGE == 1 ? sw0 + (long long)(a.n_dim / 128) * KB : sw0;
+  const float* swr = a.scale_w + (long long)e * wrows_per_expert + (col_ok ? col : 0);   // per-row weight scales
 
   for (int rb = 0; rb < a.tile_m; rb += kSimtRows) {
     int rt[kSimtRows], rs[kSimtRows];
@@ -98,25 +101,36 @@ moe_gemm_simt_kernel(GemmArgs a) {
         for (int kc = 0; kc < 8; ++kc) {
           const int koff = kb * 128 + kc * 16;
           float wf[NACC][16];
-          cvt16(__ldg(reinterpret_cast<const uint4*>(w0 + koff)), wf[0]);
-          if (NACC == 2) cvt16(__ldg(reinterpret_cast<const uint4*>(w1 + koff)), wf[NACC - 1]);
+          cvt16(__ldg(reinterpret_cast<const uint4*>(w0 + koff)), wf[0], int8_ops);
+          if (NACC == 2) cvt16(__ldg(reinterpret_cast<const uint4*>(w1 + koff)), wf[NACC - 1], int8_ops);
 #pragma unroll
           for (int i = 0; i < kSimtRows; ++i) {
             float xf[16];
-            cvt16(*reinterpret_cast<const uint4*>(xs + size_t(i) * K + koff), xf);
+            cvt16(*reinterpret_cast<const uint4*>(xs + size_t(i) * K + koff), xf, int8_ops);
 #pragma unroll
             for (int j = 0; j < NACC; ++j)
 #pragma unroll
               for (int q = 0; q < 16; ++q) part[j][i] = fmaf(xf[q], wf[j][q], part[j][i]);
           }
         }
-        const float s0 = __ldg(sw0 + kb);
-        const float s1 = __ldg(sw1 + kb);
+        const float s0 = per_token ? 1.f : __ldg(sw0 + kb);
+        const float s1 = per_token ? 1.f : __ldg(sw1 + kb);
 #pragma unroll
         for (int i = 0; i < kSimtRows; ++i) {
-          const float sa = rok[i] ? __ldg(a.scale_a + (long long)kb * a.sa_stride + sidx[i] * a.sa_row_stride) : 0.f;
+          const float sa = !rok[i] ? 0.f : per_token ? 1.f
+                         : __ldg(a.scale_a + (long long)kb * a.sa_stride + sidx[i] * a.sa_row_stride);
           acc[0][i] = fmaf(part[0][i], sa * s0, acc[0][i]);
           if (NACC == 2) acc[NACC - 1][i] = fmaf(part[NACC - 1][i], sa * s1, acc[NACC - 1][i]);
+        }
+      }
+      if (per_token) {
+        const float c0 = __ldg(swr);
+        const float c1 = STAGE == 1 ? __ldg(swr + a.n_dim) : c0;
+#pragma unroll
+        for (int i = 0; i < kSimtRows; ++i) {
+          const float sa = rok[i] ? __ldg(a.scale_a + sidx[i]) : 0.f;
+          acc[0][i] *= sa * c0;
+          if (NACC == 2) acc[NACC - 1][i] *= sa * c1;
         }
       }
     }

@@ -1,32 +1,40 @@
-// Grouped FP8 (e4m3) block-scaled GEMM for both MoE stages on sm_100a.
+// Grouped FP8 (e4m3) GEMM for both MoE stages on sm_100a.
 //
 // One persistent CTA per SM walks a static sequence of (sorted row block, N tile)
-// tiles.  Warp roles (384 threads):
+// tiles.  Warp roles (640 threads):
 //   warp 0      TMA producer: per 128-wide K block one A box (tile_m sorted rows x 128 B)
 //               and 256 weight rows x 128 B into a 4-deep (stage 2: 3-deep) shared-memory
 //               ring (128-byte swizzle, K-major).
-//   warp 1      MMA issuer: four tcgen05.mma (kind::f8f6f4, M=128, N=256, K=32) per K
-//               block into one of two 256-column TMEM accumulator stages, started from
-//               zero for every K block; tcgen05.commit releases the smem stage and
-//               publishes the TMEM stage.
+//   warp 1      MMA issuer: four tcgen05.mma (M=128, N=256, K=32) per K block into one of
+//               two 256-column TMEM accumulator stages; tcgen05.commit releases the smem
+//               stage and publishes the TMEM stage.
 //   warp 2      store warp: sends the finished rows that the epilogue threads parked in
-//               shared-memory slots to global memory as bulk stores / bulk reductions
-//               (one per slot), so their issue cost is off the epilogue's path.
-//   warps 4-11  epilogue, two warpgroups: tcgen05.ld the fp32 partial sums of the K
-//               block and fold them into register accumulators with the product of the
-//               row's activation scale and the weight block's scale (the scales are
-//               arbitrary fp32 per 128 K, so they cannot ride inside the MMA).
-//               Each thread owns one sorted row.
-// Stage 1 tile: 128 gate rows + 128 up rows of W1 (one quantisation group of the
-// output); each warpgroup takes 64 gate + 64 up columns, computes silu(gate)*up and
-// either stores f16/bf16 or requantises to e4m3 with the per-row 1x128 scale (row amax
-// exchanged between the two warpgroups through shared memory).
-// Stage 2 tile: 256 rows of W2; each warpgroup takes 128 columns; every thread multiplies
-// its row by the routing weight, parks the 256 bytes in a private shared-memory slot and
-// the store warp adds them into out[token] with one bulk reduce (cp.reduce.async.bulk),
-// bulk-stores per-pair rows for a later top-k reduce, or (ROW_DST instantiation) stores
-// each row to a caller-given address, which may be in a peer GPU's memory.  The same
-// kernel with one expert and identity routing is the dense block-scaled GEMM.
+//               the shared-memory staging tile to global memory as bulk stores / bulk
+//               reductions, one per row, so their issue cost is off the epilogue's path.
+//   warps 4-19  epilogue, four warpgroups.  Each thread owns one sorted row (its TMEM
+//               lane) and a 64-column slice of the tile, so four warps per scheduler
+//               partition cover each other's tcgen05.ld / mbarrier latency.
+//
+// Two scaling modes (template parameter SCALING):
+//   kScaleBlock128   activation scales per (row, 128 K), weight scales per 128x128 block.
+//               The scales are arbitrary fp32, so they cannot ride inside the MMA: every
+//               K block starts its TMEM stage from zero, and the epilogue folds the K
+//               block's partial sums into register accumulators with the product of the
+//               two scales (packed fma.rn.f32x2).
+//   kScalePerToken   one scale per activation row and one per weight row (output
+//               column): the MMA accumulates over the whole K range in TMEM and the
+//               epilogue drains each tile once.  fp8 e4m3 or int8 operands.
+//
+// Stage 1 tile: 128 gate rows + 128 up rows of W1 (one quantisation group of the output);
+// warpgroup w takes gate columns [32w, 32w+32) and the matching up columns, computes
+// silu(gate)*up and either stores f16/bf16 or requantises to e4m3 with the per-row 1x128
+// scale (row amax exchanged between the four warpgroups through shared memory).
+// Stage 2 tile: 256 rows of W2; warpgroup w takes columns [64w, 64w+64); every thread
+// multiplies its row by the routing weight and parks its 128 bytes in the row-major staging
+// tile; the store warp adds each 512-byte row into out[token] with one bulk reduce
+// (cp.reduce.async.bulk), bulk-stores per-pair rows for a later top-k reduce, or (ROW_DST
+// instantiation) stores each row to a caller-given address, which may be in a peer GPU's
+// memory.  The same kernel with one expert and identity routing is the dense block-scaled GEMM.
 //
 // Every wait is bounded: when one gives up it raises the CTA's abort flag and the
 // device status word, every role drains out, TMEM is released and the kernel returns.
@@ -47,23 +55,38 @@ constexpr int BK = 128;
 // at launch would otherwise run its whole tile list after the others have finished.
 static int g_cta_limit = 0;
 
+constexpr int kScaleBlock128 = 0;
+constexpr int kScalePerToken = 1;
+
 constexpr int kMaxStages = 4;
-// Depth of the shared-memory operand ring.  Stage 2 gives one slot up for a staging area from
-// which finished output rows leave by bulk reduce/store (measured: a 3-deep ring is as fast as 4).
+// Depth of the shared-memory operand ring.  Stage 2 gives one slot up for the staging tile
+// from which finished output rows leave by bulk reduce/store.
 template <int STAGE> struct RingDepth { static constexpr int value = STAGE == 1 ? 4 : 3; };
-// Per-epilogue-thread staging slot for finished output: stage 2 holds 256 B of 16-bit results,
-// stage 1 holds 64 e4m3 codes; 16 B of skew keep 16-byte shared-memory stores conflict-free.
+// Row-major staging tile for finished output: stage 1 holds the 128 e4m3 codes of one row's
+// quantisation group, stage 2 the row's 256 16-bit results; 16 B of skew per row keep the
+// 16-byte shared-memory stores of a warp (one row per lane) conflict-free.
 template <int STAGE> struct Staging {
-  static constexpr int stride = STAGE == 1 ? 80 : 272;
-  static constexpr int bytes = 256 * stride;
+  static constexpr int row_bytes = STAGE == 1 ? 128 : 512;
+  static constexpr int stride = row_bytes + 16;
+  static constexpr int bytes = BM * stride;
 };
 constexpr int kATileBytes = BM * BK;            // 16 KB
 constexpr int kBTileBytes = BN * BK;            // 32 KB
 constexpr int kStageBytes = kATileBytes + kBTileBytes;
 constexpr int kAccStages = 2;
 constexpr int kTmemCols = 512;
-constexpr int kNumThreads = 384;
-constexpr int kEpilogueWarps = 8;
+constexpr int kEpilogueGroups = 4;              // warpgroups, each on BN / 4 = 64 accumulator columns
+constexpr int kEpilogueWarps = 4 * kEpilogueGroups;
+constexpr int kNumThreads = 128 + 32 * kEpilogueWarps;   // 640
+constexpr int NACC = BN / kEpilogueGroups;      // fp32 accumulators per epilogue thread
+// Register re-split: 640 threads x 96 registers are allocated at launch; the producer warpgroup
+// drops to kRegsProducer and the four epilogue warpgroups rise to kRegsEpilogue.  The sum must not
+// exceed the launch allocation: a larger request would wait forever for registers nobody releases.
+constexpr int kRegsLaunch = 96;
+constexpr int kRegsProducer = 32;
+constexpr int kRegsEpilogue = 112;
+static_assert(128 * kRegsProducer + 32 * kEpilogueWarps * kRegsEpilogue <= kNumThreads * kRegsLaunch,
+              "setmaxnreg split exceeds the launch allocation");
 constexpr unsigned long long kWaitLimitNs = 4000000000ull;   // 4 s
 
 struct __align__(16) SmemCtrl {
@@ -72,42 +95,22 @@ struct __align__(16) SmemCtrl {
   unsigned long long tmem_full[kAccStages];
   unsigned long long tmem_empty[kAccStages];
   unsigned long long amax_bar[2];
-  unsigned long long stg_full;                  // epilogue warps -> store warp: slots and destinations written
-  unsigned long long stg_free;                  // store warp -> epilogue warps: slots have been read
-  unsigned long long stg_dst[256];              // per epilogue thread: global address of its row segment, 0 = none
+  unsigned long long stg_full;                  // epilogue warps -> store warp: staging rows and destinations written
+  unsigned long long stg_free;                  // store warp -> epilogue warps: the staging tile has been read
+  unsigned long long stg_dst[BM];               // per row of the tile: global address of its segment, 0 = none
   uint32_t tmem_base;
   int abort_flag;
-  float amax[2][2][BM];
+  float amax[2][kEpilogueGroups][BM];
 };
 template <int STAGE> constexpr size_t smem_bytes() {
   return size_t(RingDepth<STAGE>::value) * kStageBytes + Staging<STAGE>::bytes + sizeof(SmemCtrl) + 1024;
 }
+static_assert(smem_bytes<1>() <= 232448 && smem_bytes<2>() <= 232448, "shared memory budget of one SM exceeded");
 
-// Optional timeline instrumentation (build with -DFLYMOE_TRACE): CTA 0 records clock64()
-// stamps of its producer thread, MMA thread and first epilogue thread for the first
-// kTraceSlots K blocks; flymoe_trace_read() copies them out.
-#ifdef FLYMOE_TRACE
-constexpr int kTraceSlots = 256;
-__device__ long long g_trace[4][kTraceSlots][8];
-__device__ int g_trace_cfg[3] = {0, 0, 0};   // first K-block slot, first tile, CTA to record
-// trc_slot0 / trc_tile0 / trc_on are per-thread copies read once at kernel start, so that a
-// trace point costs one clock read and (inside the window) one store, and nothing else.
-#define TRACE_AT(role, rel, idx) \
-  do { if (trc_on && unsigned(rel) < unsigned(kTraceSlots)) g_trace[role][rel][idx] = clock64(); } while (0)
-#define TRACE(role, slot, idx) TRACE_AT(role, int(slot) - trc_slot0, idx)
-#define TRACE_E(slot, idx) \
-  do { if (threadIdx.x == 128) TRACE(2, slot, idx); } while (0)
-#define TRACE_T(slot, idx) \
-  do { if (threadIdx.x == 128) TRACE_AT(3, int(slot) - trc_tile0, idx); } while (0)
-#else
-#define TRACE(role, slot, idx) do {} while (0)
-#define TRACE_E(slot, idx) do {} while (0)
-#define TRACE_T(slot, idx) do {} while (0)
-#endif
-
-// Optional whole-kernel wait accounting (build with -DFLYMOE_PROF): every CTA's producer thread,
-// MMA thread and first epilogue thread add up the cycles they spend in each wait and write the
-// sums once at the end; flymoe_prof_read() copies them out: [CTA][role][8].
+// Optional whole-kernel wait accounting (build with -DFLYMOE_PROF, `python -m flydsl_b200.build
+// --prof`): every CTA's producer thread, MMA thread and first epilogue thread add up the cycles they
+// spend in each wait and write the sums once at the end; flymoe_prof_read() copies them out as
+// [CTA][role][8] int64 (`python bench.py --wait-accounting` prints the means).
 #ifdef FLYMOE_PROF
 __device__ long long g_prof[256][3][8];
 #define PROF_DECL long long prof_t0 = clock64(), prof_s = 0, prof_w[6] = {0, 0, 0, 0, 0, 0};
@@ -165,7 +168,8 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 // `backoff_ns` > 0 makes a role that has slack sleep between polls instead of competing for
 // issue slots with the epilogue warps of its scheduler partition.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int code, unsigned backoff_ns = 0) {
+                                          int* status, int code, unsigned backoff_ns = 0,
+                                          unsigned long long limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_timer_ns();
 #pragma unroll 1
@@ -174,7 +178,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (backoff_ns) __nanosleep(backoff_ns);
     if ((it & 0xFF) == 0) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
+      if (global_timer_ns() - t0 > limit_ns) {
         *abort_flag = 1;
         atomicCAS(status, 0, code);
         return false;
@@ -207,19 +211,24 @@ __device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t adesc, uint64_
       "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                : "memory");
 }
-__device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t* v) {
+__device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t* v) {
   asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
       : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
       : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ unsigned long long pack_f32x2(float x) {
@@ -258,11 +267,13 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
   d |= uint64_t(2) << 61;                            // SWIZZLE_128B
   return d;
 }
-// kind::f8f6f4, A=B=e4m3, D=f32, both K-major, M=128, N=256.
-constexpr uint32_t kInstrDesc = (1u << 4) | (0u << 7) | (0u << 10) | (uint32_t(BN >> 3) << 17) |
-                                (uint32_t(BM >> 4) << 24);
+// Instruction descriptors, both operands K-major, M=128, N=256:
+// kind::f8f6f4 with A=B=e4m3 (format 0) and D=f32 (format 1); kind::i8 with A=B=s8 (format 1) and D=s32 (format 2).
+constexpr uint32_t kInstrDescShape = (uint32_t(BN >> 3) << 17) | (uint32_t(BM >> 4) << 24);
+constexpr uint32_t kInstrDescF8 = (1u << 4) | (0u << 7) | (0u << 10) | kInstrDescShape;
+constexpr uint32_t kInstrDescI8 = (2u << 4) | (1u << 7) | (1u << 10) | kInstrDescShape;
 
-// Bulk operations from a staging slot to a contiguous global row segment (16-byte aligned, size % 16 == 0).
+// Bulk operations from the staging tile to a contiguous global row segment (16-byte aligned, size % 16 == 0).
 __device__ __forceinline__ void bulk_reduce_add_bf16(void* g, uint32_t s, uint32_t bytes) {
   asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.noftz.bf16 [%0], [%1], %2;"
                ::"l"(g), "r"(s), "r"(bytes) : "memory");
@@ -294,7 +305,7 @@ struct TileSched {
 
 // ROW_DST (stage 2 only): every output row goes to a caller-given address instead of out[t*k+s].  A
 // separate instantiation, so that the common kernel's register allocation is not touched.
-template <int STAGE, bool ROW_DST = false>
+template <int STAGE, bool ROW_DST, int SCALING>
 __global__ void __launch_bounds__(kNumThreads, 1)
 moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const GemmArgs a, const int group_m) {
@@ -308,13 +319,9 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int KB = a.k_dim / BK;
-#ifdef FLYMOE_TRACE
-  const int trc_slot0 = g_trace_cfg[0], trc_tile0 = g_trace_cfg[1];
-  const bool trc_on = int(blockIdx.x) == g_trace_cfg[2];
-#endif
 
   const int valid_rows = min(__ldg(a.num_valid_ids), a.size_expert_ids * a.tile_m);
-  // Outputs that leave through the staging slots (everything except 16-bit stage-1 and fp32 stage-2 output)
+  // Outputs that leave through the staging tile (everything except 16-bit stage-1 and fp32 stage-2 output)
   const bool uses_staging = STAGE == 1 ? a.out_dtype == FLYMOE_E4M3 : a.out_dtype != FLYMOE_F32;
   TileSched sched;
   sched.num_mblocks = (valid_rows + a.tile_m - 1) / a.tile_m;
@@ -348,25 +355,14 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   tcgen05_fence_after();
   const uint32_t tmem_base = ctrl->tmem_base;
 
-  // Register re-split: 384 threads x 168 registers are allocated at launch; the producer warpgroup
-  // drops to 40 and the two epilogue warpgroups rise to 232 (128*40 + 256*232 = 384*168 exactly --
-  // a larger request would wait forever for registers that are never released).
-  static_assert(128 * 40 + 256 * 232 <= kNumThreads * 168, "setmaxnreg split exceeds the launch allocation");
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsProducer));
     if (warp == 0 && lane == 0) {
       // ---------------------------------------------------------------- TMA producer
       int stage = 0;
       uint32_t phase = 0;
-#if defined(FLYMOE_EXP_SMALL_A)
-      const uint32_t tx_bytes = 16u * BK + kBTileBytes;          // timing experiment: 16-row A box
-#elif defined(FLYMOE_EXP_HALF_B)
-      const uint32_t tx_bytes = uint32_t(a.tile_m) * BK + kBTileBytes / 2;   // timing experiment: half of B
-#else
       const uint32_t tx_bytes = uint32_t(a.tile_m) * BK + kBTileBytes;
-#endif
       bool ok = true;
-      int tslot = 0;
       PROF_DECL
       int mb_next = 0, n_next = 0, e_next = -1;
       if (int(blockIdx.x) < sched.total) {
@@ -380,12 +376,10 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           e_next = __ldg(a.sorted_expert_ids + mb_next);
         }
         if (e < 0 || e >= a.experts) continue;
-        for (int kb = 0; kb < KB; ++kb, ++tslot) {
-          TRACE(0, tslot, 0);
+        for (int kb = 0; kb < KB; ++kb) {
           PROF_START
           if (!mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, a.status, 1, 64)) { ok = false; break; }
           PROF_STOP(0) PROF_COUNT(5)
-          TRACE(0, tslot, 1);
           const uint32_t full = smem_u32(&ctrl->full[stage]);
           const uint32_t sa = smem_u32(smem + size_t(stage) * kStageBytes);
           const uint32_t sb = sa + kATileBytes;
@@ -393,13 +387,10 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           tma_load_2d(sa, &tmap_a, full, kb * BK, mb * a.tile_m);
           if (STAGE == 1) {
             tma_load_3d(sb, &tmap_b, full, kb * BK, n * 128, e);
-#ifndef FLYMOE_EXP_HALF_B
             tma_load_3d(sb + 128 * BK, &tmap_b, full, kb * BK, a.n_dim + n * 128, e);
-#endif
           } else {
             tma_load_3d(sb, &tmap_b, full, kb * BK, n * BN, e);
           }
-          TRACE(0, tslot, 2);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -409,8 +400,8 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
-      int tslot = 0;
       PROF_DECL
+      const bool int8_ops = SCALING == kScalePerToken && a.in_dtype == FLYMOE_I8;
       int mb_next = 0, n_next = 0, e_next = -1;
       if (int(blockIdx.x) < sched.total) {
         sched.decode(blockIdx.x, mb_next, n_next);
@@ -423,37 +414,47 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           e_next = __ldg(a.sorted_expert_ids + mb_next);
         }
         if (e < 0 || e >= a.experts) continue;
-        for (int kb = 0; kb < KB; ++kb, ++tslot) {
-          TRACE(1, tslot, 0);
+        if (SCALING == kScalePerToken) {       // one accumulator stage per tile
           PROF_START
           if (!mbar_wait(smem_u32(&ctrl->tmem_empty[acc]), acc_phase ^ 1, abort_flag, a.status, 2)) { ok = false; break; }
-          PROF_STOP(0) PROF_START
+          PROF_STOP(0)
+        }
+        for (int kb = 0; kb < KB; ++kb) {
+          if (SCALING == kScaleBlock128) {     // one accumulator stage per K block, started from zero
+            PROF_START
+            if (!mbar_wait(smem_u32(&ctrl->tmem_empty[acc]), acc_phase ^ 1, abort_flag, a.status, 2)) { ok = false; break; }
+            PROF_STOP(0)
+          }
+          PROF_START
           if (!mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag, a.status, 3)) { ok = false; break; }
           PROF_STOP(1)
           PROF_COUNT(5) PROF_START
-          TRACE(1, tslot, 2);
           tcgen05_fence_after();
           const uint32_t sa = smem_u32(smem + size_t(stage) * kStageBytes);
           const uint64_t adesc = make_smem_desc(sa);
           const uint64_t bdesc = make_smem_desc(sa + kATileBytes);
           const uint32_t d_tmem = tmem_base + uint32_t(acc) * BN;
 #pragma unroll
-          for (int k = 0; k < BK / 32; ++k)
-            umma_f8(d_tmem, adesc + uint64_t(k * 2), bdesc + uint64_t(k * 2), kInstrDesc, k > 0 ? 1u : 0u);
+          for (int k = 0; k < BK / 32; ++k) {
+            const uint32_t accumulate = (k > 0 || (SCALING == kScalePerToken && kb > 0)) ? 1u : 0u;
+            if (int8_ops) umma_i8(d_tmem, adesc + uint64_t(k * 2), bdesc + uint64_t(k * 2), kInstrDescI8, accumulate);
+            else umma_f8(d_tmem, adesc + uint64_t(k * 2), bdesc + uint64_t(k * 2), kInstrDescF8, accumulate);
+          }
           umma_commit(smem_u32(&ctrl->empty[stage]));
-          umma_commit(smem_u32(&ctrl->tmem_full[acc]));
+          if (SCALING == kScaleBlock128 || kb + 1 == KB) {
+            umma_commit(smem_u32(&ctrl->tmem_full[acc]));
+            if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
+          }
           PROF_STOP(3)
-          TRACE(1, tslot, 3);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
-          if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
         }
       }
       PROF_WRITE(1);
     } else if (warp == 2 && uses_staging) {
       // ---------------------------------------------------------------- store warp
-      // Issues the bulk store / bulk reduce of every epilogue thread's staging slot, eight slots per
-      // lane, so that the ~10 cycles each of those 256 operations takes to be accepted are spent here
-      // and not by the epilogue warps between two tiles.
+      // Issues the bulk store / bulk reduce of every row of the staging tile, four rows per lane, so
+      // that the cycles each of those operations takes to be accepted are spent here and not by the
+      // epilogue warps between two tiles.
       bool ok = true;
       uint32_t it = 0;
       int mb_next = 0, n_next = 0, e_next = -1;
@@ -461,7 +462,6 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         sched.decode(blockIdx.x, mb_next, n_next);
         e_next = __ldg(a.sorted_expert_ids + mb_next);
       }
-      constexpr uint32_t kSlotBytes = STAGE == 1 ? 64u : 256u;
       const bool bf = a.out_dtype == FLYMOE_BF16;
       for (int t = blockIdx.x; t < sched.total && ok; t += gridDim.x) {
         const int e = e_next, n = n_next;
@@ -471,23 +471,22 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         }
         if (e < 0 || e >= a.experts) continue;
         if (!mbar_wait(smem_u32(&ctrl->stg_full), it & 1, abort_flag, a.status, 6, 64)) { ok = false; break; }
-        // stage 2 with n_dim = 64 mod 128 (dense GEMM only): the tile's last segment holds 64 columns
-        const int cols_left = STAGE == 2 ? a.n_dim - n * BN : 0;
+        // stage 2: the last tile of a row may hold fewer than 256 columns (n_dim = 64 or 128 mod 256)
+        const uint32_t bytes = STAGE == 1 ? 128u : uint32_t(min(BN, a.n_dim - n * BN)) * 2u;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int sl = i * 32 + lane;
-          const unsigned long long dst = ctrl->stg_dst[sl];
+        for (int i = 0; i < BM / 32; ++i) {
+          const int row = i * 32 + lane;
+          const unsigned long long dst = ctrl->stg_dst[row];
           if (dst != 0ull) {
-            const uint32_t sp = smem_u32(staging + size_t(sl) * Staging<STAGE>::stride);
+            const uint32_t sp = smem_u32(staging + size_t(row) * Staging<STAGE>::stride);
             void* gp = reinterpret_cast<void*>(dst);
-            const uint32_t bytes = (STAGE == 2 && cols_left - (sl >> 7) * 128 < 128) ? kSlotBytes / 2 : kSlotBytes;
             if (STAGE == 1 || !a.accumulate) bulk_store(gp, sp, bytes);
             else if (bf) bulk_reduce_add_bf16(gp, sp, bytes);
             else bulk_reduce_add_f16(gp, sp, bytes);
           }
         }
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-        bulk_wait_read_all();                      // the slots may be overwritten from here on
+        bulk_wait_read_all();                      // the staging tile may be overwritten from here on
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&ctrl->stg_free));
         ++it;
@@ -495,9 +494,9 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       bulk_wait_all();                             // every row segment has landed before the CTA retires
     }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsEpilogue));
     // ------------------------------------------------------------------ epilogue
-    const int wg = (warp - 4) >> 2;          // 0 or 1
+    const int wg = (warp - 4) >> 2;          // 0..3: which 64-column slice of the accumulator
     const int q = warp & 3;                  // TMEM lane quadrant of this warp
     const int row_in_tile = q * 32 + lane;
     const bool warp_active = q * 32 < a.tile_m;
@@ -506,12 +505,10 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     uint32_t acc_phase = 0;
     uint32_t tile_iter = 0;
     bool ok = true;
-    int tslot = 0;
     PROF_DECL
     static_assert(kAccStages == 2, "the epilogue's stage/phase stepping assumes two accumulator stages");
     const uint32_t full_bar0 = smem_u32(&ctrl->tmem_full[0]);     // stage 1's barrier is 8 bytes further
     const uint32_t empty_bar0 = smem_u32(&ctrl->tmem_empty[0]);
-    constexpr int NACC = 128;                // fp32 accumulators per thread
     // Routing of a tile (expert id, this thread's packed row id) is loaded one tile ahead.
     const int pad_id = (a.topk << 24) | a.num_tokens;
     int mb_next = 0, n_next = 0, e_next = -1, id_next = pad_id;
@@ -522,6 +519,10 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       id_next = (row_in_tile < a.tile_m && rr < valid_rows) ? __ldg(a.sorted_ids + rr) : pad_id;
     };
     if (int(blockIdx.x) < sched.total) load_routing(blockIdx.x);
+    // TMEM columns of this thread's two 32-column halves.  Stage 1: gate columns [32wg, 32wg+32) and
+    // the up columns 128 further; stage 2: columns [64wg, 64wg+64).
+    const uint32_t tcol0 = tmem_base + lane_base + (STAGE == 1 ? uint32_t(wg * 32) : uint32_t(wg * 64));
+    const uint32_t tcol1 = tmem_base + lane_base + (STAGE == 1 ? uint32_t(128 + wg * 32) : uint32_t(wg * 64 + 32));
     for (int t = blockIdx.x; t < sched.total && ok; t += gridDim.x) {
       const int mb = mb_next, n = n_next, e = e_next, id = id_next;
       if (t + int(gridDim.x) < sched.total) load_routing(t + gridDim.x);
@@ -536,113 +537,152 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         sidx = a.a_scale_layout == FLYMOE_ROWS_BY_TOKEN ? (long long)tok
              : a.a_scale_layout == FLYMOE_ROWS_BY_PAIR ? (long long)tok * a.topk + slot : (long long)r;
       }
-      const float* sa_ptr = a.scale_a + sidx * a.sa_row_stride;
-      // weight block scales of this tile
-      const int wblk_per_expert = (STAGE == 1 ? 2 * a.n_dim : a.n_dim) / 128;
-      const int blk0 = STAGE == 1 ? n : n * 2 + wg;
-      const int blk1 = STAGE == 1 ? a.n_dim / 128 + n : blk0;
-      const bool half_ok = STAGE == 1 ? true : (n * BN + wg * 128 < a.n_dim);
-      const float* sw0_ptr = a.scale_w + ((long long)e * wblk_per_expert + (half_ok ? blk0 : 0)) * KB;
-      const int sw1_off = (blk1 - (half_ok ? blk0 : 0)) * KB;      // up-projection scales, relative to sw0_ptr
-
+      // stage 2: a warpgroup whose 64 columns lie beyond n_dim (last tile of a row) has nothing to do
+      const bool half_ok = STAGE == 1 ? true : (n * BN + wg * 64 < a.n_dim);
+      const bool work = warp_active && half_ok;
       // routing weight of this row: loaded now, used after the K loop
       const float wgt = (a.doweight && valid) ? __ldg(a.sorted_weights + r) : 1.f;
-      // fp32 accumulators held as packed pairs so the scale-FMA runs as fma.rn.f32x2
-      unsigned long long acc2[NACC / 2];
-#pragma unroll
-      for (int j = 0; j < NACC / 2; ++j) acc2[j] = 0ull;
+      float accv[NACC];
 
-      float sa_next = valid ? __ldg(sa_ptr) : 0.f;
-      float s0_next = __ldg(sw0_ptr);
-      float s1_next = STAGE == 1 ? __ldg(sw0_ptr + sw1_off) : 0.f;
-      const float* sa_run = sa_ptr;            // running pointer: one add per K block, no multiply
-      const bool work = warp_active && half_ok;
-      // stage 1: first half = gate columns, second half = up columns; stage 2: two halves of 128 columns
-      const uint32_t tcol0 = tmem_base + lane_base + (STAGE == 1 ? uint32_t(wg * 64) : uint32_t(wg * 128));
-      const uint32_t tcol1 = tmem_base + lane_base + (STAGE == 1 ? uint32_t(128 + wg * 64) : uint32_t(wg * 128 + 64));
-      // One K block = four 32-column chunks through two register buffers, two tcgen05.ld in flight at
-      // a time: the thread waits twice per K block, not once per chunk.
-      uint32_t v0[32], v1[32];
-      // measured: two K blocks per loop trip help stage 1 (~1.5 %) and cost stage 2 about as much
-#pragma unroll (STAGE == 1 ? 2 : 1)
-      for (int kb = 0; kb < KB; ++kb, ++tslot) {
-        TRACE_E(tslot, 0);
+      if (SCALING == kScaleBlock128) {
+        const float* sa_ptr = a.scale_a + sidx * a.sa_row_stride;
+        // weight block scales of this tile: [expert][128-row block][K block]
+        const int wblk_per_expert = (STAGE == 1 ? 2 * a.n_dim : a.n_dim) / 128;
+        const int blk0 = STAGE == 1 ? n : n * 2 + (wg >> 1);
+        const int blk1 = STAGE == 1 ? a.n_dim / 128 + n : blk0;
+        const float* sw0_ptr = a.scale_w + ((long long)e * wblk_per_expert + (half_ok ? blk0 : 0)) * KB;
+        const int sw1_off = (blk1 - (half_ok ? blk0 : 0)) * KB;      // up-projection scales, relative to sw0_ptr
+        // fp32 accumulators held as packed pairs so the scale-FMA runs as fma.rn.f32x2
+        unsigned long long acc2[NACC / 2];
+#pragma unroll
+        for (int j = 0; j < NACC / 2; ++j) acc2[j] = 0ull;
+
+        float sa_next = valid ? __ldg(sa_ptr) : 0.f;
+        float s0_next = __ldg(sw0_ptr);
+        float s1_next = STAGE == 1 ? __ldg(sw0_ptr + sw1_off) : 0.f;
+        const float* sa_run = sa_ptr;            // running pointer: one add per K block, no multiply
+        // One K block = four 16-column chunks through two register buffers, two tcgen05.ld in flight at
+        // a time: the thread waits twice per K block, not once per chunk.
+        uint32_t v0[16], v1[16];
+#pragma unroll 1
+        for (int kb = 0; kb < KB; ++kb) {
+          const uint32_t stage_off = uint32_t(acc) * BN;
+          PROF_START
+          if (!mbar_wait(full_bar0 + uint32_t(acc) * 8u, acc_phase, abort_flag, a.status, 4)) { ok = false; break; }
+          PROF_STOP(0) PROF_COUNT(5)
+          tcgen05_fence_after();
+          if (work) {                            // both chunks of the first half on their way at once
+            tmem_ld_x16(tcol0 + stage_off, v0);
+            tmem_ld_x16(tcol0 + stage_off + 16, v1);
+          }
+          const unsigned long long c0 = pack_f32x2(sa_next * s0_next);
+          const unsigned long long c1 = STAGE == 1 ? pack_f32x2(sa_next * s1_next) : c0;
+          if (work) tmem_ld_wait();
+          if (kb + 1 < KB) {                     // next K block's scales: in flight during this block's math
+            sa_run += a.sa_stride;
+            sa_next = valid ? __ldg(sa_run) : 0.f;
+            s0_next = __ldg(sw0_ptr + kb + 1);
+            if (STAGE == 1) s1_next = __ldg(sw0_ptr + kb + 1 + sw1_off);
+          }
+          if (work) {
+            // each buffer is refilled with its chunk of the second half as soon as it has been folded in
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ffma2(acc2[j], v0[2 * j], v0[2 * j + 1], c0);
+            tmem_ld_x16(tcol1 + stage_off, v0);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ffma2(acc2[8 + j], v1[2 * j], v1[2 * j + 1], c0);
+            tmem_ld_x16(tcol1 + stage_off + 16, v1);
+            tmem_ld_wait();
+          }
+          // The K block's partial sums are in registers now (tcgen05.wait::ld has returned, so the loads
+          // have completed and need no further ordering): hand the TMEM stage back before the last
+          // chunk's FMAs.  The arrive publishes no memory, hence relaxed; tcgen05.wait::ld is warp-wide
+          // (.sync.aligned), so when lane 0 is past it every lane's loads have landed.
+          if (!work) __syncwarp();
+          if (lane == 0) mbar_arrive_relaxed(empty_bar0 + uint32_t(acc) * 8u);
+          if (work) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ffma2(acc2[16 + j], v0[2 * j], v0[2 * j + 1], c1);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ffma2(acc2[24 + j], v1[2 * j], v1[2 * j + 1], c1);
+          }
+          acc_phase ^= uint32_t(acc);
+          acc ^= 1;
+        }
+        if (!ok) break;
+#pragma unroll
+        for (int j = 0; j < NACC / 2; ++j) unpack_f32x2(acc2[j], accv[2 * j], accv[2 * j + 1]);
+      } else {
+        // One scale per activation row, one per weight row: the whole K range has been accumulated in
+        // TMEM; drain the tile once and scale it here.
         const uint32_t stage_off = uint32_t(acc) * BN;
         PROF_START
         if (!mbar_wait(full_bar0 + uint32_t(acc) * 8u, acc_phase, abort_flag, a.status, 4)) { ok = false; break; }
         PROF_STOP(0) PROF_COUNT(5)
         tcgen05_fence_after();
-        TRACE_E(tslot, 1);
-        if (work) {                            // both chunks of the first half on their way at once
-          tmem_ld_x32(tcol0 + stage_off, v0);
-          tmem_ld_x32(tcol0 + stage_off + 32, v1);
-        }
-        const unsigned long long c0 = pack_f32x2(sa_next * s0_next);
-        const unsigned long long c1 = STAGE == 1 ? pack_f32x2(sa_next * s1_next) : c0;
-        if (work) tmem_ld_wait();
-        TRACE_E(tslot, 2);
-        if (kb + 1 < KB) {                     // next K block's scales: in flight during this block's math
-          sa_run += a.sa_stride;
-          sa_next = valid ? __ldg(sa_run) : 0.f;
-          s0_next = __ldg(sw0_ptr + kb + 1);
-          if (STAGE == 1) s1_next = __ldg(sw0_ptr + kb + 1 + sw1_off);
-        }
+        // the raw accumulators land in the registers of accv and are scaled in place
+        uint32_t* v = reinterpret_cast<uint32_t*>(accv);
         if (work) {
-          // each buffer is refilled with its chunk of the second half as soon as it has been folded in
-#pragma unroll
-          for (int j = 0; j < 16; ++j) ffma2(acc2[j], v0[2 * j], v0[2 * j + 1], c0);
-          tmem_ld_x32(tcol1 + stage_off, v0);
-#pragma unroll
-          for (int j = 0; j < 16; ++j) ffma2(acc2[16 + j], v1[2 * j], v1[2 * j + 1], c0);
-          tmem_ld_x32(tcol1 + stage_off + 32, v1);
+          tmem_ld_x16(tcol0 + stage_off, v);
+          tmem_ld_x16(tcol0 + stage_off + 16, v + 16);
+          tmem_ld_x16(tcol1 + stage_off, v + 32);
+          tmem_ld_x16(tcol1 + stage_off + 16, v + 48);
           tmem_ld_wait();
-          TRACE_E(tslot, 5);
+        } else {
+          __syncwarp();
         }
-        // The K block's partial sums are in registers now (tcgen05.wait::ld has returned, so the loads
-        // have completed and need no further ordering): hand the TMEM stage back before the last
-        // chunk's FMAs.  The arrive publishes no memory, hence relaxed; tcgen05.wait::ld is warp-wide
-        // (.sync.aligned), so when lane 0 is past it every lane's loads have landed.
-        if (!work) __syncwarp();
         if (lane == 0) mbar_arrive_relaxed(empty_bar0 + uint32_t(acc) * 8u);
-        TRACE_E(tslot, 6);
-        if (work) {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) ffma2(acc2[32 + j], v0[2 * j], v0[2 * j + 1], c1);
-#pragma unroll
-          for (int j = 0; j < 16; ++j) ffma2(acc2[48 + j], v1[2 * j], v1[2 * j + 1], c1);
-        }
-        TRACE_E(tslot, 7);
         acc_phase ^= uint32_t(acc);
         acc ^= 1;
+        if (work) {
+          const float sa = valid ? __ldg(a.scale_a + sidx) : 0.f;
+          const long long wrows = STAGE == 1 ? 2LL * a.n_dim : (long long)a.n_dim;
+          // weight-row scales of this thread's two 32-column halves (the same addresses in every lane)
+          const float* sw0 = a.scale_w + (long long)e * wrows + (STAGE == 1 ? n * 128 + wg * 32 : n * BN + wg * 64);
+          const float* sw1 = STAGE == 1 ? sw0 + a.n_dim : sw0 + 32;
+          const bool i8 = a.in_dtype == FLYMOE_I8;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const float* sw = h == 0 ? sw0 : sw1;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              const float4 s4 = __ldg(reinterpret_cast<const float4*>(sw + j));
+              const float c[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const int idx = h * 32 + j + u;
+                const float p = i8 ? __int2float_rn(int(v[idx])) : accv[idx];
+                accv[idx] = p * (sa * c[u]);
+              }
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < NACC; ++j) accv[j] = 0.f;
+        }
       }
-      if (!ok) break;
       // Destination of this row when the caller gave per-row addresses: requested after the K loop (the
       // loop runs at the register limit) and needed only once the row has been packed.
       unsigned long long row_dst_base = 0ull;
-      if (STAGE == 2 && ROW_DST && valid)
+      if (STAGE == 2 && ROW_DST && valid && wg == 0)
         row_dst_base = __ldg(a.row_dst + ((long long)tok * a.topk + slot));
-      float accv[NACC];
-#pragma unroll
-      for (int j = 0; j < NACC / 2; ++j) unpack_f32x2(acc2[j], accv[2 * j], accv[2 * j + 1]);
 
       // ---- tile epilogue -----------------------------------------------------------
       // Kept short on purpose: this code runs once per tile between two main loops, and a long
       // straight-line tail (IEEE division, accurate exp) costs more in instruction fetch than in math.
       PROF_START
-      TRACE_T(tile_iter, 0);
       if (STAGE == 1) {
-        // accv[0..63] = gate, accv[64..127] = up, columns n*128 + wg*64 + j
+        // accv[0..31] = gate, accv[32..63] = up, columns n*128 + wg*32 + j
         float amax = 0.f;
 #pragma unroll
-        for (int j = 0; j < 64; ++j) {
+        for (int j = 0; j < 32; ++j) {
           const float g = accv[j];
-          const float hval = g * fast_rcp(1.0f + fast_exp2(-1.4426950408889634f * g)) * (accv[64 + j] * wgt);
+          const float hval = g * fast_rcp(1.0f + fast_exp2(-1.4426950408889634f * g)) * (accv[32 + j] * wgt);
           accv[j] = hval;
           amax = fmaxf(amax, fabsf(hval));
         }
-        TRACE_T(tile_iter, 1);
         const long long orow = a.out_layout == FLYMOE_ROWS_SORTED ? (long long)r : (long long)tok * a.topk + slot;
-        const long long ocol = (long long)n * 128 + wg * 64;
+        const long long ocol = (long long)n * 128 + wg * 32;
         if (a.out_dtype == FLYMOE_E4M3) {
           const int buf = tile_iter & 1;
           const uint32_t bar = smem_u32(&ctrl->amax_bar[buf]);
@@ -650,20 +690,20 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           __syncwarp();
           if (lane == 0) mbar_arrive(bar);
           if (!mbar_wait(bar, (tile_iter >> 1) & 1, abort_flag, a.status, 5)) { ok = false; break; }
-          TRACE_T(tile_iter, 2);
-          // the store warp has finished reading the previous tile's slots
+          // the store warp has finished reading the previous tile's staging rows
           if (!mbar_wait(smem_u32(&ctrl->stg_free), (tile_iter & 1) ^ 1, abort_flag, a.status, 7)) { ok = false; break; }
           unsigned long long dst_addr = 0ull;
           const bool wr = warp_active && (valid || (in_tile && a.out_layout == FLYMOE_ROWS_SORTED));
           if (wr) {
-            const float m = fmaxf(ctrl->amax[buf][0][row_in_tile], ctrl->amax[buf][1][row_in_tile]);
+            const float m = fmaxf(fmaxf(ctrl->amax[buf][0][row_in_tile], ctrl->amax[buf][1][row_in_tile]),
+                                  fmaxf(ctrl->amax[buf][2][row_in_tile], ctrl->amax[buf][3][row_in_tile]));
             float sc = __fdiv_rn(m, 448.0f);
             if (sc == 0.f) sc = 1.f;
             const float inv = valid ? __fdiv_rn(1.0f, sc) : 0.f;     // pad rows: every code becomes 0
-            // 64 codes go through this thread's staging slot and leave as one 64-byte bulk store
-            uint8_t* op = staging + size_t(threadIdx.x - 128) * Staging<STAGE>::stride;
+            // this thread's 32 codes of the row's 128; the row leaves as one 128-byte bulk store
+            uint8_t* op = staging + size_t(row_in_tile) * Staging<STAGE>::stride + wg * 32;
 #pragma unroll
-            for (int j = 0; j < 64; j += 16) {
+            for (int j = 0; j < 32; j += 16) {
               uint4 pk;
               pk.x = float4_to_e4m3x4(accv[j + 0] * inv, accv[j + 1] * inv, accv[j + 2] * inv, accv[j + 3] * inv);
               pk.y = float4_to_e4m3x4(accv[j + 4] * inv, accv[j + 5] * inv, accv[j + 6] * inv, accv[j + 7] * inv);
@@ -673,17 +713,20 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
               *reinterpret_cast<uint4*>(op + j) = pk;
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            dst_addr = reinterpret_cast<unsigned long long>(static_cast<uint8_t*>(a.out) + orow * a.n_dim + ocol);
-            if (wg == 0) a.out_scale[(long long)n * a.out_scale_stride + orow] = sc;
+            if (wg == 0) {
+              dst_addr = reinterpret_cast<unsigned long long>(static_cast<uint8_t*>(a.out) + orow * a.n_dim +
+                                                              (long long)n * 128);
+              a.out_scale[(long long)n * a.out_scale_stride + orow] = sc;
+            }
           }
-          ctrl->stg_dst[threadIdx.x - 128] = dst_addr;
+          if (wg == 0) ctrl->stg_dst[row_in_tile] = dst_addr;
           __syncwarp();
           if (lane == 0) mbar_arrive(smem_u32(&ctrl->stg_full));
         } else if (warp_active && valid) {
           uint8_t* op = static_cast<uint8_t*>(a.out) + (orow * a.n_dim + ocol) * 2;
           const bool bf = a.out_dtype == FLYMOE_BF16;
 #pragma unroll
-          for (int j = 0; j < 64; j += 8) {
+          for (int j = 0; j < 32; j += 8) {
             uint4 pk;
             pk.x = bf ? pack_bf16x2(accv[j + 0], accv[j + 1]) : pack_f16x2(accv[j + 0], accv[j + 1]);
             pk.y = bf ? pack_bf16x2(accv[j + 2], accv[j + 3]) : pack_f16x2(accv[j + 2], accv[j + 3]);
@@ -695,23 +738,22 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       } else if (a.out_dtype == FLYMOE_F32) {
         if (warp_active && valid && half_ok) {
           // fp32 output: vector reductions straight from registers (accumulate mode only)
-          float* op = static_cast<float*>(a.out) + (long long)tok * a.n_dim + (long long)n * BN + wg * 128;
+          float* op = static_cast<float*>(a.out) + (long long)tok * a.n_dim + (long long)n * BN + wg * 64;
 #pragma unroll
-          for (int j = 0; j < 128; j += 4)
+          for (int j = 0; j < NACC; j += 4)
             red_add_v4_f32(op + j, accv[j] * wgt, accv[j + 1] * wgt, accv[j + 2] * wgt, accv[j + 3] * wgt);
         }
       } else {
-        // 16-bit output: each thread parks its 128 results (256 B) in its own slot of the staging area
-        // together with the global address of its row segment; the store warp sends every slot off as
-        // ONE bulk reduce-add (or bulk store), instead of 16 scattered 16-byte atomics per thread.
-        uint8_t* slot_ptr = staging + size_t(threadIdx.x - 128) * Staging<STAGE>::stride;
+        // 16-bit output: each thread parks its 64 results (128 B) in its row of the staging tile; the
+        // thread of warpgroup 0 adds the global address of the row segment, and the store warp sends
+        // every row off as ONE bulk reduce-add (or bulk store) of up to 512 bytes.
+        uint8_t* slot_ptr = staging + size_t(row_in_tile) * Staging<STAGE>::stride + wg * 128;
         if (!mbar_wait(smem_u32(&ctrl->stg_free), (tile_iter & 1) ^ 1, abort_flag, a.status, 7)) { ok = false; break; }
         unsigned long long dst_addr = 0ull;
-        TRACE_T(tile_iter, 1);
         if (warp_active && valid && half_ok) {
           const bool bf = a.out_dtype == FLYMOE_BF16;
 #pragma unroll
-          for (int j = 0; j < 128; j += 8) {
+          for (int j = 0; j < NACC; j += 8) {
             uint4 pk;
             pk.x = bf ? pack_bf16x2(accv[j] * wgt, accv[j + 1] * wgt) : pack_f16x2(accv[j] * wgt, accv[j + 1] * wgt);
             pk.y = bf ? pack_bf16x2(accv[j + 2] * wgt, accv[j + 3] * wgt) : pack_f16x2(accv[j + 2] * wgt, accv[j + 3] * wgt);
@@ -719,24 +761,28 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             pk.w = bf ? pack_bf16x2(accv[j + 6] * wgt, accv[j + 7] * wgt) : pack_f16x2(accv[j + 6] * wgt, accv[j + 7] * wgt);
             *reinterpret_cast<uint4*>(slot_ptr + j * 2) = pk;
           }
-          TRACE_T(tile_iter, 2);
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          const long long orow = a.accumulate ? (long long)tok : (long long)tok * a.topk + slot;
-          const long long col_bytes = ((long long)n * BN + wg * 128) * 2;
-          if (ROW_DST) {
-            // rows leave for caller-given addresses (another GPU's buffer included): the bulk store
-            // carries the row segment there while the next tile is in the tensor cores
-            const unsigned long long base = row_dst_base;
-            dst_addr = base != 0ull ? base + (unsigned long long)col_bytes : 0ull;
-          } else {
-            dst_addr = reinterpret_cast<unsigned long long>(static_cast<uint8_t*>(a.out) + orow * a.n_dim * 2 + col_bytes);
+          if (wg == 0) {
+            const long long orow = a.accumulate ? (long long)tok : (long long)tok * a.topk + slot;
+            const long long col_bytes = (long long)n * BN * 2;
+            if (ROW_DST) {
+              // rows leave for caller-given addresses (another GPU's buffer included): the bulk store
+              // carries the row segment there while the next tile is in the tensor cores.  A
+              // misaligned address would fault the bulk store: drop the row and report instead.
+              if ((row_dst_base & 15ull) != 0ull) {
+                atomicCAS(a.status, 0, 17);
+              } else if (row_dst_base != 0ull) {
+                dst_addr = row_dst_base + (unsigned long long)col_bytes;
+              }
+            } else {
+              dst_addr = reinterpret_cast<unsigned long long>(static_cast<uint8_t*>(a.out) + orow * a.n_dim * 2 + col_bytes);
+            }
           }
         }
-        ctrl->stg_dst[threadIdx.x - 128] = dst_addr;
+        if (wg == 0) ctrl->stg_dst[row_in_tile] = dst_addr;
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&ctrl->stg_full));
       }
-      TRACE_T(tile_iter, 3);
       PROF_STOP(1) PROF_COUNT(4)
       ++tile_iter;
     }
@@ -752,6 +798,19 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   }
 }
 
+// One thread waits, with the kernels' own bounded wait, on a barrier that nobody arrives at.
+__global__ void bounded_wait_selftest_kernel(int* status, unsigned long long limit_ns, int code) {
+  __shared__ unsigned long long bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) mbar_wait(smem_u32(&bar), 0, &abort_flag, status, code, 64, limit_ns);
+}
+
 }  // namespace flymoe
 
 extern "C" int flymoe_set_gemm_cta_limit(int max_ctas) {
@@ -763,24 +822,21 @@ extern "C" int flymoe_set_gemm_cta_limit(int max_ctas) {
   return FLYMOE_OK;
 }
 
+extern "C" int flymoe_selftest_bounded_wait(int64_t limit_ns, void* stream) {
+  using namespace flymoe;
+  FLYMOE_REQUIRE(limit_ns > 0 && limit_ns <= 100000000, "selftest_bounded_wait: limit_ns must be in (0, 1e8]");
+  int* status = device_status_ptr();
+  FLYMOE_REQUIRE(status != nullptr, "selftest_bounded_wait: no CUDA device");
+  bounded_wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      status, static_cast<unsigned long long>(limit_ns), FLYMOE_STATUS_SELFTEST_TIMEOUT);
+  FLYMOE_CUDA_CHECK(cudaGetLastError());
+  return FLYMOE_OK;
+}
+
 #ifdef FLYMOE_PROF
 extern "C" int flymoe_prof_read(long long* host_out) {
   FLYMOE_CUDA_CHECK(cudaDeviceSynchronize());
   FLYMOE_CUDA_CHECK(cudaMemcpyFromSymbol(host_out, flymoe::g_prof, sizeof(flymoe::g_prof)));
-  return FLYMOE_OK;
-}
-#endif
-
-#ifdef FLYMOE_TRACE
-// Copies the timeline of the last traced launch to host memory: [4 roles][256 slots][8] int64.
-extern "C" int flymoe_trace_config(int first_slot, int first_tile, int cta) {
-  const int cfg[3] = {first_slot, first_tile, cta};
-  FLYMOE_CUDA_CHECK(cudaMemcpyToSymbol(flymoe::g_trace_cfg, cfg, sizeof(cfg)));
-  return FLYMOE_OK;
-}
-extern "C" int flymoe_trace_read(long long* host_out) {
-  FLYMOE_CUDA_CHECK(cudaDeviceSynchronize());
-  FLYMOE_CUDA_CHECK(cudaMemcpyFromSymbol(host_out, flymoe::g_trace, sizeof(flymoe::g_trace)));
   return FLYMOE_OK;
 }
 #endif
@@ -820,6 +876,17 @@ static int make_map(CUtensorMap* map, const void* base, int rank, const cuuint64
   return FLYMOE_OK;
 }
 
+template <int STAGE, bool ROW_DST, int SCALING>
+static int launch_one(int grid, cudaStream_t stream, const CUtensorMap& map_a, const CUtensorMap& map_b,
+                      const GemmArgs& a, int group_m) {
+  auto* kernel = moe_gemm_sm100_kernel<STAGE, ROW_DST, SCALING>;
+  FLYMOE_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         int(smem_bytes<STAGE>())));
+  kernel<<<grid, kNumThreads, smem_bytes<STAGE>(), stream>>>(map_a, map_b, a, group_m);
+  FLYMOE_CUDA_CHECK(cudaGetLastError());
+  return FLYMOE_OK;
+}
+
 int launch_gemm_sm100(int stage, const GemmArgs& a, cudaStream_t stream) {
   if (a.tile_m != 16 && a.tile_m != 32 && a.tile_m != 64 && a.tile_m != 128) {
     set_last_error_msg("tcgen05 GEMM: tile_m must be 16, 32, 64 or 128");
@@ -829,16 +896,17 @@ int launch_gemm_sm100(int stage, const GemmArgs& a, cudaStream_t stream) {
     set_last_error_msg("tcgen05 GEMM: activations must be in sorted-row order (use flymoe_gather_rows)");
     return FLYMOE_ERR_UNSUPPORTED;
   }
+  const bool per_token = a.scaling == FLYMOE_SCALE_PER_TOKEN;
+  if (per_token && (a.row_dst != nullptr || a.out_dtype == FLYMOE_E4M3)) {
+    set_last_error_msg("tcgen05 GEMM: per-token scaling supports neither per-row destinations nor e4m3 output");
+    return FLYMOE_ERR_UNSUPPORTED;
+  }
   const long long wrows = stage == 1 ? 2LL * a.n_dim : a.n_dim;
   CUtensorMap map_a, map_b;
   {
     cuuint64_t dims[2] = {cuuint64_t(a.k_dim), cuuint64_t(a.a_rows)};
     cuuint64_t strides[1] = {cuuint64_t(a.k_dim)};
-#ifdef FLYMOE_EXP_SMALL_A
-    cuuint32_t box[2] = {cuuint32_t(BK), 16};
-#else
     cuuint32_t box[2] = {cuuint32_t(BK), cuuint32_t(a.tile_m)};
-#endif
     int rc = make_map(&map_a, a.a, 2, dims, strides, box);
     if (rc != FLYMOE_OK) return rc;
   }
@@ -858,24 +926,12 @@ int launch_gemm_sm100(int stage, const GemmArgs& a, cudaStream_t stream) {
   if (g_cta_limit > 0 && g_cta_limit < ctas) ctas = g_cta_limit;
   const int grid = int(max_tiles < ctas ? max_tiles : ctas);
   if (grid <= 0) return FLYMOE_OK;
-  if (stage == 1) {
-    FLYMOE_CUDA_CHECK(cudaFuncSetAttribute(moe_gemm_sm100_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           int(smem_bytes<1>())));
-    moe_gemm_sm100_kernel<1><<<grid, kNumThreads, smem_bytes<1>(), stream>>>(map_a, map_b, a, group_m);
-  } else {
-    if (a.row_dst != nullptr) {
-      FLYMOE_CUDA_CHECK(cudaFuncSetAttribute(moe_gemm_sm100_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             int(smem_bytes<2>())));
-      moe_gemm_sm100_kernel<2, true><<<grid, kNumThreads, smem_bytes<2>(), stream>>>(map_a, map_b, a, group_m);
-      FLYMOE_CUDA_CHECK(cudaGetLastError());
-      return FLYMOE_OK;
-    }
-    FLYMOE_CUDA_CHECK(cudaFuncSetAttribute(moe_gemm_sm100_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           int(smem_bytes<2>())));
-    moe_gemm_sm100_kernel<2><<<grid, kNumThreads, smem_bytes<2>(), stream>>>(map_a, map_b, a, group_m);
-  }
-  FLYMOE_CUDA_CHECK(cudaGetLastError());
-  return FLYMOE_OK;
+  if (per_token)
+    return stage == 1 ? launch_one<1, false, kScalePerToken>(grid, stream, map_a, map_b, a, group_m)
+                      : launch_one<2, false, kScalePerToken>(grid, stream, map_a, map_b, a, group_m);
+  if (stage == 1) return launch_one<1, false, kScaleBlock128>(grid, stream, map_a, map_b, a, group_m);
+  if (a.row_dst != nullptr) return launch_one<2, true, kScaleBlock128>(grid, stream, map_a, map_b, a, group_m);
+  return launch_one<2, false, kScaleBlock128>(grid, stream, map_a, map_b, a, group_m);
 }
 
 }  // namespace flymoe

@@ -263,9 +263,12 @@ extern "C" int64_t flymoe_moe_sorting_workspace_elems(int num_tokens, int num_ex
                                                       int unit_size) {
   (void)unit_size;
   if (num_tokens < 0 || num_experts < 1 || topk < 1) return 0;
+  const int64_t pairs = int64_t(num_tokens) * topk;
+  if (pairs >= (int64_t(1) << 30))           // beyond what flymoe_moe_sorting accepts: size from the segment length
+    return ((pairs + flymoe::kSegPairs - 1) / flymoe::kSegPairs) * num_experts + num_experts;
   int seg_len, nseg;
   bool one_block;
-  flymoe::sort_plan(num_tokens * topk, &seg_len, &nseg, &one_block);
+  flymoe::sort_plan(int(pairs), &seg_len, &nseg, &one_block);
   if (one_block) return 0;
   return int64_t(nseg) * num_experts + num_experts;
 }
@@ -280,6 +283,9 @@ extern "C" int flymoe_moe_sorting(const int32_t* topk_ids, const float* topk_wei
   FLYMOE_REQUIRE(num_tokens >= 0 && num_tokens < (1 << 24), "sorting: num_tokens must be in [0, 2^24)");
   FLYMOE_REQUIRE(num_experts >= 1 && num_experts <= kMaxExperts, "sorting: num_experts must be in [1, 1024]");
   FLYMOE_REQUIRE(topk >= 1 && topk <= 255, "sorting: topk must be in [1, 255]");
+  // the padded rows total at most pairs + E*(unit-1), which fits the caller's pairs + E*unit - topk
+  // buffer only when topk <= E (a token routes to distinct experts)
+  FLYMOE_REQUIRE(topk <= num_experts, "sorting: topk must not exceed num_experts");
   FLYMOE_REQUIRE(unit_size >= 1, "sorting: unit_size must be >= 1");
   FLYMOE_REQUIRE(int64_t(num_tokens) * topk < (int64_t(1) << 30), "sorting: too many (token, slot) pairs");
   FLYMOE_REQUIRE(sorted_ids && sorted_weights && sorted_expert_ids && num_valid_ids, "sorting: null output");

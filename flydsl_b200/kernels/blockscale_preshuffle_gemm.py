@@ -23,18 +23,9 @@ import functools
 import torch
 
 from .. import _lib
-from .moe_blockscale_2stage import _FP8_DTYPES, _plain_weight
+from .moe_blockscale_2stage import _FP8_DTYPES, _LauncherScratch, _plain_weight, _resolve_scratch
 
 _OUT = {"bf16": torch.bfloat16, "fp16": torch.float16}
-_workspaces: dict = {}
-
-
-def _workspace(device, elems: int) -> torch.Tensor:
-    buf = _workspaces.get(device)
-    if buf is None or buf.numel() < elems:
-        buf = torch.empty(max(elems, 1), dtype=torch.int32, device=device)
-        _workspaces[device] = buf
-    return buf
 
 
 @functools.lru_cache(maxsize=1024)
@@ -63,8 +54,12 @@ def compile_blockscale_preshuffle_gemm(*, M: int, N: int, K: int, tile_m: int, t
         raise ValueError(f"w_layout must be 'preshuffle16x16' or 'plain', got {w_layout!r}")
     out_torch = _OUT[out_dtype]
     out_code = _lib.DTYPE_CODE[out_torch]
+    # routing tables of the grouped kernel (identity routing): one buffer per (device, stream) of this
+    # launcher, sized for M at its first call on that stream; ``workspace=`` takes the caller's own
+    scratch = _LauncherScratch(torch.int32)
+    ws_elems = int(_lib.load().flymoe_blockscale_gemm_workspace_elems(M, tile_m)) if M > 0 else 1
 
-    def launch_gemm(arg_c, arg_a, arg_b, arg_scale_a, arg_scale_b, i32_m, i32_n, stream=None):
+    def launch_gemm(arg_c, arg_a, arg_b, arg_scale_a, arg_scale_b, i32_m, i32_n, stream=None, *, workspace=None):
         m, n = int(i32_m), int(i32_n)
         if n != N:
             raise ValueError(f"launcher built for N={N}; called with N={n}")
@@ -78,7 +73,7 @@ def compile_blockscale_preshuffle_gemm(*, M: int, N: int, K: int, tile_m: int, t
         _lib.require_cuda("arg_scale_b", arg_scale_b, (torch.float32,), ((N + 127) // 128) * (K // 128))
         s = _lib.stream_handle(stream)
         b_plain = _plain_weight(arg_b, N, K, w_layout, stream)
-        ws = _workspace(arg_a.device, int(lib.flymoe_blockscale_gemm_workspace_elems(m, tile_m)))
+        ws = _resolve_scratch(scratch, workspace, "workspace", arg_a.device, s, ws_elems)
         sa_stride = arg_scale_a.numel() // (K // 128)          # the transposed layout's row length (>= m)
         _lib.check(lib.flymoe_blockscale_gemm(_lib.ptr(arg_c), _lib.ptr(arg_a), _lib.ptr(arg_scale_a), sa_stride,
                                               _lib.ptr(b_plain), _lib.ptr(arg_scale_b), _lib.ptr(ws), ws.numel(),

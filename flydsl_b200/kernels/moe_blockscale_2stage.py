@@ -35,7 +35,6 @@ from __future__ import annotations
 import functools
 import logging
 import weakref
-from collections import OrderedDict
 
 import torch
 
@@ -44,32 +43,62 @@ from .. import _lib
 logger = logging.getLogger("flydsl_b200")
 
 _FP8_DTYPES = (torch.float8_e4m3fn, torch.uint8)
+_BYTE_DTYPES = _FP8_DTYPES + (torch.int8,)     # anything the one-byte weight re-layout can move
 _OUT16 = {"f16": torch.float16, "bf16": torch.bfloat16}
 _IMPL = {"tcgen05": _lib.IMPL_TCGEN05, "simt": _lib.IMPL_SIMT}
 _TILE_M = (16, 32, 64, 128)
 
 
 # ------------------------------------------------------------------------- weight layout
-_plain_cache: "OrderedDict[tuple, tuple]" = OrderedDict()
-_PLAIN_CACHE_MAX = 8
+# Row-major copies of preshuffled weights, one per live weight tensor.  An entry lives exactly as
+# long as the storage it was converted from (a finalizer on the storage object removes it), so a
+# model with any number of layers converts every weight once, at its first launch or ahead of time
+# with ``prepare_weight``.  The default layout therefore doubles the memory of every weight that
+# is launched with it; ``w_layout="plain"`` (or converting at load time and dropping the
+# preshuffled tensor) avoids the second copy.
+_plain_cache: dict = {}
 
 
 def unshuffle_weight(w: torch.Tensor, rows: int, cols: int, stream=None) -> torch.Tensor:
-    """Return a row-major copy of a 16x16-preshuffled e4m3 weight ([rows, cols] bytes)."""
-    _lib.require_cuda("w", w, _FP8_DTYPES, rows * cols)
+    """Return a row-major copy of a 16x16-preshuffled one-byte weight ([rows, cols] bytes)."""
+    _lib.require_cuda("w", w, _BYTE_DTYPES, rows * cols)
     out = torch.empty(rows * cols, dtype=w.dtype, device=w.device)
+    _order_after_current_stream(stream, w.device)
     _lib.check(_lib.load().flymoe_shuffle_weight(_lib.ptr(w), _lib.ptr(out), rows, cols, 1,
                                                  _lib.stream_handle(stream)), "shuffle_weight")
     return out
 
 
 def shuffle_weight(w: torch.Tensor, rows: int, cols: int, stream=None) -> torch.Tensor:
-    """Row-major e4m3 weight -> the reference's 16x16 preshuffle order."""
-    _lib.require_cuda("w", w, _FP8_DTYPES, rows * cols)
+    """Row-major one-byte weight -> the reference's 16x16 preshuffle order."""
+    _lib.require_cuda("w", w, _BYTE_DTYPES, rows * cols)
     out = torch.empty(rows * cols, dtype=w.dtype, device=w.device)
+    _order_after_current_stream(stream, w.device)
     _lib.check(_lib.load().flymoe_shuffle_weight(_lib.ptr(w), _lib.ptr(out), rows, cols, 0,
                                                  _lib.stream_handle(stream)), "shuffle_weight")
     return out
+
+
+def _order_after_current_stream(stream, device) -> None:
+    """A tensor that torch has just allocated is only safe to touch in the order of torch's current
+    stream; when the caller launches on another stream, make that stream wait for the current one."""
+    if stream is None:
+        return
+    cur = torch.cuda.current_stream(device)
+    h = _lib.stream_handle(stream)
+    if h == cur.cuda_stream:
+        return
+    ev = torch.cuda.Event()
+    ev.record(cur)
+    torch.cuda.ExternalStream(h, device=device).wait_event(ev)
+
+
+def prepare_weight(w: torch.Tensor, rows: int, cols: int, stream=None) -> torch.Tensor:
+    """Convert a 16x16-preshuffled weight to row-major now (e.g. at model load) and remember the
+    copy for the lifetime of ``w``: launchers built with ``w_layout="preshuffle16x16"`` then find
+    it and only enqueue kernels.  Returns the row-major tensor, which may also be passed to
+    launchers built with ``w_layout="plain"`` in place of ``w``."""
+    return _plain_weight(w, rows, cols, "preshuffle16x16", stream)
 
 
 def _plain_weight(w: torch.Tensor, rows: int, cols: int, layout: str, stream) -> torch.Tensor:
@@ -81,13 +110,17 @@ def _plain_weight(w: torch.Tensor, rows: int, cols: int, layout: str, stream) ->
     key = (w.data_ptr(), w.numel(), w.device.index, rows, cols)
     hit = _plain_cache.get(key)
     if hit is not None and hit[0] == w._version and hit[2]() is storage:
-        _plain_cache.move_to_end(key)
         return hit[1]
     plain = unshuffle_weight(w, rows, cols, stream)
     _plain_cache[key] = (w._version, plain, weakref.ref(storage))
-    while len(_plain_cache) > _PLAIN_CACHE_MAX:
-        _plain_cache.popitem(last=False)
+    weakref.finalize(storage, _drop_plain, key, id(plain))
     return plain
+
+
+def _drop_plain(key, plain_id) -> None:
+    hit = _plain_cache.get(key)
+    if hit is not None and id(hit[1]) == plain_id:
+        del _plain_cache[key]
 
 
 def clear_weight_cache() -> None:
@@ -95,15 +128,35 @@ def clear_weight_cache() -> None:
 
 
 # ------------------------------------------------------------------------- scratch
-_scratch: dict = {}
+class _LauncherScratch:
+    """Device scratch owned by ONE compiled launcher: one buffer per (device, stream), so two
+    launchers -- or one launcher used on two streams -- never share it.  A buffer is created at the
+    first call on that stream (or ahead of time with ``reserve``) and replaced only by a larger one;
+    replaced buffers stay referenced, because kernels already enqueued on a stream torch does not
+    track may still read them.  Callers that must not allocate on the call path (graph capture,
+    a fixed memory budget) pass their own buffer to the launcher instead."""
+
+    def __init__(self, dtype):
+        self.dtype = dtype
+        self.bufs: dict = {}
+        self.retired: list = []
+
+    def get(self, device, stream_handle: int, numel: int) -> torch.Tensor:
+        key = (device.index, stream_handle)
+        buf = self.bufs.get(key)
+        if buf is None or buf.numel() < numel:
+            if buf is not None:
+                self.retired.append(buf)
+            buf = torch.empty(max(numel, 1), dtype=self.dtype, device=device)
+            self.bufs[key] = buf
+        return buf
 
 
-def _gather_buffer(device, nbytes: int) -> torch.Tensor:
-    buf = _scratch.get(device)
-    if buf is None or buf.numel() < nbytes:
-        buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
-        _scratch[device] = buf
-    return buf
+def _resolve_scratch(scratch: _LauncherScratch, given, name: str, device, stream_handle: int, numel: int):
+    if given is None:
+        return scratch.get(device, stream_handle, numel)
+    _lib.require_cuda(name, given, (scratch.dtype,), numel)
+    return given
 
 
 def _check_common(model_dim, inter_dim, experts, topk, tile_m, tile_n, tile_k, scale_block_k, w_layout,
@@ -154,10 +207,12 @@ def compile_moe_blockscale_gemm1(*, model_dim: int, inter_dim: int, experts: int
     out_torch = _FP8_DTYPES if fp8_out else (_OUT16[out_dtype],)
     sorted_rows = row_layout == "sorted"
     wrows = experts * 2 * inter_dim
+    scratch = _LauncherScratch(torch.uint8)
 
     def launch_moe_blockscale_gemm1(arg_out, arg_x, arg_w, arg_scale_x, arg_scale_w, arg_sorted_token_ids,
                                     arg_expert_ids, arg_sorted_weights, arg_max_token_ids, tokens_in,
-                                    inter_in, k_in, size_expert_ids_in, stream=None, *, arg_out_scale=None):
+                                    inter_in, k_in, size_expert_ids_in, stream=None, *, arg_out_scale=None,
+                                    gather_buffer=None):
         tokens, blocks = int(tokens_in), int(size_expert_ids_in)
         if int(inter_in) != inter_dim or int(k_in) != model_dim:
             raise ValueError(f"launcher built for inter_dim={inter_dim}, model_dim={model_dim}; "
@@ -189,7 +244,7 @@ def compile_moe_blockscale_gemm1(*, model_dim: int, inter_dim: int, experts: int
         x_layout = _lib.ROWS_SORTED if sorted_rows else _lib.ROWS_BY_TOKEN
         x_ptr = _lib.ptr(arg_x)
         if impl_code == _lib.IMPL_TCGEN05 and not sorted_rows:
-            gbuf = _gather_buffer(arg_x.device, cap_rows * model_dim)
+            gbuf = _resolve_scratch(scratch, gather_buffer, "gather_buffer", arg_x.device, h, cap_rows * model_dim)
             _lib.check(lib.flymoe_gather_rows(x_ptr, _lib.ptr(gbuf), _lib.ptr(arg_sorted_token_ids),
                                               _lib.ptr(arg_max_token_ids), tokens, topk, model_dim,
                                               _lib.ROWS_BY_TOKEN, cap_rows, h), "gather_rows")
@@ -203,6 +258,8 @@ def compile_moe_blockscale_gemm1(*, model_dim: int, inter_dim: int, experts: int
             out_code, x_layout, _lib.ROWS_SORTED if sorted_rows else _lib.ROWS_BY_TOKEN,
             _lib.ROWS_SORTED if sorted_rows else _lib.ROWS_BY_PAIR, impl_code, h), "moe_gemm1")
 
+    launch_moe_blockscale_gemm1.reserve = lambda tokens, blocks, device, stream=None: scratch.get(
+        torch.device(device), _lib.stream_handle(stream), int(blocks) * tile_m * model_dim)
     return launch_moe_blockscale_gemm1
 
 
@@ -236,10 +293,11 @@ def compile_moe_blockscale_gemm2(*, model_dim: int, inter_dim: int, experts: int
     sorted_rows = row_layout == "sorted"
     wrows = experts * model_dim
     acc = 1 if accumulate else 0
+    scratch = _LauncherScratch(torch.uint8)
 
     def launch_moe_blockscale_gemm2(arg_out, arg_x, arg_w, arg_scale_x, arg_scale_w, arg_sorted_token_ids,
                                     arg_expert_ids, arg_sorted_weights, arg_num_valid_ids, tokens_in, n_in,
-                                    k_in, size_expert_ids_in, stream=None):
+                                    k_in, size_expert_ids_in, stream=None, *, gather_buffer=None):
         tokens, blocks = int(tokens_in), int(size_expert_ids_in)
         if int(n_in) != model_dim or int(k_in) != inter_dim:
             raise ValueError(f"launcher built for model_dim={model_dim}, inter_dim={inter_dim}; "
@@ -265,7 +323,7 @@ def compile_moe_blockscale_gemm2(*, model_dim: int, inter_dim: int, experts: int
         a_layout = _lib.ROWS_SORTED if sorted_rows else _lib.ROWS_BY_PAIR
         a_ptr = _lib.ptr(arg_x)
         if impl_code == _lib.IMPL_TCGEN05 and not sorted_rows:
-            gbuf = _gather_buffer(arg_x.device, cap_rows * inter_dim)
+            gbuf = _resolve_scratch(scratch, gather_buffer, "gather_buffer", arg_x.device, h, cap_rows * inter_dim)
             _lib.check(lib.flymoe_gather_rows(a_ptr, _lib.ptr(gbuf), _lib.ptr(arg_sorted_token_ids),
                                               _lib.ptr(arg_num_valid_ids), tokens, topk, inter_dim,
                                               _lib.ROWS_BY_PAIR, cap_rows, h), "gather_rows")
@@ -278,6 +336,8 @@ def compile_moe_blockscale_gemm2(*, model_dim: int, inter_dim: int, experts: int
             experts, topk, tile_m, 1 if doweight_stage2 else 0, out_code, acc, a_layout,
             _lib.ROWS_SORTED if sorted_rows else _lib.ROWS_BY_PAIR, impl_code, h), "moe_gemm2")
 
+    launch_moe_blockscale_gemm2.reserve = lambda tokens, blocks, device, stream=None: scratch.get(
+        torch.device(device), _lib.stream_handle(stream), int(blocks) * tile_m * inter_dim)
     return launch_moe_blockscale_gemm2
 
 
@@ -320,40 +380,44 @@ class MoeGemm2Mode:
 
 
 class _MoeGemm2ReduceWrapper:
-    """Stage 2 without atomics followed by the top-k reduce; same call signature as stage 2."""
+    """Deterministic stage 2: per-(token, slot) rows without atomics, then the top-k reduce.
+
+    Called with stage 2's own positional arguments (plus ``valid_mask``).  The [tokens*topk,
+    model_dim] rows between the two kernels live in a buffer the wrapper keeps per (device,
+    stream, row count): a call with a shape it has seen before allocates nothing.  Stage 2 writes
+    the row of every (token, slot) pair routed to one of its experts.  With a mask the reduce skips
+    the other rows; without one they are cleared first (``zero_rows``, one memset on the stream), so
+    pairs routed elsewhere add zero -- switch that off when every pair is routed to an expert this
+    launcher holds.
+    """
 
     def __init__(self, gemm2_exe, reduce_exe, topk: int, model_dim: int, out_dtype_str: str = "f16",
-                 use_mask: bool = False):
+                 use_mask: bool = False, zero_rows: bool = True):
         self._gemm2_exe = gemm2_exe
         self._reduce_exe = reduce_exe
-        self._topk = topk
-        self._model_dim = model_dim
-        self._out_dtype_str = out_dtype_str
-        self._use_mask = use_mask
-
-    def _get_torch_dtype(self):
-        return {"f16": torch.float16, "fp16": torch.float16, "bf16": torch.bfloat16,
-                "f32": torch.float32}.get(self._out_dtype_str, torch.float16)
+        self._topk = int(topk)
+        self._model_dim = int(model_dim)
+        self._row_dtype = torch.bfloat16 if out_dtype_str == "bf16" else torch.float16
+        self._use_mask = bool(use_mask)
+        self._rows = _LauncherScratch(self._row_dtype)
+        self._zero_rows = bool(zero_rows) and not self._use_mask
+        self._warned = False
 
     def __call__(self, arg_out, arg_x, arg_w, arg_scale_x, arg_scale_w, arg_sorted_token_ids, arg_expert_ids,
                  arg_sorted_weights, arg_num_valid_ids, tokens_in, n_in, k_in, size_expert_ids_in,
                  valid_mask=None, stream=None):
-        if stream is None:
-            stream = torch.cuda.current_stream()
-        intermediate = torch.empty(tokens_in * self._topk, self._model_dim, device=arg_out.device,
-                                   dtype=self._get_torch_dtype())
-        if not self._use_mask:
-            intermediate.zero_()
-        self._gemm2_exe(intermediate.view(-1), arg_x, arg_w, arg_scale_x, arg_scale_w, arg_sorted_token_ids,
-                        arg_expert_ids, arg_sorted_weights, arg_num_valid_ids, tokens_in, n_in, k_in,
-                        size_expert_ids_in, stream)
-        X = intermediate.view(tokens_in, self._topk, self._model_dim)
-        Y = arg_out.view(tokens_in, self._model_dim)
-        if not self._use_mask:
-            if valid_mask is not None:
-                logging.warning("valid_mask provided but use_mask=False; ignoring valid_mask")
-            valid_mask = torch.empty((0, self._topk), device=arg_out.device, dtype=torch.uint8)
-        self._reduce_exe(X, Y, valid_mask, tokens_in, stream)
+        tokens = int(tokens_in)
+        h = _lib.stream_handle(stream)
+        pair_rows = self._rows.get(arg_out.device, h, tokens * self._topk * self._model_dim)
+        if self._zero_rows:
+            with torch.cuda.stream(torch.cuda.ExternalStream(h, device=arg_out.device)):
+                pair_rows[: tokens * self._topk * self._model_dim].zero_()
+        self._gemm2_exe(pair_rows, arg_x, arg_w, arg_scale_x, arg_scale_w, arg_sorted_token_ids, arg_expert_ids,
+                        arg_sorted_weights, arg_num_valid_ids, tokens, n_in, k_in, size_expert_ids_in, h)
+        if valid_mask is not None and not self._use_mask and not self._warned:
+            logger.warning("this launcher was built without a mask: the valid_mask argument is ignored")
+            self._warned = True
+        self._reduce_exe(pair_rows, arg_out, valid_mask if self._use_mask else None, tokens, h)
 
     @property
     def mode(self) -> str:
@@ -363,8 +427,11 @@ class _MoeGemm2ReduceWrapper:
 def compile_moe_blockscale_gemm2_ex(*, model_dim: int, inter_dim: int, experts: int, topk: int, tile_m: int,
                                     tile_n: int, tile_k: int, doweight_stage2: bool, in_dtype: str = "fp8",
                                     out_dtype: str = "f16", use_cshuffle_epilog: bool | None = None,
-                                    mode: str = MoeGemm2Mode.ATOMIC, valid_mask=None, **extra):
-    """Stage 2 with explicit mode control: "atomic" or "reduce" (no atomics + reduce kernel)."""
+                                    mode: str = MoeGemm2Mode.ATOMIC, valid_mask=None,
+                                    zero_intermediate: bool = True, **extra):
+    """Stage 2 with explicit mode control: "atomic" or "reduce" (no atomics + reduce kernel).
+    ``zero_intermediate=False`` skips clearing the per-pair rows (valid when every pair is routed to
+    one of this launcher's experts)."""
     if in_dtype != "fp8":
         raise ValueError(f"the block-scaled path is FP8-only, got in_dtype={in_dtype!r}")
     common = dict(model_dim=model_dim, inter_dim=inter_dim, experts=experts, topk=topk, tile_m=tile_m,
@@ -379,5 +446,5 @@ def compile_moe_blockscale_gemm2_ex(*, model_dim: int, inter_dim: int, experts: 
         dtype_str = "f16" if out_s in ("f16", "fp16", "half") else "bf16"
         reduce_exe = compile_moe_reduction(topk=topk, model_dim=model_dim, dtype_str=dtype_str, use_mask=use_mask)
         return _MoeGemm2ReduceWrapper(gemm2_exe=gemm2_exe, reduce_exe=reduce_exe, topk=topk, model_dim=model_dim,
-                                      out_dtype_str=dtype_str, use_mask=use_mask)
+                                      out_dtype_str=dtype_str, use_mask=use_mask, zero_rows=zero_intermediate)
     return compile_moe_blockscale_gemm2(accumulate=True, **common)

@@ -34,6 +34,18 @@ extern "C" {
 #define FLYMOE_F16 1
 #define FLYMOE_BF16 2
 #define FLYMOE_E4M3 3
+#define FLYMOE_I8 4
+
+/* how the operands of a grouped GEMM are scaled */
+#define FLYMOE_SCALE_BLOCK128 0  /* activations per (row, 128 K), weights per 128x128 block        */
+#define FLYMOE_SCALE_PER_TOKEN 1 /* one scale per activation row, one per weight row (out column) */
+
+/* values of the device status word (flymoe_device_status); 0 = healthy */
+#define FLYMOE_STATUS_WAIT_FIRST 1        /* 1..7: a bounded wait of the grouped GEMM gave up (role)  */
+#define FLYMOE_STATUS_WAIT_LAST 7
+#define FLYMOE_STATUS_DISPATCH_OVERFLOW 16 /* flymoe_dispatch_rows dropped rows beyond pos_limit      */
+#define FLYMOE_STATUS_ROW_DST_MISALIGNED 17 /* a per-row destination was not 16-byte aligned; dropped */
+#define FLYMOE_STATUS_SELFTEST_TIMEOUT 99 /* flymoe_selftest_bounded_wait ran out, as it must        */
 
 /* row layouts of an activation matrix that is indexed through the sorted-id list */
 #define FLYMOE_ROWS_BY_TOKEN 0 /* row = token id                     (stage-1 input)   */
@@ -146,9 +158,37 @@ int flymoe_moe_gemm2(void* out, const void* a2, const float* scale_a, int64_t sa
                      int out_dtype, int accumulate, int a_layout, int a_scale_layout, int impl,
                      void* stream);
 
+/* The two stages with ONE scale per activation row and ONE per weight row (output column)
+ * instead of 128-wide blocks: the per-token / per-channel family.
+ * Replace kernels/moe_gemm_2stage.py:90-108 (compile_moe_gemm1, launcher :1730-1745) and
+ * :1780-1796 (compile_moe_gemm2, launcher :3151-3166) for in_dtype "fp8", "int8" and
+ * "int8smooth".  in_dtype E4M3 or I8 (signed 8-bit operands, exact int32 accumulation).
+ * Stage 1: x [T,H] (x_layout BY_TOKEN, SIMT only), [T*k,H] (BY_PAIR: "int8smooth", SIMT only) or
+ * the gathered sorted rows (SORTED); scale_x f32 [T] (x_scale_layout BY_TOKEN), [T*k] (BY_PAIR)
+ * or per sorted row; w [E,2I,H] row-major, scale_w f32 [E*2I]; out F16/BF16 [T*k,I]
+ * (out_layout BY_PAIR) or sorted rows.  Stage 2: a2 [T*k,I] / sorted rows, scale_a f32 [T*k] /
+ * per sorted row, w [E,H,I], scale_w f32 [E*H]; out as flymoe_moe_gemm2.  The K range is
+ * accumulated in TMEM and each tile is scaled once: out = (sum_k a*w) * scale_a[row] * scale_w[col].
+ * scale_w must be 16-byte aligned. */
+int flymoe_moe_gemm1_pertoken(void* out, const void* x, const float* scale_x, const void* w,
+                              const float* scale_w, const int32_t* sorted_ids,
+                              const int32_t* sorted_expert_ids, const float* sorted_weights,
+                              const int32_t* num_valid_ids, int num_tokens, int inter_dim,
+                              int model_dim, int size_expert_ids, int experts, int topk, int tile_m,
+                              int doweight, int in_dtype, int out_dtype, int x_layout,
+                              int x_scale_layout, int out_layout, int impl, void* stream);
+int flymoe_moe_gemm2_pertoken(void* out, const void* a2, const float* scale_a, const void* w,
+                              const float* scale_w, const int32_t* sorted_ids,
+                              const int32_t* sorted_expert_ids, const float* sorted_weights,
+                              const int32_t* num_valid_ids, int num_tokens, int model_dim,
+                              int inter_dim, int size_expert_ids, int experts, int topk, int tile_m,
+                              int doweight, int in_dtype, int out_dtype, int accumulate, int a_layout,
+                              int a_scale_layout, int impl, void* stream);
+
 /* Stage 2 with a caller-given destination per output row: row_dst[t*topk+s] is the byte
  * address the H out_dtype (F16/BF16) values of that (token, slot) row are stored to, 0 drops
- * the row.  Addresses must be 16-byte aligned and may lie in another GPU's memory that is
+ * the row.  Addresses must be 16-byte aligned (a misaligned one drops the row and sets the
+ * device status word to FLYMOE_STATUS_ROW_DST_MISALIGNED) and may lie in another GPU's memory that is
  * mapped into this process with peer access: in the expert-parallel layer each rank
  * stores its expert outputs straight into the buffers of the ranks that own the tokens, so
  * the combine transfer rides on stage 2's epilogue instead of a separate all-to-all.
@@ -197,6 +237,14 @@ int flymoe_blockscale_gemm(void* c, const void* a, const float* scale_a, int64_t
                            const void* b, const float* scale_b, int32_t* workspace,
                            int64_t workspace_elems, int m, int n, int k, int tile_m, int out_dtype,
                            void* stream);
+
+/* Test hook for the bounded waits: launches one thread that waits, with the same bounded
+ * wait every kernel of the library uses, on a barrier nobody arrives at.  After limit_ns
+ * nanoseconds (at most 1e8) the wait gives up, the kernel returns normally and the device
+ * status word reads FLYMOE_STATUS_SELFTEST_TIMEOUT once.  Nothing faults or hangs; the
+ * context stays usable.  The reference spins without a bound
+ * (kernels/custom_all_reduce_kernel.py:236-246) and has no counterpart. */
+int flymoe_selftest_bounded_wait(int64_t limit_ns, void* stream);
 
 /* Caps the persistent grid of the two GEMM stages at max_ctas CTAs (0 restores one CTA per SM).
  * Process-wide.  For callers that run communication kernels next to the GEMMs (the

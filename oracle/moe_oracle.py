@@ -26,6 +26,10 @@ Reference locations each function follows (paths inside the reference project):
 * stage 2         tests/kernels/test_moe_blockscale.py:115-150
 * top-k reduce    tests/kernels/test_moe_reduce.py:88-93
 * dense GEMM      tests/kernels/test_blockscale_preshuffle_gemm.py:101-125
+* per-token-scale family (one scale per activation row / weight row)
+                  tests/kernels/test_ref.py:91-165 (stage 1), :168-239 (stage 2),
+                  quantisation of its inputs tests/kernels/test_moe_gemm.py:446-450,
+                  :463-488 (fp8, int8, per-(token, slot) "int8smooth")
 
 Differences from the reference text, all value-preserving: weights are
 dequantised one expert at a time (the reference expands every expert to fp32
@@ -245,6 +249,58 @@ def moe_layer(logits, xq, x_scale, w1q, w1_scale, w2q, w2_scale, topk: int,
     o2 = stage2(a2q, a2s, w2q, w2_scale, idx, w, H)
     return {"topk_weights": w, "topk_ids": idx, "tei": tei, "out1": o1,
             "a2q": a2q, "a2_scale": a2s, "out": o2.to(out_dtype), "out_f32": o2}
+
+
+# --------------------------------------------------------------------------- per-token-scale family
+def quant_rows(x: torch.Tensor, quant_dtype=FP8):
+    """One scale per row of the last dim: (q, scale [..., 1]); int8 uses dtype max 127."""
+    dmax = 127.0 if quant_dtype == torch.int8 else None
+    return pertoken_quant(x, quant_dtype=quant_dtype, dtype_max=dmax)
+
+
+def pertoken_stage1(x_q, scale_x, w1_q, scale_w1, topk_ids, topk_weights, inter_dim: int,
+                    doweight_stage1: bool = False):
+    """silu(x W1g^T) * (x W1u^T) with x = x_q * scale_x (per row) and W = w_q * scale_w (per row).
+
+    x_q [T,K] (or [T,k,K] when every (token, slot) pair brings its own row) of e4m3/int8, scale_x
+    [T,1] ([T,k,1]); w1_q [E,2I,K], scale_w1 [E,2I,1].  Returns f32 [T,k,I]."""
+    ids = torch.as_tensor(topk_ids).to(torch.int64)
+    T, k = ids.shape
+    E = w1_q.shape[0]
+    x = x_q.to(torch.float32) * scale_x
+    out = torch.zeros((T, k, inter_dim), dtype=torch.float32)
+    for e in range(E):
+        tok, slot = (ids == e).nonzero(as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        w = w1_q[e].to(torch.float32) * scale_w1[e]
+        rows = x[tok] if x.dim() == 2 else x[tok, slot]
+        y2 = F.linear(rows, w)
+        y = F.silu(y2[:, :inter_dim]) * y2[:, inter_dim:]
+        if doweight_stage1:
+            y = y * torch.as_tensor(topk_weights)[tok, slot].unsqueeze(-1)
+        out[tok, slot] = y
+    return out
+
+
+def pertoken_stage2(a2_q, scale_a2, w2_q, scale_w2, topk_ids, topk_weights, model_dim: int,
+                    doweight_stage2: bool = True, reduce: bool = True):
+    """out[t] = sum_s (w[t,s]) * (a2[t,s] W2_e^T); a2_q [T,k,I] with scale_a2 [T,k,1], w2_q [E,H,I]
+    with scale_w2 [E,H,1].  Returns f32 [T,H] (or [T,k,H] with ``reduce=False``)."""
+    ids = torch.as_tensor(topk_ids).to(torch.int64)
+    T, k = ids.shape
+    E = w2_q.shape[0]
+    a2 = a2_q.to(torch.float32) * scale_a2
+    out = torch.zeros((T, k, model_dim), dtype=torch.float32)
+    for e in range(E):
+        tok, slot = (ids == e).nonzero(as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        y = F.linear(a2[tok, slot], w2_q[e].to(torch.float32) * scale_w2[e])
+        if doweight_stage2:
+            y = y * torch.as_tensor(topk_weights)[tok, slot].unsqueeze(-1)
+        out[tok, slot] = y
+    return out.sum(dim=1) if reduce else out
 
 
 # --------------------------------------------------------------------------- dense GEMM

@@ -18,6 +18,9 @@ Lifted functions (reference paths):
       torch_stage2_blockscale_ref, torch_moe_blockscale_ref
   tests/kernels/test_moe_sorting.py:    moe_sorting_reference
   tests/utils.py (imported directly):   pertoken_quant, shuffle_weight
+  tests/kernels/test_ref.py:            torch_moe_gemm1, torch_moe_gemm2 and their helpers (the text
+      ``device="cuda"`` becomes ``device="cpu"`` and the ``is_cuda`` assertion is dropped while lifting,
+      since the fixtures are generated without a GPU; nothing else changes)
 Gating has no reference function; the fixture stores the result of the reference test's
 inline expression (softmax -> topk -> renormalise, test_topk_gating_softmax.py:84-89).
 """
@@ -46,8 +49,13 @@ from flydsl_b200 import workloads as wl  # noqa: E402
 FP8 = torch.float8_e4m3fn
 
 
-def lift(path: Path, names: list[str], extra_globals: dict) -> dict:
-    tree = ast.parse(path.read_text())
+def lift(path: Path, names: list[str], extra_globals: dict, replace: dict | None = None) -> dict:
+    text = path.read_text()
+    for old, new in (replace or {}).items():
+        if old not in text:
+            raise RuntimeError(f"{path}: expected text not found: {old!r}")
+        text = text.replace(old, new)
+    tree = ast.parse(text)
     wanted = [n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name in names]
     missing = set(names) - {n.name for n in wanted}
     if missing:
@@ -83,6 +91,11 @@ def sha(*arrays) -> str:
 def main() -> None:
     if REF is None or not REF.exists():
         raise SystemExit("set FLYMOE_REFERENCE_DIR to the reference checkout")
+    only = set(sys.argv[1:])          # optional: names of the fixtures to (re)write, e.g. moe_pertoken.npz
+
+    def save(name: str, **arrays) -> None:
+        if not only or name in only:
+            np.savez_compressed(HERE / name, **arrays)
     utils = import_file(REF / "tests" / "utils.py", "ref_tests_utils")
     bs = lift(REF / "tests" / "kernels" / "test_moe_blockscale.py",
               ["_expand_blockscale", "torch_stage1_blockscale_ref", "torch_stage2_blockscale_ref",
@@ -99,7 +112,7 @@ def main() -> None:
     q, s = pertoken_quant(xs.view(24, 3, 128), quant_dtype=FP8)
     wq_small = (torch.randn((2, 64, 128), generator=g) * 50).to(FP8)
     shuf = shuffle_weight(wq_small.clone(), layout=(16, 16))
-    np.savez_compressed(HERE / "quant_shuffle.npz", x=xs.numpy(), q=u8(q.view(24, 384)),
+    save("quant_shuffle.npz", x=xs.numpy(), q=u8(q.view(24, 384)),
                         scale=s.view(24, 3).numpy(), w=u8(wq_small), w_shuffled=u8(shuf))
 
     # ------------------------------------------------------------------ sorting
@@ -123,7 +136,7 @@ def main() -> None:
         out[f"c{i}_sorted_ids"], out[f"c{i}_sorted_w"] = a.numpy(), b.numpy()
         out[f"c{i}_sorted_e"], out[f"c{i}_nvalid"] = c.numpy(), d.numpy()
     out["n"] = np.array([len(sort_cases)], dtype=np.int32)
-    np.savez_compressed(HERE / "sorting.npz", **out)
+    save("sorting.npz", **out)
 
     # ------------------------------------------------------------------ gating
     gate_cases = [(64, 8, 2, "f32", True), (64, 256, 8, "f32", True), (33, 128, 6, "bf16", True),
@@ -147,7 +160,7 @@ def main() -> None:
         out[f"g{i}_w"], out[f"g{i}_idx"] = rw.numpy(), ri.to(torch.int32).numpy()
         out[f"g{i}_distinct"] = distinct.numpy()
     out["n"] = np.array([len(gate_cases)], dtype=np.int32)
-    np.savez_compressed(HERE / "gating.npz", **out)
+    save("gating.npz", **out)
 
     # ------------------------------------------------------------------ GEMM stages
     def run_moe(cfg: wl.MoEConfig, store_inputs: bool, fname: str):
@@ -185,7 +198,7 @@ def main() -> None:
         if store_inputs:
             rec.update({"logits": logits.numpy(), "xq": u8(xq), "x_scale": xs_.numpy(), "w1q": u8(w1q),
                         "w1_scale": w1s.numpy(), "w2q": u8(w2q), "w2_scale": w2s.numpy()})
-        np.savez_compressed(HERE / fname, **rec)
+        save(fname, **rec)
 
     run_moe(wl.MoEConfig("mini", 16, 256, 128, 4, 2, 7), True, "moe_mini.npz")
     run_moe(wl.CONFIGS["c1"], False, "moe_c1.npz")
@@ -205,7 +218,33 @@ def main() -> None:
         out.update({f"x{i}": u8(x), f"w{i}": u8(w), f"x_scale{i}": x_scale.numpy(), f"w_scale{i}": w_scale.numpy(),
                     f"c{i}": c.numpy()})
     out["n_cases"] = np.array([3], dtype=np.int32)
-    np.savez_compressed(HERE / "blockscale_gemm.npz", **out)
+    save("blockscale_gemm.npz", **out)
+    # ------------------------------------------------------------------ per-token-scale MoE family
+    pt = lift(REF / "tests" / "kernels" / "test_ref.py",
+              ["_detect_scale_kind", "_logical_k", "_dequant", "torch_moe_gemm1", "torch_moe_gemm2"],
+              {"torch": torch, "F": F, "_FP4_DTYPES": (torch.uint8,)},
+              replace={'device="cuda"': 'device="cpu"', "assert a2_q.is_cuda and w2_q.is_cuda": "pass"})
+    from tests.helpers import pertoken_inputs
+    out = {}
+    cases = [("fp8", 64, 256, 128, 4, 2, False), ("int8", 64, 256, 128, 4, 2, False),
+             ("int8smooth", 33, 256, 128, 4, 2, False), ("fp8", 129, 512, 256, 8, 2, True)]
+    for i, (in_dtype, T, H, I, E, k, doweight1) in enumerate(cases):
+        qd = FP8 if in_dtype == "fp8" else torch.int8
+        xq, sx, w1q, sw1, w2q, sw2, ti, tw = pertoken_inputs(in_dtype, T, H, I, E, k, 900 + i, pertoken_quant)
+        o1 = pt["torch_moe_gemm1"](xq, w1q.view(E * 2 * I, H), sx, sw1.view(E * 2 * I, 1), ti, tw, I, doweight1)
+        a2q, sa2 = pertoken_quant(o1, quant_dtype=qd)
+        o2 = pt["torch_moe_gemm2"](a2q, w2q, sa2, sw2.view(E, H, 1), ti, tw, H, not doweight1)
+        out.update({f"p{i}_cfg": np.array([T, H, I, E, k, int(doweight1), 900 + i], dtype=np.int32),
+                    f"p{i}_dtype": np.array([in_dtype]),
+                    f"p{i}_input_sha": np.array([sha(u8(xq), sx.numpy(), u8(w1q), sw1.numpy(), u8(w2q), sw2.numpy(),
+                                                     ti.numpy(), tw.numpy())]),
+                    f"p{i}_out1": o1.numpy(), f"p{i}_a2q": u8(a2q), f"p{i}_sa2": sa2.numpy(), f"p{i}_out2": o2.numpy()})
+        if i == 0:     # the first case also carries its inputs; the others are regenerated from their seeds
+            out.update({f"p{i}_xq": u8(xq), f"p{i}_sx": sx.numpy(), f"p{i}_w1q": u8(w1q), f"p{i}_sw1": sw1.numpy(),
+                        f"p{i}_w2q": u8(w2q), f"p{i}_sw2": sw2.numpy(), f"p{i}_ids": ti.numpy(), f"p{i}_tw": tw.numpy()})
+    out["n"] = np.array([len(cases)], dtype=np.int32)
+    save("moe_pertoken.npz", **out)
+
     for f in sorted(HERE.glob("*.npz")):
         print(f.name, f.stat().st_size)
 

@@ -49,3 +49,31 @@ def fast_sort_inputs(T, E, k, seed, device="cpu"):
     ids = torch.topk(scores, k, dim=1).indices.to(torch.int32)
     w = torch.rand((T, k), generator=g, dtype=torch.float32)
     return ids.to(device), w.to(device)
+
+
+def pertoken_inputs(in_dtype, T, H, I, E, k, seed, quant):
+    """Seeded inputs of the per-token-scale MoE family, following the reference test's recipe
+    (tests/kernels/test_moe_gemm.py:380-400, :446-488 in the reference project): randn activations,
+    randn/10 weights, routing = top-k of a softmax of random scores.  ``quant(x, quant_dtype=...)`` is
+    the row quantiser (the reference's own when the fixtures are generated, the oracle's in the tests).
+    Returns xq ([T,H], or [T,k,H] for "int8smooth"), sx, w1q [E,2I,H], sw1, w2q [E,H,I], sw2, ids, weights."""
+    g = torch.Generator().manual_seed(seed)
+    qd = FP8 if in_dtype == "fp8" else torch.int8
+    x = torch.randn((T, H), generator=g)
+    w1 = torch.randn((E, 2 * I, H), generator=g) / 10
+    w2 = torch.randn((E, H, I), generator=g) / 10
+    score = torch.softmax(torch.randn((T, E), generator=g), dim=1)
+    tw, ti = torch.topk(score, k, dim=1)
+    tw = tw.to(torch.float32)
+    if in_dtype == "int8smooth":
+        smooth = 0.75 + 0.5 * torch.rand((E, H), generator=g)
+        xr = x[:, None, :] * smooth[ti.to(torch.int64)]
+        amax = xr.abs().amax(dim=-1, keepdim=True)
+        sx = amax / 127.0
+        sx[sx == 0] = 1.0
+        xq = (xr / sx).to(torch.int8)                       # [T, k, H], scales [T, k, 1]
+    else:
+        xq, sx = quant(x, quant_dtype=qd)
+    w1q, sw1 = quant(w1, quant_dtype=qd)
+    w2q, sw2 = quant(w2, quant_dtype=qd)
+    return xq, sx, w1q, sw1, w2q, sw2, ti.to(torch.int32), tw

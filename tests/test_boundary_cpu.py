@@ -9,6 +9,7 @@ import torch
 from flydsl_b200 import _lib
 from flydsl_b200.kernels import moe_blockscale_2stage as bs
 from flydsl_b200.kernels.blockscale_preshuffle_gemm import compile_blockscale_preshuffle_gemm
+from flydsl_b200.kernels import moe_gemm_2stage as pt
 from flydsl_b200.kernels import moe_sorting_kernel as srt
 from flydsl_b200.kernels import topk_gating_softmax_kernel as gat
 
@@ -121,3 +122,35 @@ def test_dense_blockscale_gemm_argument_rules():
         exe(z, z, z, z, z, 4, 7168)
     with pytest.raises(ValueError, match="built for N"):
         exe(z, z, z, z, z, 4, 1024)
+
+
+def test_pertoken_builder_rules(lib):
+    base = dict(model_dim=256, inter_dim=128, experts=4, topk=2, tile_m=16, tile_n=64, tile_k=128)
+    for bad in ("fp16", "bf16", "int4", "int4_bf16"):
+        with pytest.raises(ValueError, match="not built"):
+            pt.compile_moe_gemm1(doweight_stage1=False, in_dtype=bad, **base)
+    with pytest.raises(ValueError, match="in_dtype must be one of"):
+        pt.compile_moe_gemm2(doweight_stage2=True, in_dtype="fp6", **base)
+    with pytest.raises(ValueError, match="only supports out_dtype"):
+        pt.compile_moe_gemm2(doweight_stage2=True, out_dtype="f32", accumulate=False, **base)
+    with pytest.raises(ValueError, match="split-K"):
+        pt.compile_moe_gemm1(doweight_stage1=False, k_batch=2, **base)
+    assert pt.compile_moe_gemm2_ex(doweight_stage2=True, mode=pt.MoeGemm2Mode.REDUCE, in_dtype="int8", **base).mode == "reduce"
+    import kernels.moe_gemm_2stage as shim                      # the reference's import path
+    assert shim.compile_moe_gemm1 is pt.compile_moe_gemm1
+    # C ABI: int8 operands only with per-token scaling, e4m3 output only with block scaling
+    rc = lib.flymoe_moe_gemm1_pertoken(None, None, None, None, None, None, None, None, None,
+                                       4, 128, 256, 1, 2, 2, 16, 0, _lib.I8, _lib.E4M3, 2, 0, 1, 0, None)
+    assert rc == -1 and b"out_dtype" in lib.flymoe_last_error()
+    rc = lib.flymoe_moe_gemm2_pertoken(None, None, None, None, None, None, None, None, None,
+                                       4, 256, 128, 1, 2, 2, 16, 1, _lib.F16, _lib.F16, 1, 2, 1, 0, None)
+    assert rc == -1 and b"in_dtype" in lib.flymoe_last_error()
+    rc = lib.flymoe_selftest_bounded_wait(0, None)
+    assert rc == -1 and b"limit_ns" in lib.flymoe_last_error()
+
+
+def test_sorting_rejects_topk_above_expert_count(lib):
+    rc = lib.flymoe_moe_sorting(None, None, None, None, None, None, None, 0, None, None, 0, 4, 8, 9, 32, None)
+    assert rc == -1 and b"topk" in lib.flymoe_last_error()
+    # the pair count is formed in 64 bits: no wrap-around for a huge (tokens, topk) product
+    assert lib.flymoe_moe_sorting_workspace_elems((1 << 24) - 1, 1024, 255, 32) > (1 << 31)

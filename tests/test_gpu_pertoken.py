@@ -1,0 +1,141 @@
+"""GPU parity of the per-token / per-channel-scale MoE family (kernels.moe_gemm_2stage) against
+the CPU oracle, called through the reference's launcher signatures
+(kernels/moe_gemm_2stage.py:1730-1745 and :3151-3166) on the shapes of the reference's own test
+(tests/kernels/test_moe_gemm.py:1661-1672: S, M and the aiter-style L).  The oracle is pinned to
+the reference's torch_moe_gemm1/2 by tests/golden/moe_pertoken.npz.  Bars: 16-bit and fp32
+outputs within rtol 2e-2 / atol 2e-2 (16-bit atomics: plus one rounding step of the largest sum)."""
+import pytest
+import torch
+
+from flydsl_b200.kernels import moe_gemm_2stage as pt
+from flydsl_b200.kernels.moe_blockscale_2stage import shuffle_weight
+from flydsl_b200.kernels.moe_sorting_kernel import moe_sorting_flydsl
+from oracle import moe_oracle as orc
+from tests import helpers as hp
+from tests.gpu_common import assert_close
+
+pytestmark = pytest.mark.gpu
+RTOL, ATOL = 2e-2, 2e-2
+
+#            tokens H     I     E   k  tile_m
+SHAPES = {"S": (64, 256, 128, 4, 2, 16), "M": (129, 1024, 256, 8, 2, 32), "L": (333, 4096, 2048, 17, 9, 64),
+          "T128": (700, 512, 256, 4, 2, 128)}
+_cache = {}
+
+
+def inputs(shape, in_dtype):
+    key = (shape, in_dtype)
+    if key not in _cache:
+        T, H, I, E, k, _ = SHAPES[shape]
+        _cache[key] = hp.pertoken_inputs(in_dtype, T, H, I, E, k, 77 + len(shape), orc.quant_rows)
+    return _cache[key]
+
+
+def sort(ids, tw, E, unit):
+    T, k = ids.shape
+    cap = T * k + E * unit - k
+    nblk = (cap + unit - 1) // unit
+    d = "cuda"
+    s_ids = torch.empty(cap, dtype=torch.int32, device=d)
+    s_w = torch.empty(cap, dtype=torch.float32, device=d)
+    s_e = torch.empty(nblk, dtype=torch.int32, device=d)
+    nv = torch.empty(2, dtype=torch.int32, device=d)
+    moe_sorting_flydsl(ids.cuda(), tw.cuda(), s_ids, s_w, s_e, nv, None, E, unit)
+    return s_ids, s_w, s_e, nv, nblk
+
+
+def dev_weight(wq, layout):
+    E, N, K = wq.shape
+    w = wq.cuda()
+    return w if layout == "plain" else shuffle_weight(w, E * N, K).view(-1)
+
+
+def run_stage1(shape, in_dtype, out_dtype, impl, w_layout, doweight):
+    T, H, I, E, k, tile_m = SHAPES[shape]
+    xq, sx, w1q, sw1, _w2q, _sw2, ids, tw = inputs(shape, in_dtype)
+    s_ids, s_w, s_e, nv, nblk = sort(ids, tw, E, tile_m)
+    exe = pt.compile_moe_gemm1(model_dim=H, inter_dim=I, experts=E, topk=k, tile_m=tile_m, tile_n=128, tile_k=128,
+                               doweight_stage1=doweight, in_dtype=in_dtype, out_dtype=out_dtype, w_layout=w_layout,
+                               impl=impl)
+    dt = {"f16": torch.float16, "bf16": torch.bfloat16}[out_dtype]
+    out = torch.full((T * k + 16, I), 77.0, dtype=dt, device="cuda")
+    exe(out.view(-1)[: T * k * I], xq.cuda().view(-1, H), dev_weight(w1q, w_layout), sx.cuda().view(-1),
+        sw1.cuda().view(-1), s_ids, s_e, s_w, nv, T, I, H, nblk, torch.cuda.current_stream())
+    torch.cuda.synchronize()
+    assert bool((out[T * k:] == 77.0).all()), "stage 1 wrote past its output rows"
+    ref = orc.pertoken_stage1(xq, sx, w1q, sw1, ids, tw, I, doweight)
+    return out[: T * k].view(T, k, I).cpu(), ref
+
+
+@pytest.mark.parametrize("impl", ["simt", "tcgen05"])
+@pytest.mark.parametrize("shape,in_dtype,out_dtype,w_layout,doweight", [
+    ("S", "fp8", "f16", "plain", False), ("S", "int8", "bf16", "preshuffle16x16", False),
+    ("S", "int8smooth", "f16", "plain", False), ("M", "fp8", "bf16", "preshuffle16x16", True),
+    ("M", "int8", "f16", "plain", False), ("M", "int8smooth", "bf16", "plain", False),
+    ("T128", "fp8", "bf16", "plain", False), ("T128", "int8", "f16", "plain", True),
+])
+def test_pertoken_stage1(shape, in_dtype, out_dtype, w_layout, doweight, impl):
+    out, ref = run_stage1(shape, in_dtype, out_dtype, impl, w_layout, doweight)
+    assert_close(out, ref, RTOL, ATOL, f"per-token stage 1 {shape} {in_dtype} {impl}")
+    eps = 2.0 ** -8 if out_dtype == "bf16" else 2.0 ** -11
+    assert_close(out, ref, 2 * eps, 1e-3, f"per-token stage 1 tight {shape} {in_dtype} {impl}")
+
+
+def run_stage2(shape, in_dtype, out_dtype, impl, w_layout, mode, doweight=True):
+    T, H, I, E, k, tile_m = SHAPES[shape]
+    xq, sx, w1q, sw1, w2q, sw2, ids, tw = inputs(shape, in_dtype)
+    qd = hp.FP8 if in_dtype == "fp8" else torch.int8
+    a2q, sa2 = orc.quant_rows(orc.pertoken_stage1(xq, sx, w1q, sw1, ids, tw, I, False), qd)
+    s_ids, s_w, s_e, nv, nblk = sort(ids, tw, E, tile_m)
+    common = dict(model_dim=H, inter_dim=I, experts=E, topk=k, tile_m=tile_m, tile_n=256, tile_k=128,
+                  doweight_stage2=doweight, in_dtype=in_dtype, out_dtype=out_dtype, w_layout=w_layout, impl=impl)
+    dt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}[out_dtype]
+    w = dev_weight(w2q, w_layout)
+    args = (a2q.cuda().view(-1, I), w, sa2.cuda().view(-1), sw2.cuda().view(-1), s_ids, s_e, s_w, nv, T, H, I, nblk)
+    if mode == "rows":
+        exe = pt.compile_moe_gemm2(accumulate=False, **common)
+        out = torch.zeros((T * k + 8, H), dtype=dt, device="cuda")
+        exe(out.view(-1)[: T * k * H], *args, torch.cuda.current_stream())
+        rows = T * k
+    else:
+        exe = pt.compile_moe_gemm2_ex(mode=mode, **common)
+        out = torch.zeros((T + 8, H), dtype=dt, device="cuda")
+        if mode == "reduce":
+            exe(out.view(-1)[: T * H], *args)
+            exe(out.view(-1)[: T * H], *args)          # second call reuses the wrapper's row buffer
+        else:
+            exe(out.view(-1)[: T * H], *args, torch.cuda.current_stream())
+        rows = T
+    torch.cuda.synchronize()
+    assert float(out[rows:].float().abs().sum()) == 0.0, "stage 2 wrote past its output rows"
+    ref = orc.pertoken_stage2(a2q, sa2, w2q, sw2, ids, tw, H, doweight, reduce=mode != "rows")
+    return out[:rows].cpu(), ref.view(rows, H)
+
+
+@pytest.mark.parametrize("impl", ["simt", "tcgen05"])
+@pytest.mark.parametrize("shape,in_dtype,out_dtype,w_layout,mode", [
+    ("S", "fp8", "f16", "plain", "atomic"), ("S", "fp8", "f32", "preshuffle16x16", "atomic"),
+    ("S", "int8", "bf16", "plain", "reduce"), ("S", "int8smooth", "f16", "plain", "rows"),
+    ("M", "fp8", "bf16", "plain", "atomic"), ("M", "fp8", "f16", "preshuffle16x16", "reduce"),
+    ("M", "int8", "f32", "plain", "atomic"), ("T128", "fp8", "bf16", "plain", "reduce"),
+    ("T128", "int8", "bf16", "plain", "atomic"),
+])
+def test_pertoken_stage2(shape, in_dtype, out_dtype, w_layout, mode, impl):
+    out, ref = run_stage2(shape, in_dtype, out_dtype, impl, w_layout, mode)
+    peak = float(ref.abs().max())
+    step = 0.0 if out_dtype == "f32" or mode != "atomic" else 2.0 ** (-7 if out_dtype == "bf16" else -10) * peak
+    assert_close(out, ref, RTOL, ATOL + step, f"per-token stage 2 {shape} {in_dtype} {mode} {impl}")
+    if out_dtype == "f32":
+        assert_close(out, ref, 1e-4, 1e-5 * peak, f"per-token stage 2 tight {shape} {in_dtype} {impl}")
+
+
+@pytest.mark.parametrize("in_dtype", ["fp8", "int8"])
+def test_pertoken_large_reference_shape(in_dtype):
+    """The reference's aiter-style L shape (333 tokens, 4096 x 2048, 17 experts, top-9), both stages."""
+    out1, ref1 = run_stage1("L", in_dtype, "bf16", "tcgen05", "plain", False)
+    assert_close(out1, ref1, RTOL, ATOL, f"per-token stage 1 L {in_dtype}")
+    out2, ref2 = run_stage2("L", in_dtype, "f32", "tcgen05", "plain", "atomic")
+    assert_close(out2, ref2, RTOL, ATOL, f"per-token stage 2 L {in_dtype}")
+    out2r, _ = run_stage2("L", in_dtype, "bf16", "tcgen05", "plain", "reduce")
+    assert_close(out2r, ref2, RTOL, ATOL, f"per-token stage 2 L reduce {in_dtype}")
+

@@ -114,3 +114,27 @@ def test_ulp_distance():
     a = torch.tensor([0.0, 1.0, -1.0, 448.0]).to(hp.FP8)
     b = torch.tensor([0.0, 1.125, -0.9375, 416.0]).to(hp.FP8)
     assert orc.e4m3_ulp_distance(a, b).tolist() == [0, 1, 1, 1]
+
+
+def test_pertoken_family_matches_reference_functions():
+    """oracle.pertoken_stage1/2 and quant_rows against torch_moe_gemm1/2 and pertoken_quant of the
+    reference (fixture moe_pertoken.npz): inputs regenerated from the seed must hash to the stored
+    value (which pins the quantiser), outputs must agree to fp32 round-off."""
+    g = hp.load("moe_pertoken.npz")
+    for i in range(int(g["n"][0])):
+        T, H, I, E, k, doweight1, seed = (int(v) for v in g[f"p{i}_cfg"])
+        in_dtype = str(g[f"p{i}_dtype"][0])
+        qd = hp.FP8 if in_dtype == "fp8" else torch.int8
+        xq, sx, w1q, sw1, w2q, sw2, ids, tw = hp.pertoken_inputs(in_dtype, T, H, I, E, k, seed, orc.quant_rows)
+        got_sha = hp.sha(hp.u8(xq), sx.numpy(), hp.u8(w1q), sw1.numpy(), hp.u8(w2q), sw2.numpy(), ids.numpy(), tw.numpy())
+        assert got_sha == str(g[f"p{i}_input_sha"][0]), f"case {i}: regenerated inputs differ from the fixture's"
+        if i == 0:
+            assert np.array_equal(hp.u8(xq), g["p0_xq"]) and np.array_equal(sw1.numpy(), g["p0_sw1"])
+        o1 = orc.pertoken_stage1(xq, sx, w1q, sw1, ids, tw, I, bool(doweight1))
+        ref1 = torch.from_numpy(g[f"p{i}_out1"])
+        assert torch.allclose(o1, ref1, rtol=1e-5, atol=1e-5 * float(ref1.abs().max())), f"case {i} stage 1"
+        a2q, sa2 = orc.quant_rows(ref1, qd)
+        assert np.array_equal(hp.u8(a2q), g[f"p{i}_a2q"]) and np.array_equal(sa2.numpy(), g[f"p{i}_sa2"])
+        o2 = orc.pertoken_stage2(a2q, sa2, w2q, sw2, ids, tw, H, not bool(doweight1))
+        ref2 = torch.from_numpy(g[f"p{i}_out2"])
+        assert torch.allclose(o2, ref2, rtol=1e-5, atol=1e-5 * float(ref2.abs().max())), f"case {i} stage 2"
