@@ -13,9 +13,14 @@ per GPU.  Rank 0 prints ONE JSON line.
 ``value`` is algorithmic TFLOP/s (6*T*k*H*I per step, whole job) with inputs resident in
 HBM; ``e2e`` is the same metric through the public layer call with host (pinned) buffers,
 host<->device copies inside the timed region.  ``roofline`` describes the dominant kernel
-(stage 1), timed with CUDA events inside the timed region.  ``cpu_baseline`` times the CPU
+(stage 1), timed with CUDA events inside the timed region.  ``decode`` (N=1 default run only)
+is the other half of the metric: the T=64 decode layer's weight-streaming GB/s.
+``parity_check`` compares a few tokens of the timed layer's output with the CPU oracle after
+the timed region; the run exits non-zero when it fails.  ``cpu_baseline`` times the CPU
 oracle (the reference's torch path restated) on a bounded sample on the host cores.
 ``--impl reference`` times only that CPU path and prints the same line shape.
+``--wait-accounting`` (with FLYMOE_LIB pointing at a ``python -m flydsl_b200.build --prof`` build)
+prints where the grouped-GEMM roles wait instead of the JSON line.
 """
 
 from __future__ import annotations
@@ -67,7 +72,9 @@ def cpu_baseline(cfg: wl.MoEConfig, n_sample_experts: int, device_weights=None, 
     return {"value": flops / dt / 1e12, "unit": UNIT, "cores": cores, "kind": "port",
             "sample": f"whole routing plus experts 0..{n - 1} of {cfg.experts} with the {pairs} (token, slot) "
                       f"pairs routed to them ({pairs / max(1, cfg.pairs):.3f} of the layer's FLOPs), "
-                      f"{dt:.2f} s of CPU work", "seconds": round(dt, 3)}
+                      f"{dt:.2f} s of CPU work; the rate of this sample stands for the whole layer",
+            "sample_fraction_of_layer_flops": round(pairs / max(1, cfg.pairs), 4),
+            "extrapolated_from_sample": bool(pairs < cfg.pairs), "seconds": round(dt, 3)}
 
 
 def run_reference_arm(args, cfg, rank: int) -> None:
@@ -75,15 +82,22 @@ def run_reference_arm(args, cfg, rank: int) -> None:
         return
     # Each step is one bounded sample (~1.5 s of CPU work).  W warm-up samples and up to K timed ones are
     # run, but no more than fit into about a minute, so that large K still ends within minutes.
+    from oracle import moe_oracle as orc
+    n = min(args.cpu_experts, cfg.experts)
+    weights = wl.make_weights(cfg, experts=range(n))               # generated once, outside every timed sample
+    logits = wl.make_logits(cfg)
+    _x, xq, xs = wl.make_activations(cfg)
+    tw, ids, _ = orc.topk_gating_softmax(logits, cfg.topk)
+    sample = dict(device_weights=weights, ids=ids, tw=tw, xq=xq, xs=xs)
     budget_s, t_begin = 60.0, time.perf_counter()
     warm = 0
     for _ in range(min(max(args.warmup, 0), 2)):
-        cpu_baseline(cfg, args.cpu_experts)
+        cpu_baseline(cfg, n, **sample)
         warm += 1
     vals = []
     last = None
     for _ in range(max(1, args.steps)):
-        last = cpu_baseline(cfg, args.cpu_experts)
+        last = cpu_baseline(cfg, n, **sample)
         vals.append(last["value"])
         if time.perf_counter() - t_begin > budget_s:
             break
@@ -115,8 +129,101 @@ MEASURED_TRAFFIC = {
 }
 
 
+class ExpertTable:
+    """Expert-indexable view for the oracle: ``fetch(e)`` returns one expert's tensor on the CPU."""
+
+    def __init__(self, experts: int, fetch):
+        self.n, self.fetch, self.cache = experts, fetch, {}
+
+    def __len__(self):
+        return self.n
+
+    def __getitem__(self, e):
+        if e not in self.cache:
+            self.cache[e] = self.fetch(e)
+        return self.cache[e]
+
+
+def parity_check(cfg: wl.MoEConfig, tokens, logits_c, xq_c, xs_c, out_rows, fetch_expert) -> dict:
+    """Checker, run after the timed region: the layer's output rows ``out_rows`` (bf16, one per entry of
+    ``tokens``) against the CPU oracle on the same pre-quantised inputs (bar: rtol 2e-2 / atol 2e-2).
+    ``fetch_expert(e)`` returns (w1q, w1_scale, w2q, w2_scale) of global expert e; only the experts the
+    chosen tokens route to are fetched."""
+    from oracle import moe_oracle as orc
+    sel = torch.as_tensor(tokens, dtype=torch.int64)
+    tw, ids, _ = orc.topk_gating_softmax(logits_c[sel], cfg.topk)
+    cache = {}
+
+    def fetch(e):
+        if e not in cache:
+            cache[e] = fetch_expert(e)
+        return cache[e]
+    tabs = [ExpertTable(cfg.experts, (lambda e, j=j: fetch(e)[j])) for j in range(4)]
+    o1 = orc.stage1(xq_c[sel], xs_c[sel], tabs[0], tabs[1], ids, cfg.inter_dim)
+    a2q, a2s = orc.requant(o1)
+    ref = orc.stage2(a2q, a2s, tabs[2], tabs[3], ids, tw, cfg.model_dim)
+    got = out_rows.float().cpu()
+    err = (got - ref).abs()
+    ok = bool(torch.isfinite(got).all()) and bool((err <= 2e-2 + 2e-2 * ref.abs()).all())
+    return {"tokens": [int(t) for t in tokens], "experts_checked": len(cache), "max_abs_err": round(float(err.max()), 5),
+            "ref_max_abs": round(float(ref.abs().max()), 4), "rtol": 2e-2, "atol": 2e-2, "ok": ok}
+
+
+def wait_accounting(args, cfg) -> None:
+    """Mean cycles per 128-wide K block that each role of the grouped-GEMM kernels spends waiting, read
+    from a library built with -DFLYMOE_PROF (FLYMOE_LIB=flydsl_b200/libflymoe_sm100_prof.so)."""
+    import ctypes
+    import numpy as np
+    from flydsl_b200 import _lib
+    from flydsl_b200.layer import FusedMoEBlockscale
+    lib = _lib.load()
+    if not hasattr(lib, "flymoe_prof_read"):
+        raise SystemExit("this library was built without -DFLYMOE_PROF: run `python -m flydsl_b200.build --prof` "
+                         "and set FLYMOE_LIB=flydsl_b200/libflymoe_sm100_prof.so")
+    lib.flymoe_prof_read.argtypes = [ctypes.c_void_p]
+    dev = torch.device("cuda", 0)
+    T, k, H, I, E = cfg.tokens, cfg.topk, cfg.model_dim, cfg.inter_dim, cfg.experts
+    w1q, w1s, w2q, w2s = wl.make_weights(cfg, device=dev)
+    logits = wl.make_logits(cfg).to(dev)
+    _x, xq_c, xs_c = wl.make_activations(cfg)
+    xq, xs_t = xq_c.to(dev), xs_c.t().contiguous().to(dev)
+    layer = FusedMoEBlockscale(w1q, w1s, w2q, w2s, k, max_tokens=T, tile_m=args.tile_m)
+    for _ in range(max(args.warmup, 10)):
+        layer(logits, xq, xs_t)
+    torch.cuda.synchronize()
+    buf = np.zeros((256, 3, 8), dtype=np.int64)
+
+    def show(tag):
+        lib.flymoe_prof_read(buf.ctypes.data)
+        b = buf[:torch.cuda.get_device_properties(dev).multi_processor_count].astype(np.float64)
+        p, m, e = b[:, 0], b[:, 1], b[:, 2]
+        nkb = max(m[:, 6].mean(), 1.0)
+        print(json.dumps({"kernel": tag, "workload": cfg.name, "k_blocks_per_cta": round(nkb, 1),
+                          "cycles_per_k_block": round(m[:, 0].mean() / nkb, 1),
+                          "tma_wait_free_smem_stage": round(p[:, 1].mean() / nkb, 1),
+                          "mma_wait_tmem_stage": round(m[:, 1].mean() / nkb, 1),
+                          "mma_wait_operands": round(m[:, 2].mean() / nkb, 1),
+                          "mma_issue_and_commit": round(m[:, 4].mean() / nkb, 1),
+                          "epilogue_wait_mma": round(e[:, 1].mean() / nkb, 1),
+                          "tile_end_cycles_per_tile": round(e[:, 2].mean() / max(e[:, 5].mean(), 1.0), 1)}), flush=True)
+    show("stage 2 (last launch of the layer)")
+    # stage 1 alone, so that its counters are the last ones written
+    U = layer.tile_m
+    cap = T * k + E * U - k
+    blocks = (cap + U - 1) // U
+    st = torch.cuda.current_stream().cuda_stream
+    for _ in range(3):
+        _lib.check(lib.flymoe_moe_gemm1(
+            layer.a2q.data_ptr(), layer.a2_scale.data_ptr(), layer.cap_rows, layer.xs.data_ptr(), xs_t.data_ptr(), T, 1,
+            w1q.data_ptr(), w1s.data_ptr(), layer.sorted_ids.data_ptr(), layer.sorted_expert_ids.data_ptr(),
+            layer.sorted_weights.data_ptr(), layer.num_valid_ids.data_ptr(), T, I, H, blocks, E, k, U, 0, _lib.E4M3,
+            _lib.ROWS_SORTED, _lib.ROWS_BY_TOKEN, _lib.ROWS_SORTED, 0, st), "moe_gemm1")
+    torch.cuda.synchronize()
+    show("stage 1")
+
+
 # ------------------------------------------------------------------------------------ GPU arm
-def run_single_gpu(args, cfg) -> dict:
+def run_single_gpu(args, cfg, with_e2e: bool = True, with_cpu: bool = True, with_parity: bool = True) -> dict:
     from flydsl_b200 import _lib
     from flydsl_b200.layer import FusedMoEBlockscale
     dev = torch.device("cuda", 0)
@@ -165,9 +272,13 @@ def run_single_gpu(args, cfg) -> dict:
     ids = layer.topk_ids[:T].cpu()
     e_act = int(torch.unique(ids).numel())
     rows = int(layer.num_valid_ids[0])
-    s1_bytes = (e_act * 2.0 * I * H * (1 + 4.0 / (128 * 128))      # W1 of active experts + block scales
-                + rows * H + T * (H // 128) * 4.0                  # gathered activations + their scales
-                + rows * I * (1 + 4.0 / 128))                      # e4m3 intermediate + scales written
+    # algorithmic bytes of one stage-1 launch: W1 of the active experts with their block scales, the
+    # activations with their 1x128 scales once per token, the e4m3 intermediate with its scales once per
+    # (token, slot) pair.  What the design moves on top of that (gathered and padded rows) is reported apart.
+    s1_bytes = (e_act * 2.0 * I * H * (1 + 4.0 / (128 * 128)) + T * H * (1 + 4.0 / 128)
+                + T * k * I * (1 + 4.0 / 128))
+    s1_moved = (e_act * 2.0 * I * H * (1 + 4.0 / (128 * 128)) + rows * H + T * (H // 128) * 4.0
+                + rows * I * (1 + 4.0 / 128))
     s1_ms = statistics.mean(g1) if g1 else float("nan")
     s2_ms = statistics.mean(g2) if g2 else float("nan")
     achieved = s1_bytes / (s1_ms * 1e-3) / 1e9
@@ -177,12 +288,36 @@ def run_single_gpu(args, cfg) -> dict:
                 "peak": peaks["hbm_gbs"], "peak_source": peaks["source"], "unit": "GB/s",
                 "frac": round(achieved / peaks["hbm_gbs"], 4),
                 "traffic": MEASURED_TRAFFIC.get((cfg.name, args.tile_m)),
-                "algorithmic_bytes_per_launch": int(s1_bytes), "ms_per_launch": round(s1_ms, 4),
+                "algorithmic_bytes_per_launch": int(s1_bytes), "bytes_moved_by_design": int(s1_moved),
+                "ms_per_launch": round(s1_ms, 4),
                 "stage2_ms_per_launch": round(s2_ms, 4),
                 "tensor_tflops": round(s1_flops / (s1_ms * 1e-3) / 1e12, 1),
                 "tensor_frac_of_2x_bf16_peak": round(s1_flops / (s1_ms * 1e-3) / 1e12 / fp8_peak, 4),
                 "active_experts": e_act, "padded_rows": rows}
     total_bytes = wl.weight_bytes_active(cfg, ids)
+
+    parity = None
+    if with_parity:
+        n_chk = min(8, T)
+        toks = sorted({int(round(i * (T - 1) / max(1, n_chk - 1))) for i in range(n_chk)})
+        out_d = step()
+        torch.cuda.synchronize()
+        parity = parity_check(cfg, toks, logits.cpu(), xq_c, xs_c, out_d[torch.tensor(toks, device=dev)],
+                              lambda e: (w1q[e].cpu(), w1s[e].cpu(), w2q[e].cpu(), w2s[e].cpu()))
+
+    result = {"metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+              "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+              "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate and scales)",
+              "data": "synthetic",
+              "config": {**wl.describe(cfg), "tile_m": args.tile_m, "stage2_mode": args.stage2_mode,
+                         "parallelism": "single GPU",
+                         "l2_policy": "inputs exceed L2: %.1f GB of expert weights stream per step" % (e_act * 3.0 * H * I / 1e9)},
+              "layer_hbm_gbs": round(total_bytes / (ms_per_step * 1e-3) / 1e9, 1),
+              "layer_hbm_frac": round(total_bytes / (ms_per_step * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
+              "roofline": roofline, "parity_check": parity, "cpu_baseline": None, "e2e": None, "clocks": clocks,
+              "gpu_launches": args.steps * layer.kernel_launches(T)}
+    if not with_e2e:
+        return result
 
     # ---- end to end: pinned host inputs -> device -> layer -> pinned host output, every step,
     # through the host-streaming front end (copies of neighbouring steps overlap this step's kernels)
@@ -209,22 +344,25 @@ def run_single_gpu(args, cfg) -> dict:
            "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
            "how": "HostPipeline, depth 2: pinned host in, pinned host out, copies overlapped across steps"}
 
-    cpu = None
-    if not args.no_cpu_baseline:
-        cpu = cpu_baseline(cfg, args.cpu_experts, device_weights=(w1q, w1s, w2q, w2s), ids=ids,
-                           tw=layer.topk_weights[:T].cpu(), xq=xq_c, xs=xs_c)
+    result["e2e"] = e2e
+    if with_cpu and not args.no_cpu_baseline:
+        result["cpu_baseline"] = cpu_baseline(cfg, args.cpu_experts, device_weights=(w1q, w1s, w2q, w2s), ids=ids,
+                                              tw=layer.topk_weights[:T].cpu(), xq=xq_c, xs=xs_c)
+    return result
 
-    return {"metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate and scales)",
-            "data": "synthetic",
-            "config": {**wl.describe(cfg), "tile_m": args.tile_m, "stage2_mode": args.stage2_mode,
-                       "parallelism": "single GPU",
-                       "l2_policy": "inputs exceed L2: %.1f GB of expert weights stream per step" % (e_act * 3.0 * H * I / 1e9)},
-            "layer_hbm_gbs": round(total_bytes / (ms_per_step * 1e-3) / 1e9, 1),
-            "layer_hbm_frac": round(total_bytes / (ms_per_step * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
-            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
-            "gpu_launches": args.steps * layer.kernel_launches(T)}
+
+def run_decode_leg(args) -> dict:
+    """The decode half of the metric for the default line: the T=64 DeepSeek-V3-shaped layer (workload c3,
+    row block 16), whose time is the streaming of the routed experts' weights from HBM."""
+    import copy
+    a = copy.copy(args)
+    a.tile_m, a.steps, a.warmup = 16, max(50, min(args.steps, 200)), max(args.warmup, 5)
+    r = run_single_gpu(a, wl.CONFIGS["c3"], with_e2e=False, with_cpu=False)
+    keep = ("ms_per_step", "steps", "layer_hbm_gbs", "layer_hbm_frac", "value", "roofline", "parity_check", "clocks")
+    d = {"workload": r["config"]["workload"], "tile_m": 16, "metric": "weight-streaming HBM GB/s of the decode layer",
+         **{kk: r[kk] for kk in keep}}
+    d["tflops"] = d.pop("value")
+    return d
 
 
 def run_dense_gemm(args) -> dict:
@@ -303,10 +441,19 @@ def main() -> None:
     ap.add_argument("--ep-combine", choices=("auto", "nccl", "fused", "direct"), default="auto",
                     help="expert-parallel transport: NCCL all-to-all both ways; 'fused' = combine as peer stores "
                          "from stage 2's epilogue; 'direct' = dispatch as peer stores into the owners' operand buffers too")
+    ap.add_argument("--ep-host-plan", action="store_true",
+                    help="expert-parallel direct dispatch: plan each step on the host (one synchronisation per step, "
+                         "capacity checked with an exception) instead of on the device")
     ap.add_argument("--ep-comm-sms", type=int, default=0, help="SMs the pipelined EP step leaves to NCCL")
     ap.add_argument("--nccl-max-ctas", type=int, default=0, help="sets NCCL_MAX_CTAS before the group is created")
-    ap.add_argument("--cpu-experts", type=int, default=24, help="experts in the CPU baseline sample")
+    ap.add_argument("--cpu-experts", type=int, default=48, help="experts in the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the post-run check against the CPU oracle")
+    ap.add_argument("--no-same-work", action="store_true",
+                    help="multi-GPU: skip timing the same per-GPU work on one GPU (weak_scaling_eff)")
+    ap.add_argument("--no-decode", action="store_true", help="skip the decode (c3) leg of the default N=1 line")
+    ap.add_argument("--wait-accounting", action="store_true",
+                    help="print the grouped-GEMM wait accounting (needs a -DFLYMOE_PROF build in FLYMOE_LIB)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -330,12 +477,26 @@ def main() -> None:
         return
     if args.gpus > 1 or world > 1:
         from flydsl_b200.ep_bench import run_expert_parallel
-        line = run_expert_parallel(args, cfg)
+        line = run_expert_parallel(args, cfg, parity_fn=None if args.no_parity else parity_check)
         if line is not None:
             print(json.dumps(line), flush=True)
+            if line.get("parity_check") is not None and not line["parity_check"]["ok"]:
+                print("[bench] parity check against the CPU oracle FAILED", file=sys.stderr)
+                sys.exit(3)
         return
-    line = run_single_gpu(args, cfg)
+    if args.wait_accounting:
+        wait_accounting(args, cfg)
+        return
+    line = run_single_gpu(args, cfg, with_parity=not args.no_parity)
+    default_run = args.workload is None and args.tokens is None and args.experts is None
+    if default_run and not args.no_decode:
+        torch.cuda.empty_cache()
+        line["decode"] = run_decode_leg(args)
     print(json.dumps(line), flush=True)
+    checks = [line.get("parity_check"), (line.get("decode") or {}).get("parity_check")]
+    if any(c is not None and not c["ok"] for c in checks):
+        print("[bench] parity check against the CPU oracle FAILED", file=sys.stderr)
+        sys.exit(3)
 
 
 if __name__ == "__main__":

@@ -58,6 +58,10 @@ _SIGNATURES = {
                                               c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                               c_int, c_int, _P]),
     "flymoe_dispatch_rows": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, c_int64, c_int, c_int, c_int, c_int, c_int, _P]),
+    "flymoe_expert_counts": (c_int, [_P, _P, _P, c_int, c_int, _P]),
+    "flymoe_ep_plan_workspace_elems": (c_int64, [c_int, c_int]),
+    "flymoe_ep_plan_direct": (c_int, [_P, _P, c_int64, c_int64, c_int64, _P, _P, _P, _P, _P, _P, _P, _P, c_int64,
+                                      c_int, c_int, c_int, c_int, c_int, c_int64, _P]),
     "flymoe_blockscale_gemm_workspace_elems": (c_int64, [c_int, c_int]),
     "flymoe_blockscale_gemm": (c_int, [_P, _P, _P, c_int64, _P, _P, _P, c_int64, c_int, c_int, c_int, c_int, c_int, _P]),
     "flymoe_set_gemm_cta_limit": (c_int, [c_int]),

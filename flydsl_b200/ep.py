@@ -304,11 +304,13 @@ class ExpertParallelMoE:
         P = T * k
         s_ids, s_eids = ops.sort_by_expert(topk_ids, topk_w, T, 0)
         mine = ops.expert_counts(s_eids, P)                                   # int64 [E]
-        gathered = [torch.empty_like(mine) for _ in range(self.world)]
+        matrix = ops.counts_matrix(self.world) if hasattr(ops, "counts_matrix") else None
+        gathered = (list(matrix.unbind(0)) if matrix is not None
+                    else [torch.empty_like(mine) for _ in range(self.world)])
         dist.all_gather(gathered, mine, group=g)
         if getattr(ops, "device_plan", False):
             # the whole plan stays on the device: no host synchronisation in the step
-            self._counts_dev = torch.stack(gathered)
+            self._counts_dev = matrix if matrix is not None else torch.stack(gathered)
             self.last_plans = []
             ops.run_direct_on_device(xq, x_scale, s_ids, s_eids, self._counts_dev, self.rank, T)
             return ops.combine(ops.returned_rows(P), s_ids, topk_w, 0, T, T, 0)
@@ -369,6 +371,9 @@ class CudaOps:
                 "send_s": torch.empty((packed, self.H // 128), dtype=f32, device=dev),
                 "inverse": torch.empty(pc, dtype=i32, device=dev), "y": None})
         self.headroom = headroom
+        # set by a caller that copies ``out`` away on another stream: the reduce of the next step waits
+        # for this event before it overwrites ``out`` (the rest of that step runs without waiting)
+        self.out_free_event = None
         self.inner = None
         self._ensure_inner(int(pc * headroom))
         # Fused combine: a [tokens * topk, H] bf16 buffer per rank that all ranks can store into.
@@ -388,6 +393,17 @@ class CudaOps:
             self._off_back = self._off_xsc + al(rows * (self.H // 128) * 4)
             self.peers = PeerBuffers(self._off_back + tokens * topk * self.H * 2, dev, group)
             self._rendezvous_flag = torch.zeros(1, dtype=i32, device=dev)
+            if self.direct_dispatch:
+                # everything the device-side planner writes, allocated once
+                world = len(self.peers.ptrs)
+                i64 = torch.int64
+                self._counts_mine = torch.zeros(experts, dtype=i64, device=dev)
+                self._counts_all = torch.zeros((world, experts), dtype=i64, device=dev)
+                self._peer_ptrs = torch.tensor(self.peers.ptrs, dtype=i64, device=dev)
+                self._plan_tables = torch.zeros((3, experts), dtype=i64, device=dev)      # dst_x, dst_scale, pos_base
+                self._plan_row_dst = torch.zeros(self.inner.cap_rows, dtype=i64, device=dev)
+                ws = int(self.lib.flymoe_ep_plan_workspace_elems(world, experts))
+                self._plan_ws = torch.zeros(max(ws, 1), dtype=i32, device=dev)
 
     def _ensure_inner(self, rows: int) -> None:
         from .layer import FusedMoEBlockscale
@@ -455,10 +471,16 @@ class CudaOps:
 
     # ---- direct dispatch --------------------------------------------------------------------
     def expert_counts(self, s_eids: torch.Tensor, pairs: int) -> torch.Tensor:
-        """Rows per global expert from the ascending per-row expert ids of the unit-1 sort."""
-        bounds = torch.arange(0, self.E + 1, device=s_eids.device, dtype=s_eids.dtype)
-        pos = torch.searchsorted(s_eids[:pairs].contiguous(), bounds)
-        return (pos[1:] - pos[:-1]).to(torch.int64)
+        """Rows per global expert from the ascending per-row expert ids of the unit-1 sort (one kernel)."""
+        b = self.chunk_bufs[0]
+        self._lib.check(self.lib.flymoe_expert_counts(s_eids.data_ptr(), b["nvalid"].data_ptr(),
+                                                      self._counts_mine.data_ptr(), self.E, pairs, self._stream()),
+                        "expert_counts")
+        return self._counts_mine
+
+    def counts_matrix(self, world: int) -> torch.Tensor:
+        """The [world, E] buffer the per-expert row counts of all ranks are gathered into."""
+        return self._counts_all
 
     def check_direct_capacity(self, dp: DirectPlan) -> None:
         if dp.max_padded_rows > self.inner.cap_rows:       # same verdict on every rank: all hold the same matrix
@@ -479,37 +501,28 @@ class CudaOps:
                                               T, self.k, self.H, self.E, T * self.k, self._stream()), "dispatch_rows")
 
     def run_direct_on_device(self, xq, x_scale, s_ids, s_eids, counts, rank: int, T: int) -> None:
-        """Dispatch, local experts and the two rendezvous with the plan computed by tensor operations on
-        the GPU.  Launch sizes use the buffers' capacity; the kernels read the real extents from device
-        memory.  A step that does not fit the capacity drops the rows that would fall outside and raises
-        the device status word (``flymoe_device_status``) instead of an exception."""
-        L, b, inner, dev = self._lib, self.chunk_bufs[0], self.inner, self.dev
+        """Dispatch, local experts and the two rendezvous with the plan computed on the GPU
+        (``flymoe_ep_plan_direct``: two small kernels, the arithmetic of ``plan_direct``).  Launch sizes use
+        the buffers' capacity; the kernels read the real extents from device memory.  A step that does not
+        fit the capacity drops the rows that would fall outside and raises the device status word
+        (``flymoe_device_status``) instead of an exception."""
+        L, b, inner = self._lib, self.chunk_bufs[0], self.inner
         cap, U, H = inner.cap_rows, self.tile_m, self.H
-        pl = plan_direct_tensors(counts, rank, self.E_local, U, cap)
-        if not hasattr(self, "_owner_ptrs"):
-            owner = torch.arange(self.E, device=dev) // self.E_local
-            ptrs = torch.tensor(self.peers.ptrs, dtype=torch.int64, device=dev)
-            self._owner_ptrs, self._peer_ptrs = ptrs[owner], ptrs
-        kb4 = (H // 128) * 4
-        tab = torch.stack([self._owner_ptrs + self._off_xs + pl["pos_base"] * H,
-                           self._owner_ptrs + self._off_xsc + pl["pos_base"] * kb4, pl["pos_base"]])
-        self._tables = tab
+        tab = self._plan_tables
+        L.check(self.lib.flymoe_ep_plan_direct(
+            counts.data_ptr(), self._peer_ptrs.data_ptr(), self._off_xs, self._off_xsc, self._off_back,
+            tab[0].data_ptr(), tab[1].data_ptr(), tab[2].data_ptr(), inner.sorted_ids.data_ptr(),
+            inner.sorted_expert_ids.data_ptr(), inner.num_valid_ids.data_ptr(), self._plan_row_dst.data_ptr(),
+            self._plan_ws.data_ptr(), self._plan_ws.numel(), counts.shape[0], rank, self.E, U, H, cap,
+            self._stream()), "ep_plan_direct")
         L.check(self.lib.flymoe_dispatch_rows(xq.data_ptr(), x_scale.data_ptr(), s_ids.data_ptr(), s_eids.data_ptr(),
                                               b["nvalid"].data_ptr(), tab[0].data_ptr(), tab[1].data_ptr(),
                                               tab[2].data_ptr(), cap, T, self.k, H, self.E, T * self.k,
                                               self._stream()), "dispatch_rows")
         self.peer_rendezvous()
-        rows = torch.clamp(pl["padded_rows"], max=cap)
-        pos = torch.arange(cap, dtype=torch.int64, device=dev)
-        valid = (pl["src"] >= 0) & (pos < rows)
-        inner.sorted_ids[:cap] = torch.where(valid, pos, (1 << 24) | cap).to(torch.int32)
-        inner.sorted_expert_ids[:cap // U] = pl["block_expert"]
-        inner.num_valid_ids[:] = rows.to(torch.int32)
-        row_dst = torch.where(valid, self._peer_ptrs[pl["src"].clamp(min=0)] + self._off_back
-                              + pl["src_row"] * (H * 2), 0)
         base_ptr = self.peers.local.data_ptr()
         inner.experts_forward_sorted(base_ptr + self._off_xs, base_ptr + self._off_xsc, cap, cap // U,
-                                     self._stream(), row_dst)
+                                     self._stream(), self._plan_row_dst)
         self.peer_rendezvous()
 
     def local_experts_direct(self, dp: DirectPlan) -> None:
@@ -554,6 +567,8 @@ class CudaOps:
         L, b = self._lib, self.chunk_bufs[chunk]
         n = hi - lo
         P = n * self.k
+        if self.out_free_event is not None:
+            torch.cuda.current_stream().wait_event(self.out_free_event)
         L.check(self.lib.flymoe_sorted_inverse(s_ids.data_ptr(), b["nvalid"].data_ptr(), b["inverse"].data_ptr(),
                                                n, self.k, P, self._stream()), "sorted_inverse")
         L.check(self.lib.flymoe_moe_reduce(back.data_ptr(), self.out[lo:hi].data_ptr(), None, topk_w.data_ptr(),

@@ -17,7 +17,9 @@ from . import workloads as wl
 from .benchutil import METRIC, UNIT, ClockSampler, load_peaks, physical_gpu_index
 
 
-def run_expert_parallel(args, cfg: wl.MoEConfig):
+def run_expert_parallel(args, cfg: wl.MoEConfig, parity_fn=None):
+    """``parity_fn`` (the benchmark's checker against the CPU oracle; this package imports no oracle) is
+    called on every rank after the timed region with a few of the rank's own tokens."""
     from . import _lib
     from .ep import CudaOps, ExpertParallelMoE, expert_range
 
@@ -49,7 +51,7 @@ def run_expert_parallel(args, cfg: wl.MoEConfig):
         def make_ops(m):
             return CudaOps(w1q, w1s, w2q, w2s, E, k, T, tile_m=args.tile_m, chunks=chunks, comm_sms=comm_sms,
                            fused_combine=m in ("fused", "direct"), direct_dispatch=m in ("direct", "auto"),
-                           headroom=headroom)
+                           device_plan=not getattr(args, "ep_host_plan", False), headroom=headroom)
         try:
             ops = make_ops(mode)
         except RuntimeError as exc:                          # no peer mapping here: same outcome on every rank
@@ -107,6 +109,7 @@ def run_expert_parallel(args, cfg: wl.MoEConfig):
                  for _ in range(2)]
         out_free = torch.cuda.Event()
         out_free.record(stream)
+        ops.out_free_event = out_free
         for sl in slots:
             sl["free"].record(stream)
         step_no = [0]
@@ -121,7 +124,8 @@ def run_expert_parallel(args, cfg: wl.MoEConfig):
                 sl["xs"].copy_(h_xs, non_blocking=True)
                 sl["ready"].record(h2d_s)
             stream.wait_event(sl["ready"])
-            stream.wait_event(out_free)                 # the previous result has left the output buffer
+            # the previous result must have left the output buffer only when this step's reduce writes
+            # it: the wait sits in front of the combine (ops.out_free_event), not in front of the layer
             out = layer(sl["logits"], sl["xq"], sl["xs"])
             sl["free"].record(stream)
             done = torch.cuda.Event()
@@ -150,14 +154,81 @@ def run_expert_parallel(args, cfg: wl.MoEConfig):
         for _ in range(2):
             e2e_step()
         e2e_ms = e2e_timed(max(2, args.steps // 2))
+        ops.out_free_event = None
         if _lib.device_status() != 0:
             raise RuntimeError("a kernel reported a device-side timeout during the timed region")
+
+        # host link rates with every rank copying at once (the ranks share the host's memory and PCIe
+        # root): the floor of an end-to-end step is the slower direction's bytes over its achieved rate
+        def copy_rate(fn, nbytes):
+            dist.barrier()
+            torch.cuda.synchronize()
+            c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            c0.record(stream)
+            for _ in range(3):
+                fn()
+            c1.record(stream)
+            torch.cuda.synchronize()
+            t = torch.tensor([c0.elapsed_time(c1) / 3], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return nbytes / (float(t.item()) * 1e-3) / 1e9, float(t.item())
+
+        def h2d_all():
+            slots[0]["logits"].copy_(h_logits, non_blocking=True)
+            slots[0]["xq"].copy_(h_xq, non_blocking=True)
+            slots[0]["xs"].copy_(h_xs, non_blocking=True)
+        h2d_bytes_rank = h_logits.numel() * 4 + h_xq.numel() + h_xs.numel() * 4
+        d2h_bytes_rank = h_out.numel() * 2
+        h2d_gbs, h2d_ms = copy_rate(h2d_all, h2d_bytes_rank)
+        d2h_gbs, d2h_ms = copy_rate(lambda: h_out.copy_(ops.out, non_blocking=True), d2h_bytes_rank)
+
+        # ---- checker: a few of this rank's own tokens against the CPU oracle
+        parity = None
+        if parity_fn is not None:
+            toks = sorted({0, T // 3, (2 * T) // 3, T - 1})
+            out_d = layer(logits, xq, xs)
+            torch.cuda.synchronize()
+
+            def fetch(e):
+                w = wl.make_weights(cfg, device=dev, experts=[e])
+                return tuple(t[0].cpu() for t in w)
+            mine_chk = parity_fn(cfg, toks, logits.cpu(), xq_c, xs_c, out_d[torch.tensor(toks, device=dev)], fetch)
+            gathered = [None] * world
+            dist.all_gather_object(gathered, mine_chk)
+            parity = {"tokens_per_rank": len(toks), "ranks": world, "tokens": toks,
+                      "experts_checked": sum(c["experts_checked"] for c in gathered),
+                      "max_abs_err": max(c["max_abs_err"] for c in gathered), "rtol": 2e-2, "atol": 2e-2,
+                      "ok_per_rank": [bool(c["ok"]) for c in gathered], "ok": all(c["ok"] for c in gathered)}
+
+        # ---- the same per-GPU work on ONE GPU (rank 0 alone, every expert local, no exchange): the
+        # denominator of the weak-scaling efficiency on equal work
+        same_work_ms = None
+        if not getattr(args, "no_same_work", False):
+            if rank == 0:
+                from .layer import FusedMoEBlockscale
+                aw = wl.make_weights(cfg, device=dev)
+                one = FusedMoEBlockscale(*aw, k, max_tokens=T, tile_m=args.tile_m)
+                xs_t = xs.t().contiguous()
+                for _ in range(3):
+                    one(logits, xq, xs_t)
+                torch.cuda.synchronize()
+                s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s0.record(stream)
+                for _ in range(10):
+                    one(logits, xq, xs_t)
+                s1.record(stream)
+                torch.cuda.synchronize()
+                same_work_ms = s0.elapsed_time(s1) / 10
+                del one, aw
+            dist.barrier()
 
         # this library's kernels per step: gate, unit-1 sort, pack (2 row gathers) or the dispatch kernel,
         # the local experts (their own sort + gather unless the rows arrive sorted), inverse (2) + reduce
         sort1 = 1 if (T // chunks) * k <= 8192 else 3
         if direct:
-            launches = 1 + sort1 + 1 + 2 + 3
+            # gate, sort, [expert counts, 2 planner kernels when planned on the device], dispatch, 2 GEMMs,
+            # inverse (2) + reduce
+            launches = 1 + sort1 + (3 if ops.device_plan else 0) + 1 + 2 + 3
         else:
             launches = 1 + chunks * (sort1 + 2 + ops.inner.experts_kernel_launches(rows_in // chunks) + 3)
         if rank != 0:
@@ -198,6 +269,8 @@ def run_expert_parallel(args, cfg: wl.MoEConfig):
                            "tile_m": args.tile_m, "parallelism": f"ep{world}", "pipeline_chunks": chunks, "sms_left_to_nccl": comm_sms,
                            "dispatch": (f"peer stores into the owners' sorted operand buffers ({ops.peers.kind})"
                                         if direct else "nccl all_to_all"),
+                           "step_plan": ("on the device (no host synchronisation in the step)" if ops.device_plan
+                                         else "on the host (one synchronisation per step)"),
                            "combine": (f"peer stores from the stage-2 epilogue ({ops.peers.kind})" if fused
                                        else "nccl all_to_all"),
                            "l2_policy": "inputs exceed L2 (dispatched rows and expert weights are GBs per step)"},
@@ -205,10 +278,18 @@ def run_expert_parallel(args, cfg: wl.MoEConfig):
                 "fused_stage2_roofline": fused_roofline,
                 "comm": {"dispatch_bytes_rank0": int(remote * (H + H // 128 * 4 + (0 if direct else 4))),
                          "combine_bytes_rank0": int(remote * H * 2), "load_imbalance_max_over_mean": round(imbalance, 3)},
+                "parity_check": parity,
+                "same_work_1gpu_ms": None if same_work_ms is None else round(same_work_ms, 4),
+                "weak_scaling_eff": None if same_work_ms is None else round(same_work_ms / ms, 4),
                 "cpu_baseline": None,
                 "e2e": {"value": round(flops / (e2e_ms * 1e-3) / 1e12, 2), "unit": UNIT, "ms_per_step": round(e2e_ms, 4),
-                        "h2d_bytes_per_step": int(world * (h_logits.numel() * 4 + h_xq.numel() + h_xs.numel() * 4)),
-                        "d2h_bytes_per_step": int(world * h_out.numel() * 2)},
+                        "h2d_bytes_per_step": int(world * h2d_bytes_rank),
+                        "d2h_bytes_per_step": int(world * d2h_bytes_rank),
+                        "h2d_gbs_per_rank_all_ranks_copying": round(h2d_gbs, 2),
+                        "d2h_gbs_per_rank_all_ranks_copying": round(d2h_gbs, 2),
+                        "pcie_floor_ms": round(max(h2d_ms, d2h_ms), 4),
+                        "bound": "pcie" if max(h2d_ms, d2h_ms) > ms else "device",
+                        "how": "two input slots; the result's device-to-host copy overlaps the next step up to its reduce"},
                 "clocks": clocks,
                 "gpu_launches": args.steps * launches}
     finally:

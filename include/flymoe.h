@@ -224,6 +224,30 @@ int flymoe_dispatch_rows(const void* x, const float* x_scale, const int32_t* sor
                          int64_t pos_limit, int num_tokens, int topk, int model_dim, int experts,
                          int max_rows, void* stream);
 
+/* Expert-parallel step planning on the device (no reference counterpart: the reference has no
+ * dispatch/combine).  flymoe_expert_counts: counts[e] = rows of the ascending per-row expert list
+ * (the sorted_expert_ids of a unit-1 sort) that belong to expert e.  flymoe_ep_plan_direct: from the
+ * rows-per-(rank, expert) matrix counts [world, experts] (every rank's flymoe_expert_counts,
+ * all-gathered) it writes what rank `rank` needs for a step whose dispatch and combine are peer stores:
+ * pos_base / dst_x / dst_scale [experts] for flymoe_dispatch_rows (each rank's operand buffer holds its
+ * local experts in ascending order, every expert padded to a multiple of `unit` rows, sources in rank
+ * order inside an expert; peer_base[r] + off_x / off_scale is where rank r's operand rows / scales
+ * start), and for the rows this rank receives: sorted_ids [cap_rows] (row index, or the pad id
+ * (1<<24)|cap_rows), sorted_expert_ids [cap_rows/unit] (local expert of each row block), num_valid_ids
+ * {extent, extent} and row_dst [cap_rows] (peer_base[source] + off_back + source_row * model_dim * 2,
+ * 0 for pad rows) for flymoe_moe_gemm2_scatter_rows.  Rows beyond cap_rows are not planned; the
+ * dispatch kernel drops them and reports FLYMOE_STATUS_DISPATCH_OVERFLOW.  world <= 8, experts <= 1024;
+ * workspace: flymoe_ep_plan_workspace_elems(world, experts) int32. */
+int flymoe_expert_counts(const int32_t* row_expert, const int32_t* num_valid_ids, int64_t* counts,
+                         int experts, int max_rows, void* stream);
+int64_t flymoe_ep_plan_workspace_elems(int world, int experts);
+int flymoe_ep_plan_direct(const int64_t* counts, const int64_t* peer_base, int64_t off_x,
+                          int64_t off_scale, int64_t off_back, int64_t* dst_x, int64_t* dst_scale,
+                          int64_t* pos_base, int32_t* sorted_ids, int32_t* sorted_expert_ids,
+                          int32_t* num_valid_ids, int64_t* row_dst, int32_t* workspace,
+                          int64_t workspace_elems, int world, int rank, int experts, int unit,
+                          int model_dim, int64_t cap_rows, void* stream);
+
 /* Dense block-scaled FP8 GEMM  c[M,N] = (a . b^T) with per-1x128 activation scales and
  * per-128x128 weight scales -- the stage-2 kernel run with one expert and identity routing.
  * Replaces kernels/blockscale_preshuffle_gemm.py:32-45 (builder) and the launcher :865-901.

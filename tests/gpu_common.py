@@ -53,3 +53,42 @@ def assert_close(actual: torch.Tensor, ref: torch.Tensor, rtol: float, atol: flo
     bad = err > (atol + rtol * r.abs())
     assert not bad.any(), (f"{what}: {int(bad.sum())}/{bad.numel()} outside rtol={rtol} atol={atol}; "
                            f"max abs err {float(err.max()):.4g}, ref max {float(r.abs().max()):.4g}")
+
+
+def covering_subset(topk_ids: torch.Tensor, min_tokens: int = 32, base=()) -> list:
+    """Tokens (ascending) such that every expert that received a token is hit by at least one of them,
+    padded with evenly spaced tokens up to ``min_tokens``: the oracle then dequantises, and the check
+    compares, the weight tiles of every active expert."""
+    ids = torch.as_tensor(topk_ids).to(torch.int64)
+    T = ids.shape[0]
+    chosen = set(int(t) for t in base)
+    covered = set(ids[sorted(chosen)].reshape(-1).tolist()) if chosen else set()
+    active = set(ids.reshape(-1).tolist())
+    for t in range(T):
+        if covered >= active:
+            break
+        row = set(ids[t].tolist())
+        if not row <= covered:
+            chosen.add(t)
+            covered |= row
+    want = min(min_tokens, T)
+    i = 0
+    while len(chosen) < want:
+        chosen.add(int(round(i * (T - 1) / max(1, want - 1))))
+        i += 1
+        if i > 4 * want:
+            chosen.update(range(want))
+    return sorted(chosen)
+
+
+class LazyExperts:
+    """Expert-indexable view that copies one expert's weights to the CPU on demand."""
+
+    def __init__(self, t):
+        self.t = t
+
+    def __len__(self):
+        return self.t.shape[0]
+
+    def __getitem__(self, e):
+        return self.t[e].cpu()

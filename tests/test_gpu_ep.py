@@ -15,12 +15,41 @@ import torch.multiprocessing as mp
 pytestmark = pytest.mark.gpu
 
 
-def _collect(q, world):
-    res = []
-    for _ in range(world):
-        item = q.get(timeout=300)
-        assert item[0] != "error", f"rank {item[1]} failed: {item[2]}"
-        res.append(item)
+def _run_ranks(world, args_of_rank):
+    """Spawn one daemon process per rank, collect one result per rank, and never leave a rank behind: on a
+    failure or a timeout every child is terminated (then killed) before the assertion is raised, so no
+    rank keeps spinning in a collective on a shared GPU."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=args_of_rank(r, q), daemon=True) for r in range(world)]
+    for p in procs:
+        p.start()
+    res, failure = [], None
+    try:
+        for _ in range(world):
+            try:
+                item = q.get(timeout=300)
+            except Exception:                     # noqa: BLE001 - queue.Empty: a rank never reported
+                failure = "a rank did not report within 300 s"
+                break
+            if item[0] == "error":
+                failure = f"rank {item[1]} failed: {item[2]}"
+                break
+            res.append(item)
+        if failure is None:
+            for p in procs:
+                p.join(timeout=120)
+                if p.exitcode != 0:
+                    failure = f"a rank exited with code {p.exitcode}"
+    finally:
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+        for p in procs:
+            p.join(timeout=10)
+            if p.is_alive():
+                p.kill()
+    assert failure is None, failure
     return res
 
 
@@ -42,9 +71,10 @@ def _worker(rank, world, port, routing, chunks, q, fused=False, direct=False):
         _run(rank, world, routing, chunks, q, fused, direct, dev)
     except Exception as exc:                      # noqa: BLE001 - the parent fails at once instead of timing out
         q.put(("error", rank, repr(exc)))
-        raise
-    finally:
-        dist.destroy_process_group()
+        q.close()
+        q.join_thread()
+        os._exit(1)                               # no collective teardown on the error path: it could block
+    dist.destroy_process_group()
 
 
 def _run(rank, world, routing, chunks, q, fused, direct, dev):
@@ -87,16 +117,8 @@ def _run(rank, world, routing, chunks, q, fused, direct, dev):
 def test_expert_parallel_matches_single_gpu(world, routing, chunks):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs, found {torch.cuda.device_count()}")
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, routing, chunks, q)) for r in range(world)]
-    for p in procs:
-        p.start()
-    res = _collect(q, world)
-    for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
+    res = _run_ranks(world, lambda r, q: (r, world, port, routing, chunks, q))
     total_rows = 0
     for rank, same_as_single, repeatable, oracle_ok, status, rows_in, _kind in res:
         assert status == 0, f"rank {rank}: device-side timeout reported"
@@ -120,16 +142,8 @@ def test_fused_combine_matches_single_gpu(world, routing, direct):
     trip in the step)."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs, found {torch.cuda.device_count()}")
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, routing, 1, q, True, direct)) for r in range(world)]
-    for p in procs:
-        p.start()
-    res = _collect(q, world)
-    for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
+    res = _run_ranks(world, lambda r, q: (r, world, port, routing, 1, q, True, direct))
     kinds = {r[6] for r in res}
     assert kinds == {"symmetric_memory"}
     for rank, same_as_single, repeatable, oracle_ok, status, rows_in, _kind in res:

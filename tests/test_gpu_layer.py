@@ -11,7 +11,7 @@ from flydsl_b200 import _lib
 from flydsl_b200 import workloads as wl
 from flydsl_b200.layer import FusedMoEBlockscale, quant_act_1x128
 from oracle import moe_oracle as orc
-from tests.gpu_common import Problem, assert_close, ulp_stats
+from tests.gpu_common import LazyExperts, Problem, assert_close, covering_subset, ulp_stats
 
 pytestmark = pytest.mark.gpu
 RTOL, ATOL = 2e-2, 2e-2
@@ -72,22 +72,13 @@ def test_layer_matches_oracle(cfg, tile_m, impl, mode):
         assert torch.equal(out2, out), "reduce mode must be run-to-run deterministic"
 
 
-class LazyExperts:
-    """Expert-indexable view that copies one expert's weights to the CPU on demand."""
-
-    def __init__(self, t):
-        self.t = t
-
-    def __len__(self):
-        return self.t.shape[0]
-
-    def __getitem__(self, e):
-        return self.t[e].cpu()
-
-
-def dsv3_case(name, subset):
+def dsv3_case(name, base, min_tokens=64):
+    """Runs the layer at full size and checks, against the CPU oracle, a token subset that reaches every
+    active expert at least once (so every expert's weight tiles are compared), plus the ``base`` tokens."""
     cfg = wl.CONFIGS[name]
     p = Problem(cfg, weights_on="cuda")
+    subset = covering_subset(p.ids, min_tokens, base)
+    assert set(p.ids[subset].reshape(-1).tolist()) == set(p.ids.reshape(-1).tolist())
     layer = make_layer(p, 128)
     out = layer(p.d_logits, p.d_xq, p.d_xs_t)
     torch.cuda.synchronize()

@@ -108,8 +108,9 @@ def run_stage2(shape, in_dtype, out_dtype, impl, w_layout, mode, doweight=True):
         rows = T
     torch.cuda.synchronize()
     assert float(out[rows:].float().abs().sum()) == 0.0, "stage 2 wrote past its output rows"
-    ref = orc.pertoken_stage2(a2q, sa2, w2q, sw2, ids, tw, H, doweight, reduce=mode != "rows")
-    return out[:rows].cpu(), ref.view(rows, H)
+    pair = orc.pertoken_stage2(a2q, sa2, w2q, sw2, ids, tw, H, doweight, reduce=False)
+    ref = pair.view(rows, H) if mode == "rows" else pair.sum(dim=1)
+    return out[:rows].cpu(), ref, float(pair.abs().max())
 
 
 @pytest.mark.parametrize("impl", ["simt", "tcgen05"])
@@ -121,12 +122,13 @@ def run_stage2(shape, in_dtype, out_dtype, impl, w_layout, mode, doweight=True):
     ("T128", "int8", "bf16", "plain", "atomic"),
 ])
 def test_pertoken_stage2(shape, in_dtype, out_dtype, w_layout, mode, impl):
-    out, ref = run_stage2(shape, in_dtype, out_dtype, impl, w_layout, mode)
-    peak = float(ref.abs().max())
-    step = 0.0 if out_dtype == "f32" or mode != "atomic" else 2.0 ** (-7 if out_dtype == "bf16" else -10) * peak
+    out, ref, pair_peak = run_stage2(shape, in_dtype, out_dtype, impl, w_layout, mode)
+    # 16-bit outputs round every (token, slot) term (per-pair rows, or the running sum of the atomics):
+    # allow one rounding step of the largest term on top of the bar (terms of opposite sign cancel)
+    step = 0.0 if out_dtype == "f32" or mode == "rows" else 2.0 ** (-7 if out_dtype == "bf16" else -10) * pair_peak
     assert_close(out, ref, RTOL, ATOL + step, f"per-token stage 2 {shape} {in_dtype} {mode} {impl}")
     if out_dtype == "f32":
-        assert_close(out, ref, 1e-4, 1e-5 * peak, f"per-token stage 2 tight {shape} {in_dtype} {impl}")
+        assert_close(out, ref, 1e-4, 1e-5 * pair_peak, f"per-token stage 2 tight {shape} {in_dtype} {impl}")
 
 
 @pytest.mark.parametrize("in_dtype", ["fp8", "int8"])
@@ -134,8 +136,8 @@ def test_pertoken_large_reference_shape(in_dtype):
     """The reference's aiter-style L shape (333 tokens, 4096 x 2048, 17 experts, top-9), both stages."""
     out1, ref1 = run_stage1("L", in_dtype, "bf16", "tcgen05", "plain", False)
     assert_close(out1, ref1, RTOL, ATOL, f"per-token stage 1 L {in_dtype}")
-    out2, ref2 = run_stage2("L", in_dtype, "f32", "tcgen05", "plain", "atomic")
+    out2, ref2, pair_peak = run_stage2("L", in_dtype, "f32", "tcgen05", "plain", "atomic")
     assert_close(out2, ref2, RTOL, ATOL, f"per-token stage 2 L {in_dtype}")
-    out2r, _ = run_stage2("L", in_dtype, "bf16", "tcgen05", "plain", "reduce")
-    assert_close(out2r, ref2, RTOL, ATOL, f"per-token stage 2 L reduce {in_dtype}")
+    out2r, _, _ = run_stage2("L", in_dtype, "bf16", "tcgen05", "plain", "reduce")
+    assert_close(out2r, ref2, RTOL, ATOL + 2.0 ** -7 * pair_peak, f"per-token stage 2 L reduce {in_dtype}")
 
