@@ -200,6 +200,8 @@ def wait_accounting(args, cfg) -> None:
         nkb = max(m[:, 6].mean(), 1.0)
         print(json.dumps({"kernel": tag, "workload": cfg.name, "k_blocks_per_cta": round(nkb, 1),
                           "cycles_per_k_block": round(m[:, 0].mean() / nkb, 1),
+                          "tma_role_cycles_per_k_block": round(p[:, 0].mean() / nkb, 1),
+                          "epilogue_role_cycles_per_k_block": round(e[:, 0].mean() / nkb, 1),
                           "tma_wait_free_smem_stage": round(p[:, 1].mean() / nkb, 1),
                           "mma_wait_tmem_stage": round(m[:, 1].mean() / nkb, 1),
                           "mma_wait_operands": round(m[:, 2].mean() / nkb, 1),
@@ -421,6 +423,101 @@ def run_dense_gemm(args) -> dict:
             "cpu_baseline": None, "e2e": None, "clocks": clocks, "gpu_launches": 2 * args.steps}
 
 
+def run_pertoken(args, cfg) -> dict:
+    """`--scaling pertoken`: the two grouped GEMM stages of the per-token / per-channel-scale family
+    (kernels.moe_gemm_2stage, fp8) on the workload's shapes and routing.  The whole K range accumulates in
+    tensor memory and every tile is drained once, so this is the control for the block-scaled kernels: same
+    main loop without the per-K-block scale pass.  Stage 2's input is the quantised stage-1 output, prepared
+    outside the timed region (the reference quantises between the stages outside its kernels, too)."""
+    from flydsl_b200 import _lib
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks = load_peaks()
+    lib = _lib.load()
+    T, k, H, I, E, U = cfg.tokens, cfg.topk, cfg.model_dim, cfg.inter_dim, cfg.experts, args.tile_m
+    g = torch.Generator(device=dev).manual_seed(cfg.seed)
+    w1q = torch.empty((E, 2 * I, H), dtype=torch.float8_e4m3fn, device=dev)
+    w2q = torch.empty((E, H, I), dtype=torch.float8_e4m3fn, device=dev)
+    sw1 = torch.empty((E, 2 * I), dtype=torch.float32, device=dev)
+    sw2 = torch.empty((E, H), dtype=torch.float32, device=dev)
+    for e in range(E):
+        q, sc = wl.quant_groups(torch.randn((2 * I, H), generator=g, device=dev) * 0.02)
+        w1q[e], sw1[e] = q, sc.view(-1)
+        q, sc = wl.quant_groups(torch.randn((H, I), generator=g, device=dev) * 0.02)
+        w2q[e], sw2[e] = q, sc.view(-1)
+    xq, sx = wl.quant_groups(torch.randn((T, H), generator=g, device=dev))
+    logits = wl.make_logits(cfg).to(dev)
+    i32, f32 = torch.int32, torch.float32
+    tw, ids, tei = (torch.empty((T, k), dtype=dt, device=dev) for dt in (f32, i32, i32))
+    cap = T * k + E * U - k
+    blocks = (cap + U - 1) // U
+    rows = blocks * U
+    s_ids, s_w = torch.empty(rows, dtype=i32, device=dev), torch.empty(rows, dtype=f32, device=dev)
+    s_e, nv = torch.empty(blocks, dtype=i32, device=dev), torch.zeros(2, dtype=i32, device=dev)
+    ws = torch.empty(max(1, int(lib.flymoe_moe_sorting_workspace_elems(T, E, k, U))), dtype=i32, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+    _lib.check(lib.flymoe_topk_gating_softmax(logits.data_ptr(), _lib.F32, tw.data_ptr(), ids.data_ptr(), tei.data_ptr(),
+                                              T, E, k, 1, st), "gating")
+    _lib.check(lib.flymoe_moe_sorting(ids.data_ptr(), tw.data_ptr(), s_ids.data_ptr(), s_w.data_ptr(), s_e.data_ptr(),
+                                      nv.data_ptr(), None, 0, None, ws.data_ptr(), ws.numel(), T, E, k, U, st), "sorting")
+    xs = torch.empty((rows, H), dtype=torch.uint8, device=dev)
+    _lib.check(lib.flymoe_gather_rows(xq.data_ptr(), xs.data_ptr(), s_ids.data_ptr(), nv.data_ptr(), T, k, H,
+                                      _lib.ROWS_BY_TOKEN, rows, st), "gather")
+    out1 = torch.zeros((rows, I), dtype=torch.bfloat16, device=dev)
+    out2 = torch.zeros((T, H), dtype=torch.bfloat16, device=dev)
+
+    def stage1():
+        _lib.check(lib.flymoe_moe_gemm1_pertoken(
+            out1.data_ptr(), xs.data_ptr(), sx.data_ptr(), w1q.data_ptr(), sw1.data_ptr(), s_ids.data_ptr(),
+            s_e.data_ptr(), s_w.data_ptr(), nv.data_ptr(), T, I, H, blocks, E, k, U, 0, _lib.E4M3, _lib.BF16,
+            _lib.ROWS_SORTED, _lib.ROWS_BY_TOKEN, _lib.ROWS_SORTED, _lib.IMPL_TCGEN05, st), "gemm1_pertoken")
+    stage1()
+    a2q, sa2 = wl.quant_groups(out1.float())
+    sa2 = sa2.view(-1).contiguous()
+
+    def stage2():
+        _lib.check(lib.flymoe_moe_gemm2_pertoken(
+            out2.data_ptr(), a2q.data_ptr(), sa2.data_ptr(), w2q.data_ptr(), sw2.data_ptr(), s_ids.data_ptr(),
+            s_e.data_ptr(), s_w.data_ptr(), nv.data_ptr(), T, H, I, blocks, E, k, U, 1, _lib.E4M3, _lib.BF16, 1,
+            _lib.ROWS_SORTED, _lib.ROWS_SORTED, _lib.IMPL_TCGEN05, st), "gemm2_pertoken")
+    stream = torch.cuda.current_stream()
+    for _ in range(args.warmup):
+        stage1()
+        stage2()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(physical_gpu_index(0))
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps + 1)]
+    evs[0].record(stream)
+    for i in range(args.steps):
+        stage1()
+        evs[2 * i + 1].record(stream)
+        out2.zero_()
+        stage2()
+        evs[2 * i + 2].record(stream)
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    if _lib.device_status() != 0:
+        raise RuntimeError("a kernel reported a device-side timeout")
+    s1 = statistics.mean(evs[2 * i].elapsed_time(evs[2 * i + 1]) for i in range(args.steps))
+    s2 = statistics.mean(evs[2 * i + 1].elapsed_time(evs[2 * i + 2]) for i in range(args.steps))
+    f1, f2 = 4.0 * T * k * I * H, 2.0 * T * k * H * I
+    fp8_peak = 2.0 * peaks["bf16_tflops"]
+    e_act = int(torch.unique(ids).numel())
+    wbytes1, wbytes2 = e_act * 2.0 * I * H, e_act * 1.0 * I * H
+    return {"metric": "fp8_pertoken_moe_gemm_tflops", "value": round((f1 + f2) / ((s1 + s2) * 1e-3) / 1e12, 2), "unit": UNIT,
+            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(s1 + s2, 4),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "fp8_e4m3 (fp32 accumulate, one scale per row and per weight row)", "data": "synthetic",
+            "config": {**wl.describe(cfg), "tile_m": U, "what": "stage 1 + stage 2 kernels of kernels.moe_gemm_2stage only"},
+            "stage1": {"ms": round(s1, 4), "tflops": round(f1 / (s1 * 1e-3) / 1e12, 1),
+                       "frac_of_2x_bf16_peak": round(f1 / (s1 * 1e-3) / 1e12 / fp8_peak, 4),
+                       "weight_gbs": round(wbytes1 / (s1 * 1e-3) / 1e9, 1)},
+            "stage2": {"ms": round(s2, 4), "tflops": round(f2 / (s2 * 1e-3) / 1e12, 1),
+                       "frac_of_2x_bf16_peak": round(f2 / (s2 * 1e-3) / 1e12 / fp8_peak, 4),
+                       "weight_gbs": round(wbytes2 / (s2 * 1e-3) / 1e9, 1)},
+            "roofline": None, "cpu_baseline": None, "e2e": None, "clocks": clocks, "gpu_launches": 2 * args.steps}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -448,6 +545,8 @@ def main() -> None:
     ap.add_argument("--nccl-max-ctas", type=int, default=0, help="sets NCCL_MAX_CTAS before the group is created")
     ap.add_argument("--cpu-experts", type=int, default=48, help="experts in the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--scaling", default="block", choices=["block", "pertoken"],
+                    help="'pertoken': time the per-token-scale GEMM stages (kernels.moe_gemm_2stage) on the workload's shapes")
     ap.add_argument("--no-parity", action="store_true", help="skip the post-run check against the CPU oracle")
     ap.add_argument("--no-same-work", action="store_true",
                     help="multi-GPU: skip timing the same per-GPU work on one GPU (weak_scaling_eff)")
@@ -486,6 +585,9 @@ def main() -> None:
         return
     if args.wait_accounting:
         wait_accounting(args, cfg)
+        return
+    if args.scaling == "pertoken":
+        print(json.dumps(run_pertoken(args, cfg)), flush=True)
         return
     line = run_single_gpu(args, cfg, with_parity=not args.no_parity)
     default_run = args.workload is None and args.tokens is None and args.experts is None

@@ -1,7 +1,7 @@
 // Grouped FP8 (e4m3) GEMM for both MoE stages on sm_100a.
 //
 // One persistent CTA per SM walks a static sequence of (sorted row block, N tile)
-// tiles.  Warp roles (640 threads):
+// tiles.  Warp roles (384 threads):
 //   warp 0      TMA producer: per 128-wide K block one A box (tile_m sorted rows x 128 B)
 //               and 256 weight rows x 128 B into a 4-deep (stage 2: 3-deep) shared-memory
 //               ring (128-byte swizzle, K-major).
@@ -9,36 +9,31 @@
 //               two 256-column TMEM accumulator stages; tcgen05.commit releases the smem
 //               stage and publishes the TMEM stage.
 //   warp 2      store warp: sends the finished rows that the epilogue threads parked in
-//               the shared-memory staging tile to global memory as bulk stores / bulk
-//               reductions, one per row, so their issue cost is off the epilogue's path.
-//   warp 3      scale producer (block-scaled mode): per K block the product of every row's
-//               activation scale and the tile's two weight-block scales, loaded one K block
-//               ahead and parked in a two-slot shared-memory table, so the epilogue threads
-//               hold no scale pointers or prefetched scales in registers.
-//   warps 4-19  epilogue, four warpgroups.  Each thread owns one sorted row (its TMEM
-//               lane) and a 64-column slice of the tile, so four warps per scheduler
-//               partition cover each other's tcgen05.ld / mbarrier latency.
+//               shared-memory slots to global memory as bulk stores / bulk reductions
+//               (one per slot), so their issue cost is off the epilogue's path.
+//   warps 4-11  epilogue, two warpgroups.  Each thread owns one sorted row (its TMEM lane)
+//               and 128 of the tile's 256 accumulator columns.
 //
 // Two scaling modes (template parameter SCALING):
 //   kScaleBlock128   activation scales per (row, 128 K), weight scales per 128x128 block.
 //               The scales are arbitrary fp32, so they cannot ride inside the MMA: every
 //               K block starts its TMEM stage from zero, and the epilogue folds the K
 //               block's partial sums into register accumulators with the product of the
-//               two scales (packed fma.rn.f32x2).
+//               row's activation scale and the weight block's scale (packed fma.rn.f32x2).
 //   kScalePerToken   one scale per activation row and one per weight row (output
 //               column): the MMA accumulates over the whole K range in TMEM and the
 //               epilogue drains each tile once.  fp8 e4m3 or int8 operands.
 //
-// Stage 1 tile: 128 gate rows + 128 up rows of W1 (one quantisation group of the output);
-// warpgroup w takes gate columns [32w, 32w+32) and the matching up columns, computes
-// silu(gate)*up and either stores f16/bf16 or requantises to e4m3 with the per-row 1x128
-// scale (row amax exchanged between the four warpgroups through shared memory).
-// Stage 2 tile: 256 rows of W2; warpgroup w takes columns [64w, 64w+64); every thread
-// multiplies its row by the routing weight and parks its 128 bytes in the row-major staging
-// tile; the store warp adds each 512-byte row into out[token] with one bulk reduce
-// (cp.reduce.async.bulk), bulk-stores per-pair rows for a later top-k reduce, or (ROW_DST
-// instantiation) stores each row to a caller-given address, which may be in a peer GPU's
-// memory.  The same kernel with one expert and identity routing is the dense block-scaled GEMM.
+// Stage 1 tile: 128 gate rows + 128 up rows of W1 (one quantisation group of the
+// output); each warpgroup takes 64 gate + 64 up columns, computes silu(gate)*up and
+// either stores f16/bf16 or requantises to e4m3 with the per-row 1x128 scale (row amax
+// exchanged between the two warpgroups through shared memory).
+// Stage 2 tile: 256 rows of W2; each warpgroup takes 128 columns; every thread multiplies
+// its row by the routing weight, parks the 256 bytes in a private shared-memory slot and
+// the store warp adds them into out[token] with one bulk reduce (cp.reduce.async.bulk),
+// bulk-stores per-pair rows for a later top-k reduce, or (ROW_DST instantiation) stores
+// each row to a caller-given address, which may be in a peer GPU's memory.  The same
+// kernel with one expert and identity routing is the dense block-scaled GEMM.
 //
 // Every wait is bounded: when one gives up it raises the CTA's abort flag and the
 // device status word, every role drains out, TMEM is released and the kernel returns.
@@ -63,47 +58,23 @@ constexpr int kScaleBlock128 = 0;
 constexpr int kScalePerToken = 1;
 
 constexpr int kMaxStages = 4;
-// Depth of the shared-memory operand ring.  Stage 2 gives one slot up for the staging tile
-// from which finished output rows leave by bulk reduce/store.
+// Depth of the shared-memory operand ring.  Stage 2 gives one slot up for a staging area from
+// which finished output rows leave by bulk reduce/store (measured: a 3-deep ring is as fast as 4).
 template <int STAGE> struct RingDepth { static constexpr int value = STAGE == 1 ? 4 : 3; };
-// Row-major staging tile for finished output: stage 1 holds the 128 e4m3 codes of one row's
-// quantisation group, stage 2 the row's 256 16-bit results; 16 B of skew per row keep the
-// 16-byte shared-memory stores of a warp (one row per lane) conflict-free.
+// Per-epilogue-thread staging slot for finished output: stage 2 holds 256 B of 16-bit results,
+// stage 1 holds 64 e4m3 codes; 16 B of skew keep 16-byte shared-memory stores conflict-free.
 template <int STAGE> struct Staging {
-  static constexpr int row_bytes = STAGE == 1 ? 128 : 512;
-  static constexpr int stride = row_bytes + 16;
-  static constexpr int bytes = BM * stride;
+  static constexpr int stride = STAGE == 1 ? 80 : 272;
+  static constexpr int bytes = 256 * stride;
 };
 constexpr int kATileBytes = BM * BK;            // 16 KB
 constexpr int kBTileBytes = BN * BK;            // 32 KB
 constexpr int kStageBytes = kATileBytes + kBTileBytes;
 constexpr int kAccStages = 2;
 constexpr int kTmemCols = 512;
-// Epilogue warpgroups: each takes BN / kEpilogueGroups accumulator columns of every row.  Two groups
-// (384 threads, 128 accumulators per thread) or four (640 threads, 64 per thread).
-#ifndef FLYMOE_EPI_GROUPS
-#define FLYMOE_EPI_GROUPS 2
-#endif
-constexpr int kEpilogueGroups = FLYMOE_EPI_GROUPS;
-static_assert(kEpilogueGroups == 2 || kEpilogueGroups == 4, "two or four epilogue warpgroups");
-constexpr int kEpilogueWarps = 4 * kEpilogueGroups;
-constexpr int kNumThreads = 128 + 32 * kEpilogueWarps;
-constexpr int NACC = BN / kEpilogueGroups;      // fp32 accumulators per epilogue thread
-constexpr int NHALF = NACC / 2;                 // stage 1: gate columns (and as many up columns) per thread
-// Register re-split: kNumThreads x kRegsLaunch registers are allocated at launch; the producer
-// warpgroup drops to kRegsProducer and the epilogue warpgroups rise to kRegsEpilogue.  The sum must not
-// exceed the launch allocation: a larger request would wait forever for registers nobody releases.
-constexpr int kRegsLaunch = kEpilogueGroups == 2 ? 168 : 96;
-constexpr int kRegsProducer = kEpilogueGroups == 2 ? 40 : 32;
-constexpr int kRegsEpilogue = kEpilogueGroups == 2 ? 232 : 112;
-static_assert(kNumThreads * kRegsLaunch <= 65536, "launch allocation exceeds the register file");
-static_assert(128 * kRegsProducer + 32 * kEpilogueWarps * kRegsEpilogue <= kNumThreads * kRegsLaunch,
-              "setmaxnreg split exceeds the launch allocation");
+constexpr int kNumThreads = 384;
+constexpr int kEpilogueWarps = 8;
 constexpr unsigned long long kWaitLimitNs = 4000000000ull;   // 4 s
-// Accumulator columns one tcgen05.ld of the block-scaled epilogue fetches (two such buffers per thread).
-#ifndef FLYMOE_EPI_CHUNK
-#define FLYMOE_EPI_CHUNK (FLYMOE_EPI_GROUPS == 2 ? 32 : 8)
-#endif
 
 struct __align__(16) SmemCtrl {
   unsigned long long full[kMaxStages];
@@ -111,21 +82,16 @@ struct __align__(16) SmemCtrl {
   unsigned long long tmem_full[kAccStages];
   unsigned long long tmem_empty[kAccStages];
   unsigned long long amax_bar[2];
-  unsigned long long scl_full[kAccStages];      // scale producer -> epilogue: scl[stage] written
-  unsigned long long stg_full;                  // epilogue warps -> store warp: staging rows and destinations written
-  unsigned long long stg_free;                  // store warp -> epilogue warps: the staging tile has been read
-  unsigned long long stg_dst[BM];               // per row of the tile: global address of its segment, 0 = none
+  unsigned long long stg_full;                  // epilogue warps -> store warp: slots and destinations written
+  unsigned long long stg_free;                  // store warp -> epilogue warps: slots have been read
+  unsigned long long stg_dst[256];              // per epilogue thread: global address of its row segment, 0 = none
   uint32_t tmem_base;
   int abort_flag;
-  float amax[2][kEpilogueGroups][BM];
-  // per accumulator stage and row: {c0, c0, c1, c1}, c = activation scale x weight-block scale of the
-  // K block in that stage (stage 1: c0 gate, c1 up; stage 2: c0 columns 0-127, c1 columns 128-255)
-  float4 scl[kAccStages][BM];
+  float amax[2][2][BM];
 };
 template <int STAGE> constexpr size_t smem_bytes() {
   return size_t(RingDepth<STAGE>::value) * kStageBytes + Staging<STAGE>::bytes + sizeof(SmemCtrl) + 1024;
 }
-static_assert(smem_bytes<1>() <= 232448 && smem_bytes<2>() <= 232448, "shared memory budget of one SM exceeded");
 
 // Optional whole-kernel wait accounting (build with -DFLYMOE_PROF, `python -m flydsl_b200.build
 // --prof`): every CTA's producer thread, MMA thread and first epilogue thread add up the cycles they
@@ -179,50 +145,27 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "=r"(done) : "r"(bar), "r"(parity) : "memory");
   return done;
 }
-// Non-suspending probe of a barrier phase (try_wait may park the thread until the phase flips).
-__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-  return done;
-}
 __device__ __forceinline__ unsigned long long global_timer_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
-// Probe used by the waits on the critical path (those without back-off).
-#ifndef FLYMOE_HOT_WAIT
-#define FLYMOE_HOT_WAIT mbar_try_wait
-#endif
 // Bounded wait.  Returns false when the CTA is aborting or the time limit ran out.
 // `backoff_ns` > 0 makes a role that has slack sleep between polls instead of competing for
 // issue slots with the epilogue warps of its scheduler partition.
-__device__ __forceinline__ int ld_shared_volatile(uint32_t addr) {
-  int v;
-  asm volatile("ld.volatile.shared::cta.b32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_shared_volatile(uint32_t addr, int v) {
-  asm volatile("st.volatile.shared::cta.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
-}
-// `abort_flag` is the shared-memory address of the CTA's abort word.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t abort_flag,
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int code, unsigned backoff_ns = 0,
                                           unsigned long long limit_ns = kWaitLimitNs) {
-  if (FLYMOE_HOT_WAIT(bar, parity)) return true;
+  if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_timer_ns();
 #pragma unroll 1
   for (uint32_t it = 1;; ++it) {
-    if (backoff_ns ? mbar_try_wait(bar, parity) : FLYMOE_HOT_WAIT(bar, parity)) return true;
+    if (mbar_try_wait(bar, parity)) return true;
     if (backoff_ns) __nanosleep(backoff_ns);
     if ((it & 0xFF) == 0) {
-      if (ld_shared_volatile(abort_flag)) return false;
+      if (*abort_flag) return false;
       if (global_timer_ns() - t0 > limit_ns) {
-        st_shared_volatile(abort_flag, 1);
+        *abort_flag = 1;
         atomicCAS(status, 0, code);
         return false;
       }
@@ -266,20 +209,6 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                : "memory");
 }
-__device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t* v) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-      : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_x8(uint32_t taddr, uint32_t* v) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
-      : "r"(taddr) : "memory");
-}
 __device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t* v) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -290,12 +219,6 @@ __device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t* v) {
         "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
         "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
       : "r"(taddr) : "memory");
-}
-template <int N> __device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t* v) {
-  static_assert(N == 8 || N == 16 || N == 32, "tcgen05.ld chunk of 8, 16 or 32 columns");
-  if (N == 8) tmem_ld_x8(taddr, v);
-  else if (N == 16) tmem_ld_x16(taddr, v);
-  else tmem_ld_x32(taddr, v);
 }
 __device__ __forceinline__ unsigned long long pack_f32x2(float x) {
   unsigned long long r;
@@ -339,7 +262,7 @@ constexpr uint32_t kInstrDescShape = (uint32_t(BN >> 3) << 17) | (uint32_t(BM >>
 constexpr uint32_t kInstrDescF8 = (1u << 4) | (0u << 7) | (0u << 10) | kInstrDescShape;
 constexpr uint32_t kInstrDescI8 = (2u << 4) | (1u << 7) | (1u << 10) | kInstrDescShape;
 
-// Bulk operations from the staging tile to a contiguous global row segment (16-byte aligned, size % 16 == 0).
+// Bulk operations from a staging slot to a contiguous global row segment (16-byte aligned, size % 16 == 0).
 __device__ __forceinline__ void bulk_reduce_add_bf16(void* g, uint32_t s, uint32_t bytes) {
   asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.noftz.bf16 [%0], [%1], %2;"
                ::"l"(g), "r"(s), "r"(bytes) : "memory");
@@ -380,14 +303,14 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   constexpr int kStages = RingDepth<STAGE>::value;
   uint8_t* staging = smem + size_t(kStages) * kStageBytes;
   SmemCtrl* ctrl = reinterpret_cast<SmemCtrl*>(staging + Staging<STAGE>::bytes);
-  const uint32_t abort_flag = smem_u32(&ctrl->abort_flag);
+  volatile int* abort_flag = &ctrl->abort_flag;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int KB = a.k_dim / BK;
 
   const int valid_rows = min(__ldg(a.num_valid_ids), a.size_expert_ids * a.tile_m);
-  // Outputs that leave through the staging tile (everything except 16-bit stage-1 and fp32 stage-2 output)
+  // Outputs that leave through the staging slots (everything except 16-bit stage-1 and fp32 stage-2 output)
   const bool uses_staging = STAGE == 1 ? a.out_dtype == FLYMOE_E4M3 : a.out_dtype != FLYMOE_F32;
   TileSched sched;
   sched.num_mblocks = (valid_rows + a.tile_m - 1) / a.tile_m;
@@ -404,7 +327,6 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       mbar_init(smem_u32(&ctrl->tmem_full[i]), 1);
       mbar_init(smem_u32(&ctrl->tmem_empty[i]), kEpilogueWarps);
     }
-    for (int i = 0; i < kAccStages; ++i) mbar_init(smem_u32(&ctrl->scl_full[i]), 1);
     mbar_init(smem_u32(&ctrl->amax_bar[0]), kEpilogueWarps);
     mbar_init(smem_u32(&ctrl->amax_bar[1]), kEpilogueWarps);
     mbar_init(smem_u32(&ctrl->stg_full), kEpilogueWarps);
@@ -422,8 +344,12 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   tcgen05_fence_after();
   const uint32_t tmem_base = ctrl->tmem_base;
 
+  // Register re-split: 384 threads x 168 registers are allocated at launch; the producer warpgroup
+  // drops to 40 and the two epilogue warpgroups rise to 232 (128*40 + 256*232 = 384*168 exactly --
+  // a larger request would wait forever for registers that are never released).
+  static_assert(128 * 40 + 256 * 232 <= kNumThreads * 168, "setmaxnreg split exceeds the launch allocation");
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsProducer));
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
     if (warp == 0 && lane == 0) {
       // ---------------------------------------------------------------- TMA producer
       int stage = 0;
@@ -519,9 +445,9 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       PROF_WRITE(1);
     } else if (warp == 2 && uses_staging) {
       // ---------------------------------------------------------------- store warp
-      // Issues the bulk store / bulk reduce of every row of the staging tile, four rows per lane, so
-      // that the cycles each of those operations takes to be accepted are spent here and not by the
-      // epilogue warps between two tiles.
+      // Issues the bulk store / bulk reduce of every epilogue thread's staging slot, eight slots per
+      // lane, so that the ~10 cycles each of those 256 operations takes to be accepted are spent here
+      // and not by the epilogue warps between two tiles.
       bool ok = true;
       uint32_t it = 0;
       int mb_next = 0, n_next = 0, e_next = -1;
@@ -529,6 +455,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         sched.decode(blockIdx.x, mb_next, n_next);
         e_next = __ldg(a.sorted_expert_ids + mb_next);
       }
+      constexpr uint32_t kSlotBytes = STAGE == 1 ? 64u : 256u;
       const bool bf = a.out_dtype == FLYMOE_BF16;
       for (int t = blockIdx.x; t < sched.total && ok; t += gridDim.x) {
         const int e = e_next, n = n_next;
@@ -538,90 +465,33 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         }
         if (e < 0 || e >= a.experts) continue;
         if (!mbar_wait(smem_u32(&ctrl->stg_full), it & 1, abort_flag, a.status, 6, 64)) { ok = false; break; }
-        // stage 2: the last tile of a row may hold fewer than 256 columns (n_dim = 64 or 128 mod 256)
-        const uint32_t bytes = STAGE == 1 ? 128u : uint32_t(min(BN, a.n_dim - n * BN)) * 2u;
+        // stage 2 with n_dim = 64 mod 128 (dense GEMM only): the tile's last segment holds 64 columns
+        const int cols_left = STAGE == 2 ? a.n_dim - n * BN : 0;
 #pragma unroll
-        for (int i = 0; i < BM / 32; ++i) {
-          const int row = i * 32 + lane;
-          const unsigned long long dst = ctrl->stg_dst[row];
+        for (int i = 0; i < 8; ++i) {
+          const int sl = i * 32 + lane;
+          const unsigned long long dst = ctrl->stg_dst[sl];
           if (dst != 0ull) {
-            const uint32_t sp = smem_u32(staging + size_t(row) * Staging<STAGE>::stride);
+            const uint32_t sp = smem_u32(staging + size_t(sl) * Staging<STAGE>::stride);
             void* gp = reinterpret_cast<void*>(dst);
+            const uint32_t bytes = (STAGE == 2 && cols_left - (sl >> 7) * 128 < 128) ? kSlotBytes / 2 : kSlotBytes;
             if (STAGE == 1 || !a.accumulate) bulk_store(gp, sp, bytes);
             else if (bf) bulk_reduce_add_bf16(gp, sp, bytes);
             else bulk_reduce_add_f16(gp, sp, bytes);
           }
         }
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-        bulk_wait_read_all();                      // the staging tile may be overwritten from here on
+        bulk_wait_read_all();                      // the slots may be overwritten from here on
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&ctrl->stg_free));
         ++it;
       }
       bulk_wait_all();                             // every row segment has landed before the CTA retires
-    } else if (warp == 3 && SCALING == kScaleBlock128) {
-      // ---------------------------------------------------------------- scale producer
-      // Each lane serves four rows of the tile.  The scales of K block kb+1 are requested while
-      // those of kb are written, so their latency is spent here; a table slot is rewritten only
-      // after every epilogue warp has handed the TMEM stage of the same index back, which it does
-      // after reading the slot.
-      int acc = 0;
-      uint32_t acc_phase = 0;
-      bool ok = true;
-      const int pad_id = (a.topk << 24) | a.num_tokens;
-      const int wblk_per_expert = (STAGE == 1 ? 2 * a.n_dim : a.n_dim) / 128;
-      for (int t = blockIdx.x; t < sched.total && ok; t += gridDim.x) {
-        int mb, n;
-        sched.decode(t, mb, n);
-        const int e = __ldg(a.sorted_expert_ids + mb);
-        if (e < 0 || e >= a.experts) continue;
-        int soff[4];                           // element offset of the row's first scale, -1 = none (pad row)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int row = j * 32 + lane;
-          const int r = mb * a.tile_m + row;
-          const int id = (row < a.tile_m && r < valid_rows) ? __ldg(a.sorted_ids + r) : pad_id;
-          const int tok = id_token(id), slot = id_slot(id);
-          const bool valid = tok < a.num_tokens && slot < a.topk;
-          const int sidx = a.a_scale_layout == FLYMOE_ROWS_BY_TOKEN ? tok
-                         : a.a_scale_layout == FLYMOE_ROWS_BY_PAIR ? tok * a.topk + slot : r;
-          soff[j] = valid ? sidx * int(a.sa_row_stride) : -1;
-        }
-        const int blk0 = STAGE == 1 ? n : n * 2;
-        const bool blk1_ok = STAGE == 1 ? true : (n * BN + 128 < a.n_dim);
-        const int blk1 = STAGE == 1 ? a.n_dim / 128 + n : (blk1_ok ? blk0 + 1 : blk0);
-        const float* sw0 = a.scale_w + ((long long)e * wblk_per_expert + blk0) * KB;
-        const int sw1_off = (blk1 - blk0) * KB;
-        const int sa_stride = int(a.sa_stride);
-        float sa[4], s0, s1;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) sa[j] = soff[j] >= 0 ? __ldg(a.scale_a + soff[j]) : 0.f;
-        s0 = __ldg(sw0);
-        s1 = __ldg(sw0 + sw1_off);
-        for (int kb = 0; kb < KB; ++kb) {
-          if (!mbar_wait(smem_u32(&ctrl->tmem_empty[acc]), acc_phase ^ 1, abort_flag, a.status, 8, 32)) { ok = false; break; }
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float c0 = sa[j] * s0, c1 = sa[j] * s1;
-            ctrl->scl[acc][j * 32 + lane] = make_float4(c0, c0, c1, c1);
-          }
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&ctrl->scl_full[acc]));
-          if (kb + 1 < KB) {
-            const float* sa_kb = a.scale_a + (long long)(kb + 1) * sa_stride;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) sa[j] = soff[j] >= 0 ? __ldg(sa_kb + soff[j]) : 0.f;
-            s0 = __ldg(sw0 + kb + 1);
-            s1 = __ldg(sw0 + kb + 1 + sw1_off);
-          }
-          if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
-        }
-      }
     }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsEpilogue));
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
     // ------------------------------------------------------------------ epilogue
-    const int wg = (warp - 4) >> 2;          // 0..3: which 64-column slice of the accumulator
+    const int wg = (warp - 4) >> 2;          // 0 or 1
     const int q = warp & 3;                  // TMEM lane quadrant of this warp
     const int row_in_tile = q * 32 + lane;
     const bool warp_active = q * 32 < a.tile_m;
@@ -634,22 +504,24 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     static_assert(kAccStages == 2, "the epilogue's stage/phase stepping assumes two accumulator stages");
     const uint32_t full_bar0 = smem_u32(&ctrl->tmem_full[0]);     // stage 1's barrier is 8 bytes further
     const uint32_t empty_bar0 = smem_u32(&ctrl->tmem_empty[0]);
-    const uint32_t scl_bar0 = smem_u32(&ctrl->scl_full[0]);
+    constexpr int NACC = 128;                // fp32 accumulators per thread
+    // Routing of a tile (expert id, this thread's packed row id) is loaded one tile ahead.
     const int pad_id = (a.topk << 24) | a.num_tokens;
-    // TMEM columns of this thread's two 32-column halves.  Stage 1: gate columns [32wg, 32wg+32) and
-    // the up columns 128 further; stage 2: columns [64wg, 64wg+64).
-    const uint32_t tcol0 = tmem_base + lane_base + (STAGE == 1 ? uint32_t(wg * NHALF) : uint32_t(wg * NACC));
-    const uint32_t tcol1 = tmem_base + lane_base + (STAGE == 1 ? uint32_t(128 + wg * NHALF) : uint32_t(wg * NACC + NHALF));
+    int mb_next = 0, n_next = 0, e_next = -1, id_next = pad_id;
+    auto load_routing = [&](int tt) {
+      sched.decode(tt, mb_next, n_next);
+      e_next = __ldg(a.sorted_expert_ids + mb_next);
+      const int rr = mb_next * a.tile_m + row_in_tile;
+      id_next = (row_in_tile < a.tile_m && rr < valid_rows) ? __ldg(a.sorted_ids + rr) : pad_id;
+    };
+    if (int(blockIdx.x) < sched.total) load_routing(blockIdx.x);
     for (int t = blockIdx.x; t < sched.total && ok; t += gridDim.x) {
-      // Routing of the tile (expert id, this thread's packed row id): the loads overlap the tile's first
-      // K block, which the tensor cores are still working on.
-      int mb, n;
-      sched.decode(t, mb, n);
-      const int e = __ldg(a.sorted_expert_ids + mb);
+      const int mb = mb_next, n = n_next, e = e_next, id = id_next;
+      if (t + int(gridDim.x) < sched.total) load_routing(t + gridDim.x);
       if (e < 0 || e >= a.experts) continue;
+
       const int r = mb * a.tile_m + row_in_tile;
       const bool in_tile = row_in_tile < a.tile_m && r < valid_rows;
-      const int id = in_tile ? __ldg(a.sorted_ids + r) : pad_id;
       const int tok = id_token(id), slot = id_slot(id);
       const bool valid = in_tile && tok < a.num_tokens && slot < a.topk;
       long long sidx = 0;
@@ -657,77 +529,88 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         sidx = a.a_scale_layout == FLYMOE_ROWS_BY_TOKEN ? (long long)tok
              : a.a_scale_layout == FLYMOE_ROWS_BY_PAIR ? (long long)tok * a.topk + slot : (long long)r;
       }
-      // stage 2: a warpgroup whose 64 columns lie beyond n_dim (last tile of a row) has nothing to do
-      const bool half_ok = STAGE == 1 ? true : (n * BN + wg * NACC < a.n_dim);
+      // stage 2: a warpgroup whose 128 columns lie beyond n_dim (last tile of a row) has nothing to do
+      const bool half_ok = STAGE == 1 ? true : (n * BN + wg * 128 < a.n_dim);
+      // routing weight of this row, used after the K loop.  The loop runs at the register limit, and where
+      // this value is requested decides whether ptxas spills inside it: stage 2 asks here (its latency
+      // hides behind the loop), stage 1 after the loop (measured: no spills either way, `-Xptxas -v`).
+      float wgt = 1.f;
+      if (STAGE == 2 && a.doweight && valid) wgt = __ldg(a.sorted_weights + r);
       const bool work = warp_active && half_ok;
-      // routing weight of this row: loaded now, used after the K loop
-      const float wgt = (a.doweight && valid) ? __ldg(a.sorted_weights + r) : 1.f;
+      // stage 1: first half = gate columns, second half = up columns; stage 2: two halves of 128 columns
+      const uint32_t tcol0 = tmem_base + lane_base + (STAGE == 1 ? uint32_t(wg * 64) : uint32_t(wg * 128));
+      const uint32_t tcol1 = tmem_base + lane_base + (STAGE == 1 ? uint32_t(128 + wg * 64) : uint32_t(wg * 128 + 64));
       float accv[NACC];
-
       if (SCALING == kScaleBlock128) {
-        // fp32 accumulators held as packed pairs so the scale-FMA runs as fma.rn.f32x2
-        unsigned long long acc2[NACC / 2];
+      const float* sa_ptr = a.scale_a + sidx * a.sa_row_stride;
+      // weight block scales of this tile
+      const int wblk_per_expert = (STAGE == 1 ? 2 * a.n_dim : a.n_dim) / 128;
+      const int blk0 = STAGE == 1 ? n : n * 2 + wg;
+      const int blk1 = STAGE == 1 ? a.n_dim / 128 + n : blk0;
+      const float* sw0_ptr = a.scale_w + ((long long)e * wblk_per_expert + (half_ok ? blk0 : 0)) * KB;
+      const int sw1_off = (blk1 - (half_ok ? blk0 : 0)) * KB;      // up-projection scales, relative to sw0_ptr
+
+      // fp32 accumulators held as packed pairs so the scale-FMA runs as fma.rn.f32x2
+      unsigned long long acc2[NACC / 2];
 #pragma unroll
-        for (int j = 0; j < NACC / 2; ++j) acc2[j] = 0ull;
-        // this thread's entries of the scale table: {c0, c0} for its first half, {c1, c1} for its second
-        // (stage 2: both halves lie in one weight block, 0 or 1)
-        const uint32_t scl0 = smem_u32(&ctrl->scl[0][row_in_tile]) + (STAGE == 2 ? uint32_t((wg * NACC) >> 7) * 8u : 0u);
-        // One K block = NACC / kChunk column chunks through two register buffers, two tcgen05.ld in
-        // flight at a time: the thread waits once per pair of chunks, not once per chunk.
-        constexpr int kChunk = FLYMOE_EPI_CHUNK;       // columns per tcgen05.ld (16 or 8)
-        constexpr int kChunks = NACC / kChunk;
-        uint32_t v0[kChunk], v1[kChunk];
-        auto chunk_addr = [&](int i) -> uint32_t {     // TMEM address of chunk i of this thread's 64 columns
-          return (i < kChunks / 2 ? tcol0 + uint32_t(i * kChunk) : tcol1 + uint32_t((i - kChunks / 2) * kChunk));
-        };
-#pragma unroll 1
-        for (int kb = 0; kb < KB; ++kb) {
-          const uint32_t stage_off = uint32_t(acc) * BN;
-          PROF_START
-          if (!mbar_wait(full_bar0 + uint32_t(acc) * 8u, acc_phase, abort_flag, a.status, 4)) { ok = false; break; }
-          PROF_STOP(0) PROF_COUNT(5)
-          tcgen05_fence_after();
-          if (work) {                            // the first two chunks on their way at once
-            tmem_ld<kChunk>(chunk_addr(0) + stage_off, v0);
-            tmem_ld<kChunk>(chunk_addr(1) + stage_off, v1);
-          }
-          // the scale producer runs a K block ahead: this wait normally passes at its first probe
-          if (!mbar_wait(scl_bar0 + uint32_t(acc) * 8u, acc_phase, abort_flag, a.status, 9)) { ok = false; break; }
-          const uint32_t scl_addr = scl0 + uint32_t(acc) * uint32_t(sizeof(float4) * BM);
-          unsigned long long c;
-          asm volatile("ld.shared::cta.b64 %0, [%1];" : "=l"(c) : "r"(scl_addr) : "memory");
-          if (work) tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < kChunks; i += 2) {
-            // each buffer is refilled with a later chunk as soon as it has been folded in
-            if (work) {
-#pragma unroll
-              for (int j = 0; j < kChunk / 2; ++j) ffma2(acc2[i * kChunk / 2 + j], v0[2 * j], v0[2 * j + 1], c);
-              if (i + 2 < kChunks) tmem_ld<kChunk>(chunk_addr(i + 2) + stage_off, v0);
-#pragma unroll
-              for (int j = 0; j < kChunk / 2; ++j) ffma2(acc2[(i + 1) * kChunk / 2 + j], v1[2 * j], v1[2 * j + 1], c);
-              if (i + 3 < kChunks) tmem_ld<kChunk>(chunk_addr(i + 3) + stage_off, v1);
-            }
-            if (STAGE == 1 && i + 2 == kChunks / 2)     // the second half (up columns) has its own scale
-              asm volatile("ld.shared::cta.b64 %0, [%1+8];" : "=l"(c) : "r"(scl_addr) : "memory");
-            if (i + 2 < kChunks && work) tmem_ld_wait();
-            if (i + 4 == kChunks) {
-              // The K block's partial sums and scales are in registers now (tcgen05.wait::ld has
-              // returned, so the loads have completed and need no further ordering): hand the TMEM
-              // stage -- and with it the scale-table slot -- back before the last two chunks' FMAs.
-              // tcgen05.wait::ld is warp-wide (.sync.aligned), so when lane 0 is past it every lane's
-              // loads have landed; the arrive orders this warp's reads of the slot before the
-              // producer's next write (release).
-              __syncwarp();
-              if (lane == 0) mbar_arrive(empty_bar0 + uint32_t(acc) * 8u);
-            }
-          }
-          acc_phase ^= uint32_t(acc);
-          acc ^= 1;
+      for (int j = 0; j < NACC / 2; ++j) acc2[j] = 0ull;
+
+      float sa_next = valid ? __ldg(sa_ptr) : 0.f;
+      float s0_next = __ldg(sw0_ptr);
+      float s1_next = STAGE == 1 ? __ldg(sw0_ptr + sw1_off) : 0.f;
+      const float* sa_run = sa_ptr;            // running pointer: one add per K block, no multiply
+      // One K block = four 32-column chunks through two register buffers, two tcgen05.ld in flight at
+      // a time: the thread waits twice per K block, not once per chunk.
+      uint32_t v0[32], v1[32];
+      // measured: two K blocks per loop trip help stage 1 (~1.5 %) and cost stage 2 about as much
+#pragma unroll (STAGE == 1 ? 2 : 1)
+      for (int kb = 0; kb < KB; ++kb) {
+        const uint32_t stage_off = uint32_t(acc) * BN;
+        PROF_START
+        if (!mbar_wait(full_bar0 + uint32_t(acc) * 8u, acc_phase, abort_flag, a.status, 4)) { ok = false; break; }
+        PROF_STOP(0) PROF_COUNT(5)
+        tcgen05_fence_after();
+        if (work) {                            // both chunks of the first half on their way at once
+          tmem_ld_x32(tcol0 + stage_off, v0);
+          tmem_ld_x32(tcol0 + stage_off + 32, v1);
         }
-        if (!ok) break;
+        const unsigned long long c0 = pack_f32x2(sa_next * s0_next);
+        const unsigned long long c1 = STAGE == 1 ? pack_f32x2(sa_next * s1_next) : c0;
+        if (work) tmem_ld_wait();
+        if (kb + 1 < KB) {                     // next K block's scales: in flight during this block's math
+          sa_run += a.sa_stride;
+          sa_next = valid ? __ldg(sa_run) : 0.f;
+          s0_next = __ldg(sw0_ptr + kb + 1);
+          if (STAGE == 1) s1_next = __ldg(sw0_ptr + kb + 1 + sw1_off);
+        }
+        if (work) {
+          // each buffer is refilled with its chunk of the second half as soon as it has been folded in
 #pragma unroll
-        for (int j = 0; j < NACC / 2; ++j) unpack_f32x2(acc2[j], accv[2 * j], accv[2 * j + 1]);
+          for (int j = 0; j < 16; ++j) ffma2(acc2[j], v0[2 * j], v0[2 * j + 1], c0);
+          tmem_ld_x32(tcol1 + stage_off, v0);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) ffma2(acc2[16 + j], v1[2 * j], v1[2 * j + 1], c0);
+          tmem_ld_x32(tcol1 + stage_off + 32, v1);
+          tmem_ld_wait();
+        }
+        // The K block's partial sums are in registers now (tcgen05.wait::ld has returned, so the loads
+        // have completed and need no further ordering): hand the TMEM stage back before the last
+        // chunk's FMAs.  The arrive publishes no memory, hence relaxed; tcgen05.wait::ld is warp-wide
+        // (.sync.aligned), so when lane 0 is past it every lane's loads have landed.
+        if (!work) __syncwarp();
+        if (lane == 0) mbar_arrive_relaxed(empty_bar0 + uint32_t(acc) * 8u);
+        if (work) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) ffma2(acc2[32 + j], v0[2 * j], v0[2 * j + 1], c1);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) ffma2(acc2[48 + j], v1[2 * j], v1[2 * j + 1], c1);
+        }
+        acc_phase ^= uint32_t(acc);
+        acc ^= 1;
+      }
+      if (!ok) break;
+#pragma unroll
+      for (int j = 0; j < NACC / 2; ++j) unpack_f32x2(acc2[j], accv[2 * j], accv[2 * j + 1]);
       } else {
         // One scale per activation row, one per weight row: the whole K range has been accumulated in
         // TMEM; drain the tile once and scale it here.
@@ -739,11 +622,10 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         // the raw accumulators land in the registers of accv and are scaled in place
         uint32_t* v = reinterpret_cast<uint32_t*>(accv);
         if (work) {
-#pragma unroll
-          for (int j = 0; j < NHALF; j += 16) {
-            tmem_ld_x16(tcol0 + stage_off + j, v + j);
-            tmem_ld_x16(tcol1 + stage_off + j, v + NHALF + j);
-          }
+          tmem_ld_x32(tcol0 + stage_off, v);
+          tmem_ld_x32(tcol0 + stage_off + 32, v + 32);
+          tmem_ld_x32(tcol1 + stage_off, v + 64);
+          tmem_ld_x32(tcol1 + stage_off + 32, v + 96);
           tmem_ld_wait();
         } else {
           __syncwarp();
@@ -754,23 +636,24 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         if (work) {
           const float sa = valid ? __ldg(a.scale_a + sidx) : 0.f;
           const long long wrows = STAGE == 1 ? 2LL * a.n_dim : (long long)a.n_dim;
-          // weight-row scales of this thread's two 32-column halves (the same addresses in every lane)
-          const float* sw0 = a.scale_w + (long long)e * wrows + (STAGE == 1 ? n * 128 + wg * NHALF : n * BN + wg * NACC);
-          const float* sw1 = STAGE == 1 ? sw0 + a.n_dim : sw0 + NHALF;
+          // weight-row scales of this thread's two 64-column halves (the same addresses in every lane)
+          const float* sw0 = a.scale_w + (long long)e * wrows + (STAGE == 1 ? n * 128 + wg * 64 : n * BN + wg * 128);
+          const float* sw1 = STAGE == 1 ? sw0 + a.n_dim : sw0 + 64;
           const bool i8 = a.in_dtype == FLYMOE_I8;
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             const float* sw = h == 0 ? sw0 : sw1;
 #pragma unroll
-            for (int j = 0; j < NHALF; j += 4) {
+            for (int j = 0; j < 64; j += 4) {
               const float4 s4 = __ldg(reinterpret_cast<const float4*>(sw + j));
               const float c[4] = {s4.x, s4.y, s4.z, s4.w};
 #pragma unroll
               for (int u = 0; u < 4; ++u) {
-                const int idx = h * NHALF + j + u;
+                const int idx = h * 64 + j + u;
                 const float p = i8 ? __int2float_rn(int(v[idx])) : accv[idx];
                 accv[idx] = p * (sa * c[u]);
               }
+              asm volatile("" ::: "memory");       // keeps the 32 scale loads from being hoisted in front of the math
             }
           }
         } else {
@@ -781,25 +664,26 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       // Destination of this row when the caller gave per-row addresses: requested after the K loop (the
       // loop runs at the register limit) and needed only once the row has been packed.
       unsigned long long row_dst_base = 0ull;
-      if (STAGE == 2 && ROW_DST && valid && wg == 0)
+      if (STAGE == 2 && ROW_DST && valid)
         row_dst_base = __ldg(a.row_dst + ((long long)tok * a.topk + slot));
+      if (STAGE == 1 && a.doweight && valid) wgt = __ldg(a.sorted_weights + r);
 
       // ---- tile epilogue -----------------------------------------------------------
       // Kept short on purpose: this code runs once per tile between two main loops, and a long
       // straight-line tail (IEEE division, accurate exp) costs more in instruction fetch than in math.
       PROF_START
       if (STAGE == 1) {
-        // accv[0, NHALF) = gate, accv[NHALF, NACC) = up, columns n*128 + wg*NHALF + j
+        // accv[0..63] = gate, accv[64..127] = up, columns n*128 + wg*64 + j
         float amax = 0.f;
 #pragma unroll
-        for (int j = 0; j < NHALF; ++j) {
+        for (int j = 0; j < 64; ++j) {
           const float g = accv[j];
-          const float hval = g * fast_rcp(1.0f + fast_exp2(-1.4426950408889634f * g)) * (accv[NHALF + j] * wgt);
+          const float hval = g * fast_rcp(1.0f + fast_exp2(-1.4426950408889634f * g)) * (accv[64 + j] * wgt);
           accv[j] = hval;
           amax = fmaxf(amax, fabsf(hval));
         }
         const long long orow = a.out_layout == FLYMOE_ROWS_SORTED ? (long long)r : (long long)tok * a.topk + slot;
-        const long long ocol = (long long)n * 128 + wg * NHALF;
+        const long long ocol = (long long)n * 128 + wg * 64;
         if (a.out_dtype == FLYMOE_E4M3) {
           const int buf = tile_iter & 1;
           const uint32_t bar = smem_u32(&ctrl->amax_bar[buf]);
@@ -807,21 +691,19 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           __syncwarp();
           if (lane == 0) mbar_arrive(bar);
           if (!mbar_wait(bar, (tile_iter >> 1) & 1, abort_flag, a.status, 5)) { ok = false; break; }
-          // the store warp has finished reading the previous tile's staging rows
+          // the store warp has finished reading the previous tile's slots
           if (!mbar_wait(smem_u32(&ctrl->stg_free), (tile_iter & 1) ^ 1, abort_flag, a.status, 7)) { ok = false; break; }
           unsigned long long dst_addr = 0ull;
           const bool wr = warp_active && (valid || (in_tile && a.out_layout == FLYMOE_ROWS_SORTED));
           if (wr) {
-            float m = fmaxf(ctrl->amax[buf][0][row_in_tile], ctrl->amax[buf][1][row_in_tile]);
-#pragma unroll
-            for (int g = 2; g < kEpilogueGroups; ++g) m = fmaxf(m, ctrl->amax[buf][g][row_in_tile]);
+            const float m = fmaxf(ctrl->amax[buf][0][row_in_tile], ctrl->amax[buf][1][row_in_tile]);
             float sc = __fdiv_rn(m, 448.0f);
             if (sc == 0.f) sc = 1.f;
             const float inv = valid ? __fdiv_rn(1.0f, sc) : 0.f;     // pad rows: every code becomes 0
-            // this thread's NHALF codes of the row's 128; the row leaves as one 128-byte bulk store
-            uint8_t* op = staging + size_t(row_in_tile) * Staging<STAGE>::stride + wg * NHALF;
+            // 64 codes go through this thread's staging slot and leave as one 64-byte bulk store
+            uint8_t* op = staging + size_t(threadIdx.x - 128) * Staging<STAGE>::stride;
 #pragma unroll
-            for (int j = 0; j < NHALF; j += 16) {
+            for (int j = 0; j < 64; j += 16) {
               uint4 pk;
               pk.x = float4_to_e4m3x4(accv[j + 0] * inv, accv[j + 1] * inv, accv[j + 2] * inv, accv[j + 3] * inv);
               pk.y = float4_to_e4m3x4(accv[j + 4] * inv, accv[j + 5] * inv, accv[j + 6] * inv, accv[j + 7] * inv);
@@ -831,20 +713,17 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
               *reinterpret_cast<uint4*>(op + j) = pk;
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            if (wg == 0) {
-              dst_addr = reinterpret_cast<unsigned long long>(static_cast<uint8_t*>(a.out) + orow * a.n_dim +
-                                                              (long long)n * 128);
-              a.out_scale[(long long)n * a.out_scale_stride + orow] = sc;
-            }
+            dst_addr = reinterpret_cast<unsigned long long>(static_cast<uint8_t*>(a.out) + orow * a.n_dim + ocol);
+            if (wg == 0) a.out_scale[(long long)n * a.out_scale_stride + orow] = sc;
           }
-          if (wg == 0) ctrl->stg_dst[row_in_tile] = dst_addr;
+          ctrl->stg_dst[threadIdx.x - 128] = dst_addr;
           __syncwarp();
           if (lane == 0) mbar_arrive(smem_u32(&ctrl->stg_full));
         } else if (warp_active && valid) {
           uint8_t* op = static_cast<uint8_t*>(a.out) + (orow * a.n_dim + ocol) * 2;
           const bool bf = a.out_dtype == FLYMOE_BF16;
 #pragma unroll
-          for (int j = 0; j < NHALF; j += 8) {
+          for (int j = 0; j < 64; j += 8) {
             uint4 pk;
             pk.x = bf ? pack_bf16x2(accv[j + 0], accv[j + 1]) : pack_f16x2(accv[j + 0], accv[j + 1]);
             pk.y = bf ? pack_bf16x2(accv[j + 2], accv[j + 3]) : pack_f16x2(accv[j + 2], accv[j + 3]);
@@ -856,22 +735,22 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       } else if (a.out_dtype == FLYMOE_F32) {
         if (warp_active && valid && half_ok) {
           // fp32 output: vector reductions straight from registers (accumulate mode only)
-          float* op = static_cast<float*>(a.out) + (long long)tok * a.n_dim + (long long)n * BN + wg * NACC;
+          float* op = static_cast<float*>(a.out) + (long long)tok * a.n_dim + (long long)n * BN + wg * 128;
 #pragma unroll
-          for (int j = 0; j < NACC; j += 4)
+          for (int j = 0; j < 128; j += 4)
             red_add_v4_f32(op + j, accv[j] * wgt, accv[j + 1] * wgt, accv[j + 2] * wgt, accv[j + 3] * wgt);
         }
       } else {
-        // 16-bit output: each thread parks its NACC results in its row of the staging tile; the
-        // thread of warpgroup 0 adds the global address of the row segment, and the store warp sends
-        // every row off as ONE bulk reduce-add (or bulk store) of up to 512 bytes.
-        uint8_t* slot_ptr = staging + size_t(row_in_tile) * Staging<STAGE>::stride + wg * NACC * 2;
+        // 16-bit output: each thread parks its 128 results (256 B) in its own slot of the staging area
+        // together with the global address of its row segment; the store warp sends every slot off as
+        // ONE bulk reduce-add (or bulk store), instead of 16 scattered 16-byte atomics per thread.
+        uint8_t* slot_ptr = staging + size_t(threadIdx.x - 128) * Staging<STAGE>::stride;
         if (!mbar_wait(smem_u32(&ctrl->stg_free), (tile_iter & 1) ^ 1, abort_flag, a.status, 7)) { ok = false; break; }
         unsigned long long dst_addr = 0ull;
         if (warp_active && valid && half_ok) {
           const bool bf = a.out_dtype == FLYMOE_BF16;
 #pragma unroll
-          for (int j = 0; j < NACC; j += 8) {
+          for (int j = 0; j < 128; j += 8) {
             uint4 pk;
             pk.x = bf ? pack_bf16x2(accv[j] * wgt, accv[j + 1] * wgt) : pack_f16x2(accv[j] * wgt, accv[j + 1] * wgt);
             pk.y = bf ? pack_bf16x2(accv[j + 2] * wgt, accv[j + 3] * wgt) : pack_f16x2(accv[j + 2] * wgt, accv[j + 3] * wgt);
@@ -880,24 +759,20 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             *reinterpret_cast<uint4*>(slot_ptr + j * 2) = pk;
           }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          if (wg == 0) {
-            const long long orow = a.accumulate ? (long long)tok : (long long)tok * a.topk + slot;
-            const long long col_bytes = (long long)n * BN * 2;
-            if (ROW_DST) {
-              // rows leave for caller-given addresses (another GPU's buffer included): the bulk store
-              // carries the row segment there while the next tile is in the tensor cores.  A
-              // misaligned address would fault the bulk store: drop the row and report instead.
-              if ((row_dst_base & 15ull) != 0ull) {
-                atomicCAS(a.status, 0, 17);
-              } else if (row_dst_base != 0ull) {
-                dst_addr = row_dst_base + (unsigned long long)col_bytes;
-              }
-            } else {
-              dst_addr = reinterpret_cast<unsigned long long>(static_cast<uint8_t*>(a.out) + orow * a.n_dim * 2 + col_bytes);
-            }
+          const long long orow = a.accumulate ? (long long)tok : (long long)tok * a.topk + slot;
+          const long long col_bytes = ((long long)n * BN + wg * 128) * 2;
+          if (ROW_DST) {
+            // rows leave for caller-given addresses (another GPU's buffer included): the bulk store
+            // carries the row segment there while the next tile is in the tensor cores
+            // a misaligned address would fault the bulk store: drop the row and report instead
+            const unsigned long long base = row_dst_base;
+            if ((base & 15ull) != 0ull) atomicCAS(a.status, 0, FLYMOE_STATUS_ROW_DST_MISALIGNED);
+            else dst_addr = base != 0ull ? base + (unsigned long long)col_bytes : 0ull;
+          } else {
+            dst_addr = reinterpret_cast<unsigned long long>(static_cast<uint8_t*>(a.out) + orow * a.n_dim * 2 + col_bytes);
           }
         }
-        if (wg == 0) ctrl->stg_dst[row_in_tile] = dst_addr;
+        ctrl->stg_dst[threadIdx.x - 128] = dst_addr;
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&ctrl->stg_full));
       }
@@ -926,7 +801,7 @@ __global__ void bounded_wait_selftest_kernel(int* status, unsigned long long lim
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  if (threadIdx.x == 0) mbar_wait(smem_u32(&bar), 0, smem_u32(&abort_flag), status, code, 64, limit_ns);
+  if (threadIdx.x == 0) mbar_wait(smem_u32(&bar), 0, &abort_flag, status, code, 64, limit_ns);
 }
 
 }  // namespace flymoe
