@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
 
-One "step" = one pass of the whole path (gating -> sort -> gather -> stage 1 -> stage 2)
+One "step" = one pass of the whole path (gating -> sort -> [gather] -> stage 1 -> stage 2)
 over one batch of seeded synthetic tokens.  N=1 runs the DeepSeek-V3-shaped prefill
 layer (T=4096, H=7168, I=2048, E=256, top-8; workload ``c4a``); N>1 runs the
 expert-parallel configuration (T=16384 tokens per GPU, experts sharded over the ranks,
@@ -216,10 +216,12 @@ def wait_accounting(args, cfg) -> None:
     st = torch.cuda.current_stream().cuda_stream
     for _ in range(3):
         _lib.check(lib.flymoe_moe_gemm1(
-            layer.a2q.data_ptr(), layer.a2_scale.data_ptr(), layer.cap_rows, layer.xs.data_ptr(), xs_t.data_ptr(), T, 1,
+            layer.a2q.data_ptr(), layer.a2_scale.data_ptr(), layer.cap_rows,
+            xq.data_ptr() if layer.gather_in_kernel else layer.xs.data_ptr(), xs_t.data_ptr(), T, 1,
             w1q.data_ptr(), w1s.data_ptr(), layer.sorted_ids.data_ptr(), layer.sorted_expert_ids.data_ptr(),
             layer.sorted_weights.data_ptr(), layer.num_valid_ids.data_ptr(), T, I, H, blocks, E, k, U, 0, _lib.E4M3,
-            _lib.ROWS_SORTED, _lib.ROWS_BY_TOKEN, _lib.ROWS_SORTED, 0, st), "moe_gemm1")
+            _lib.ROWS_BY_TOKEN if layer.gather_in_kernel else _lib.ROWS_SORTED, _lib.ROWS_BY_TOKEN, _lib.ROWS_SORTED,
+            0, st), "moe_gemm1")
     torch.cuda.synchronize()
     show("stage 1")
 
@@ -276,7 +278,8 @@ def run_single_gpu(args, cfg, with_e2e: bool = True, with_cpu: bool = True, with
     rows = int(layer.num_valid_ids[0])
     # algorithmic bytes of one stage-1 launch: W1 of the active experts with their block scales, the
     # activations with their 1x128 scales once per token, the e4m3 intermediate with its scales once per
-    # (token, slot) pair.  What the design moves on top of that (gathered and padded rows) is reported apart.
+    # (token, slot) pair.  What the design moves on top of that (every sorted row's activations fetched by index,
+    # mostly from L2, and the padded rows of the intermediate) is reported apart.
     s1_bytes = (e_act * 2.0 * I * H * (1 + 4.0 / (128 * 128)) + T * H * (1 + 4.0 / 128)
                 + T * k * I * (1 + 4.0 / 128))
     s1_moved = (e_act * 2.0 * I * H * (1 + 4.0 / (128 * 128)) + rows * H + T * (H // 128) * 4.0

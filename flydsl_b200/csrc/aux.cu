@@ -53,10 +53,15 @@ dispatch_rows_kernel(const uint4* __restrict__ x, const float* __restrict__ x_sc
     const int t = id_token(id), s = id_slot(id);
     if (t >= num_tokens || s >= topk || e < 0 || e >= experts) continue;
     if (pos_base != nullptr && __ldg(pos_base + e) + r >= pos_limit) {   // would fall outside the receiver's buffer
-      if (lane == 0) atomicCAS(status, 0, 16);
+      if (lane == 0) atomicCAS(status, 0, FLYMOE_STATUS_DISPATCH_OVERFLOW);
       continue;
     }
-    uint4* dx = reinterpret_cast<uint4*>(__ldg(dst_x + e) + (long long)r * row_vec * 16);
+    const long long dst_base = __ldg(dst_x + e);
+    if ((dst_base & 15) != 0) {                // the 16-byte stores below would fault: drop the row and report
+      if (lane == 0) atomicCAS(status, 0, FLYMOE_STATUS_ROW_DST_MISALIGNED);
+      continue;
+    }
+    uint4* dx = reinterpret_cast<uint4*>(dst_base + (long long)r * row_vec * 16);
     const uint4* p = x + size_t(t) * row_vec;
     for (int i = lane; i < row_vec; i += 32) dx[i] = __ldg(p + i);
     float* ds = reinterpret_cast<float*>(__ldg(dst_scale + e) + (long long)r * kblocks * 4);

@@ -11,6 +11,11 @@
 //   warp 2      store warp: sends the finished rows that the epilogue threads parked in
 //               shared-memory slots to global memory as bulk stores / bulk reductions
 //               (one per slot), so their issue cost is off the epilogue's path.
+//   warp 3      row gather (only when the activations are not in sorted-row order): copies the
+//               tile's A rows, picked through the sorted-id list, into the ring with cp.async
+//               (16 bytes per request, the 128-byte swizzle applied by hand), two K blocks in
+//               flight; the TMA producer then fetches the weights only.  Meant for row blocks
+//               of 16 or 32 rows; larger ones are gathered ahead of the launch.
 //   warps 4-11  epilogue, two warpgroups.  Each thread owns one sorted row (its TMEM lane)
 //               and 128 of the tile's 256 accumulator columns.
 //
@@ -92,6 +97,7 @@ struct __align__(16) SmemCtrl {
 template <int STAGE> constexpr size_t smem_bytes() {
   return size_t(RingDepth<STAGE>::value) * kStageBytes + Staging<STAGE>::bytes + sizeof(SmemCtrl) + 1024;
 }
+static_assert(smem_bytes<1>() <= 232448 && smem_bytes<2>() <= 232448, "shared memory budget of one SM exceeded");
 
 // Optional whole-kernel wait accounting (build with -DFLYMOE_PROF, `python -m flydsl_b200.build
 // --prof`): every CTA's producer thread, MMA thread and first epilogue thread add up the cycles they
@@ -294,7 +300,8 @@ struct TileSched {
 
 // ROW_DST (stage 2 only): every output row goes to a caller-given address instead of out[t*k+s].  A
 // separate instantiation, so that the common kernel's register allocation is not touched.
-template <int STAGE, bool ROW_DST, int SCALING>
+// GATHER: a separate instantiation, so that the kernels reading sorted rows keep their register allocation.
+template <int STAGE, bool ROW_DST, int SCALING, bool GATHER>
 __global__ void __launch_bounds__(kNumThreads, 1)
 moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const GemmArgs a, const int group_m) {
@@ -310,6 +317,8 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   const int KB = a.k_dim / BK;
 
   const int valid_rows = min(__ldg(a.num_valid_ids), a.size_expert_ids * a.tile_m);
+  // A rows are fetched by index (row = token, or token*topk+slot) instead of by one TMA box per K block
+  constexpr bool gather = GATHER;
   // Outputs that leave through the staging slots (everything except 16-bit stage-1 and fp32 stage-2 output)
   const bool uses_staging = STAGE == 1 ? a.out_dtype == FLYMOE_E4M3 : a.out_dtype != FLYMOE_F32;
   TileSched sched;
@@ -320,7 +329,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) {
-      mbar_init(smem_u32(&ctrl->full[i]), 1);
+      mbar_init(smem_u32(&ctrl->full[i]), gather ? 2 : 1);     // TMA thread (+ the gather warp)
       mbar_init(smem_u32(&ctrl->empty[i]), 1);
     }
     for (int i = 0; i < kAccStages; ++i) {
@@ -354,7 +363,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       // ---------------------------------------------------------------- TMA producer
       int stage = 0;
       uint32_t phase = 0;
-      const uint32_t tx_bytes = uint32_t(a.tile_m) * BK + kBTileBytes;
+      const uint32_t tx_bytes = (gather ? 0u : uint32_t(a.tile_m) * BK) + kBTileBytes;
       bool ok = true;
       PROF_DECL
       int mb_next = 0, n_next = 0, e_next = -1;
@@ -377,7 +386,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           const uint32_t sa = smem_u32(smem + size_t(stage) * kStageBytes);
           const uint32_t sb = sa + kATileBytes;
           mbar_expect_tx(full, tx_bytes);
-          tma_load_2d(sa, &tmap_a, full, kb * BK, mb * a.tile_m);
+          if (!gather) tma_load_2d(sa, &tmap_a, full, kb * BK, mb * a.tile_m);
           if (STAGE == 1) {
             tma_load_3d(sb, &tmap_b, full, kb * BK, n * 128, e);
             tma_load_3d(sb + 128 * BK, &tmap_b, full, kb * BK, a.n_dim + n * 128, e);
@@ -487,6 +496,71 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         ++it;
       }
       bulk_wait_all();                             // every row segment has landed before the CTA retires
+    } else if (warp == 3 && gather) {
+      // ---------------------------------------------------------------- row gather
+      // Lane l serves rows l, l+32, l+64, l+96 of the tile: eight 16-byte cp.async per row and K block,
+      // written where the 128-byte swizzle puts them (chunk c of row r at r*128 + ((c ^ (r & 7)) << 4)).
+      // A K block's copies are completed two K blocks later (cp.async.wait_group), made visible to the
+      // tensor cores' proxy (fence.proxy.async) and then signalled on the stage's full barrier, next to
+      // the TMA thread's arrival for the weights.  Pad rows are zero-filled (source size 0).
+      // One warp issues every request, which keeps up with row blocks of 16 or 32 rows (decode); for
+      // 64 and 128 rows it is slower than gathering ahead of the launch (measured: stage 1 of the
+      // T=4096 layer 2.5 ms against 1.9 + 0.08 ms), so the host wrappers gather ahead for those.
+      constexpr int kInFlight = 2;
+      int stage = 0, pending = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      const int pad_id = (a.topk << 24) | a.num_tokens;
+      auto complete_oldest = [&]() {             // the oldest pending K block's rows have landed
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        const int s_old = (stage - pending + 2 * kStages) % kStages;
+        if (lane == 0) mbar_arrive(smem_u32(&ctrl->full[s_old]));
+        --pending;
+      };
+      for (int t = blockIdx.x; t < sched.total && ok; t += gridDim.x) {
+        int mb, n;
+        sched.decode(t, mb, n);
+        const int e = __ldg(a.sorted_expert_ids + mb);
+        if (e < 0 || e >= a.experts) continue;
+        const uint8_t* src[4];
+        uint32_t nbytes[4];                      // 16 = copy, 0 = zero-fill (pad row)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int row = j * 32 + lane;
+          const int r = mb * a.tile_m + row;
+          const int id = (row < a.tile_m && r < valid_rows) ? __ldg(a.sorted_ids + r) : pad_id;
+          const int tok = id_token(id), slot = id_slot(id);
+          const bool valid = tok < a.num_tokens && slot < a.topk;
+          const long long srow = a.a_layout == FLYMOE_ROWS_BY_TOKEN ? (long long)tok : (long long)tok * a.topk + slot;
+          src[j] = a.a + (valid ? srow : 0) * a.k_dim;
+          nbytes[j] = valid ? 16u : 0u;
+        }
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, a.status, 10, 32)) { ok = false; break; }
+          const uint32_t sa = smem_u32(smem + size_t(stage) * kStageBytes);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int row = j * 32 + lane;
+            if (row < a.tile_m) {
+              const uint8_t* g = src[j] + kb * BK;
+              const uint32_t d = sa + uint32_t(row) * 128u;
+#pragma unroll
+              for (int c = 0; c < 8; ++c)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                             ::"r"(d + (uint32_t(c ^ (row & 7)) << 4)), "l"(g + c * 16), "r"(nbytes[j]) : "memory");
+            }
+          }
+          asm volatile("cp.async.commit_group;" ::: "memory");
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+          if (++pending > kInFlight) {
+            asm volatile("cp.async.wait_group %0;" ::"n"(kInFlight) : "memory");
+            complete_oldest();
+          }
+        }
+      }
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      while (pending > 0) complete_oldest();
     }
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
@@ -869,10 +943,10 @@ static int make_map(CUtensorMap* map, const void* base, int rank, const cuuint64
   return FLYMOE_OK;
 }
 
-template <int STAGE, bool ROW_DST, int SCALING>
-static int launch_one(int grid, cudaStream_t stream, const CUtensorMap& map_a, const CUtensorMap& map_b,
-                      const GemmArgs& a, int group_m) {
-  auto* kernel = moe_gemm_sm100_kernel<STAGE, ROW_DST, SCALING>;
+template <int STAGE, bool ROW_DST, int SCALING, bool GATHER>
+static int launch_kernel(int grid, cudaStream_t stream, const CUtensorMap& map_a, const CUtensorMap& map_b,
+                         const GemmArgs& a, int group_m) {
+  auto* kernel = moe_gemm_sm100_kernel<STAGE, ROW_DST, SCALING, GATHER>;
   FLYMOE_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          int(smem_bytes<STAGE>())));
   kernel<<<grid, kNumThreads, smem_bytes<STAGE>(), stream>>>(map_a, map_b, a, group_m);
@@ -880,13 +954,21 @@ static int launch_one(int grid, cudaStream_t stream, const CUtensorMap& map_a, c
   return FLYMOE_OK;
 }
 
+template <int STAGE, bool ROW_DST, int SCALING>
+static int launch_one(int grid, cudaStream_t stream, const CUtensorMap& map_a, const CUtensorMap& map_b,
+                      const GemmArgs& a, int group_m) {
+  if (a.a_layout != FLYMOE_ROWS_SORTED)
+    return launch_kernel<STAGE, ROW_DST, SCALING, true>(grid, stream, map_a, map_b, a, group_m);
+  return launch_kernel<STAGE, ROW_DST, SCALING, false>(grid, stream, map_a, map_b, a, group_m);
+}
+
 int launch_gemm_sm100(int stage, const GemmArgs& a, cudaStream_t stream) {
   if (a.tile_m != 16 && a.tile_m != 32 && a.tile_m != 64 && a.tile_m != 128) {
     set_last_error_msg("tcgen05 GEMM: tile_m must be 16, 32, 64 or 128");
     return FLYMOE_ERR_UNSUPPORTED;
   }
-  if (a.a_layout != FLYMOE_ROWS_SORTED) {
-    set_last_error_msg("tcgen05 GEMM: activations must be in sorted-row order (use flymoe_gather_rows)");
+  if (a.a_layout != FLYMOE_ROWS_SORTED && a.a_layout != FLYMOE_ROWS_BY_TOKEN && a.a_layout != FLYMOE_ROWS_BY_PAIR) {
+    set_last_error_msg("tcgen05 GEMM: unknown activation row layout");
     return FLYMOE_ERR_UNSUPPORTED;
   }
   const bool per_token = a.scaling == FLYMOE_SCALE_PER_TOKEN;

@@ -47,6 +47,9 @@ _BYTE_DTYPES = _FP8_DTYPES + (torch.int8,)     # anything the one-byte weight re
 _OUT16 = {"f16": torch.float16, "bf16": torch.bfloat16}
 _IMPL = {"tcgen05": _lib.IMPL_TCGEN05, "simt": _lib.IMPL_SIMT}
 _TILE_M = (16, 32, 64, 128)
+# Row blocks of up to this many rows have their rows fetched by index inside the GEMM kernel (one warp
+# keeps up with them); larger ones are gathered into sorted order ahead of the launch, which is faster.
+_GATHER_IN_KERNEL_MAX = 32
 
 
 # ------------------------------------------------------------------------- weight layout
@@ -134,7 +137,8 @@ class _LauncherScratch:
     first call on that stream (or ahead of time with ``reserve``) and replaced only by a larger one;
     replaced buffers stay referenced, because kernels already enqueued on a stream torch does not
     track may still read them.  Callers that must not allocate on the call path (graph capture,
-    a fixed memory budget) pass their own buffer to the launcher instead."""
+    a fixed memory budget) pass their own buffer to the launcher instead.  Launchers built for row
+    blocks of 16 or 32 rows need no gather buffer at all."""
 
     def __init__(self, dtype):
         self.dtype = dtype
@@ -243,7 +247,7 @@ def compile_moe_blockscale_gemm1(*, model_dim: int, inter_dim: int, experts: int
         w_plain = _plain_weight(arg_w, wrows, model_dim, w_layout, h)
         x_layout = _lib.ROWS_SORTED if sorted_rows else _lib.ROWS_BY_TOKEN
         x_ptr = _lib.ptr(arg_x)
-        if impl_code == _lib.IMPL_TCGEN05 and not sorted_rows:
+        if impl_code == _lib.IMPL_TCGEN05 and not sorted_rows and tile_m > _GATHER_IN_KERNEL_MAX:
             gbuf = _resolve_scratch(scratch, gather_buffer, "gather_buffer", arg_x.device, h, cap_rows * model_dim)
             _lib.check(lib.flymoe_gather_rows(x_ptr, _lib.ptr(gbuf), _lib.ptr(arg_sorted_token_ids),
                                               _lib.ptr(arg_max_token_ids), tokens, topk, model_dim,
@@ -322,7 +326,7 @@ def compile_moe_blockscale_gemm2(*, model_dim: int, inter_dim: int, experts: int
         w_plain = _plain_weight(arg_w, wrows, inter_dim, w_layout, h)
         a_layout = _lib.ROWS_SORTED if sorted_rows else _lib.ROWS_BY_PAIR
         a_ptr = _lib.ptr(arg_x)
-        if impl_code == _lib.IMPL_TCGEN05 and not sorted_rows:
+        if impl_code == _lib.IMPL_TCGEN05 and not sorted_rows and tile_m > _GATHER_IN_KERNEL_MAX:
             gbuf = _resolve_scratch(scratch, gather_buffer, "gather_buffer", arg_x.device, h, cap_rows * inter_dim)
             _lib.check(lib.flymoe_gather_rows(a_ptr, _lib.ptr(gbuf), _lib.ptr(arg_sorted_token_ids),
                                               _lib.ptr(arg_num_valid_ids), tokens, topk, inter_dim,

@@ -33,7 +33,7 @@ import functools
 import torch
 
 from .. import _lib
-from .moe_blockscale_2stage import (MoeGemm2Mode, _IMPL, _LauncherScratch, _MoeGemm2ReduceWrapper, _OUT16,
+from .moe_blockscale_2stage import (MoeGemm2Mode, _GATHER_IN_KERNEL_MAX, _IMPL, _LauncherScratch, _MoeGemm2ReduceWrapper, _OUT16,
                                     _plain_weight, _resolve_scratch, compile_moe_reduction, logger)
 
 _VALID_IN = ("fp8", "fp16", "bf16", "int8", "int8smooth", "int4", "int4_bf16")
@@ -111,7 +111,7 @@ def compile_moe_gemm1(*, model_dim: int, inter_dim: int, experts: int, topk: int
         w_plain = _plain_weight(arg_w, wrows, model_dim, w_layout, h)
         row_layout = _lib.ROWS_BY_PAIR if by_pair else _lib.ROWS_BY_TOKEN
         x_ptr, x_layout = _lib.ptr(arg_x), row_layout
-        if impl_code == _lib.IMPL_TCGEN05:
+        if impl_code == _lib.IMPL_TCGEN05 and tile_m > _GATHER_IN_KERNEL_MAX:
             gbuf = _resolve_scratch(scratch, gather_buffer, "gather_buffer", arg_x.device, h, cap_rows * model_dim)
             _lib.check(lib.flymoe_gather_rows(x_ptr, _lib.ptr(gbuf), _lib.ptr(arg_sorted_token_ids),
                                               _lib.ptr(arg_max_token_ids), tokens, topk, model_dim, row_layout,
@@ -175,7 +175,7 @@ def compile_moe_gemm2(*, model_dim: int, inter_dim: int, experts: int, topk: int
         lib = _lib.load()
         w_plain = _plain_weight(arg_w, wrows, inter_dim, w_layout, h)
         a_ptr, a_layout = _lib.ptr(arg_x), _lib.ROWS_BY_PAIR
-        if impl_code == _lib.IMPL_TCGEN05:
+        if impl_code == _lib.IMPL_TCGEN05 and tile_m > _GATHER_IN_KERNEL_MAX:
             gbuf = _resolve_scratch(scratch, gather_buffer, "gather_buffer", arg_x.device, h, cap_rows * inter_dim)
             _lib.check(lib.flymoe_gather_rows(a_ptr, _lib.ptr(gbuf), _lib.ptr(arg_sorted_token_ids),
                                               _lib.ptr(arg_num_valid_ids), tokens, topk, inter_dim,

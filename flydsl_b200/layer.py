@@ -67,7 +67,10 @@ class FusedMoEBlockscale:
         self.num_valid_ids = torch.zeros(2, dtype=i32, device=dev)
         ws = int(self.lib.flymoe_moe_sorting_workspace_elems(T, E, k, U))
         self.workspace = torch.empty(max(ws, 1), dtype=i32, device=dev)
-        self.xs = torch.empty((self.cap_rows, H), dtype=torch.uint8, device=dev)
+        # Row blocks of 16 or 32 rows: stage 1 fetches each sorted row's activations by token id inside
+        # the kernel.  Larger blocks: a gather kernel copies them into sorted order first (faster there).
+        self.gather_in_kernel = self.tile_m <= 32
+        self.xs = None if self.gather_in_kernel else torch.empty((self.cap_rows, H), dtype=torch.uint8, device=dev)
         self.a2q = torch.empty((self.cap_rows, I), dtype=torch.uint8, device=dev)
         self.a2_scale = torch.empty((I // 128, self.cap_rows), dtype=f32, device=dev)
         self.out = torch.empty((T, H), dtype=out_dtype, device=dev)
@@ -97,7 +100,7 @@ class FusedMoEBlockscale:
     def experts_forward(self, topk_ids, topk_weights, xq, x_scale_t, tokens: int, stream: int,
                         out: torch.Tensor | None = None, x_scale_row_major: bool = False,
                         row_dst: torch.Tensor | None = None) -> torch.Tensor:
-        """sort -> gather -> stage 1 -> stage 2 for already-routed tokens.
+        """sort -> (gather, for row blocks of 64 or 128 rows) -> stage 1 -> stage 2 for already-routed tokens.
 
         topk_ids i32 [tokens, k] (ids in [0, E) of this layer's experts; ids outside
         that range are ignored), topk_weights f32 [tokens, k], xq e4m3 [tokens, H],
@@ -125,16 +128,19 @@ class FusedMoEBlockscale:
             out.data_ptr() if self.stage2_mode == "atomic" else None,
             T * H * out.element_size() if self.stage2_mode == "atomic" else 0, None, self.workspace.data_ptr(),
             self.workspace.numel(), T, E, k, U, stream), "moe_sorting")
-        _lib.check(lib.flymoe_gather_rows(
-            xq.data_ptr(), self.xs.data_ptr(), self.sorted_ids.data_ptr(), self.num_valid_ids.data_ptr(),
-            T, k, H, _lib.ROWS_BY_TOKEN, cap_rows, stream), "gather_rows")
+        if not self.gather_in_kernel:
+            _lib.check(lib.flymoe_gather_rows(
+                xq.data_ptr(), self.xs.data_ptr(), self.sorted_ids.data_ptr(), self.num_valid_ids.data_ptr(),
+                T, k, H, _lib.ROWS_BY_TOKEN, cap_rows, stream), "gather_rows")
         sx_stride, sx_row_stride = (1, H // 128) if x_scale_row_major else (x_scale_t.numel() // (H // 128), 1)
         t0 = self._mark()
         _lib.check(lib.flymoe_moe_gemm1(
-            self.a2q.data_ptr(), self.a2_scale.data_ptr(), self.cap_rows, self.xs.data_ptr(),
+            self.a2q.data_ptr(), self.a2_scale.data_ptr(), self.cap_rows,
+            xq.data_ptr() if self.gather_in_kernel else self.xs.data_ptr(),
             x_scale_t.data_ptr(), sx_stride, sx_row_stride, self.w1q.data_ptr(), self.w1_scale.data_ptr(),
             self.sorted_ids.data_ptr(), self.sorted_expert_ids.data_ptr(), self.sorted_weights.data_ptr(),
-            self.num_valid_ids.data_ptr(), T, I, H, blocks, E, k, U, 0, _lib.E4M3, _lib.ROWS_SORTED,
+            self.num_valid_ids.data_ptr(), T, I, H, blocks, E, k, U, 0, _lib.E4M3,
+            _lib.ROWS_BY_TOKEN if self.gather_in_kernel else _lib.ROWS_SORTED,
             _lib.ROWS_BY_TOKEN, _lib.ROWS_SORTED, self.impl, stream), "moe_gemm1")
         t1 = self._mark()
         accumulate = self.stage2_mode == "atomic"
@@ -219,7 +225,7 @@ class FusedMoEBlockscale:
     def kernel_launches(self, tokens: int) -> int:
         """Kernels this layer enqueues per forward (memset of the output not counted)."""
         sort = 1 if tokens * self.topk <= 8192 else 3
-        return 1 + sort + 1 + 1 + 1 + (1 if self.stage2_mode == "reduce" else 0)
+        return 1 + sort + (0 if self.gather_in_kernel else 1) + 1 + 1 + (1 if self.stage2_mode == "reduce" else 0)
 
     def experts_kernel_launches(self, rows: int) -> int:
         """Kernels experts_forward enqueues for ``rows`` input rows."""

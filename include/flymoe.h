@@ -116,16 +116,20 @@ int flymoe_moe_sorting_noalloc(const int32_t* topk_ids, const float* topk_weight
 /* Copies rows of a one-byte-element matrix into sorted order: dst row r = src row
  * selected by sorted_ids[r] under src_layout (BY_TOKEN or BY_PAIR); pad rows are
  * zero-filled; rows at or beyond num_valid_ids[0] are left untouched.
- * Replaces the in-kernel gather of kernels/moe_blockscale_2stage.py:401-427 and
- * :1576-1590 (the tensor-core kernels here read contiguous sorted rows by TMA). */
+ * A stand-alone version of the in-kernel gather of kernels/moe_blockscale_2stage.py:401-427 and
+ * :1576-1590.  The GEMM stages below can do that gather themselves (x_layout / a_layout BY_TOKEN or
+ * BY_PAIR), which is the better choice for row blocks of 16 or 32 rows; for 64 and 128 rows gathering
+ * with this entry point first and passing the SORTED layout is faster. */
 int flymoe_gather_rows(const void* src, void* dst, const int32_t* sorted_ids,
                        const int32_t* num_valid_ids, int num_tokens, int topk, int row_bytes,
                        int src_layout, int max_rows, void* stream);
 
 /* Stage 1: gate/up grouped FP8 GEMM over sorted rows + SiLU(gate)*up.
  * Replaces kernels/moe_blockscale_2stage.py:70-84 (builder) and the launcher
- * :1142-1157.  x e4m3: [T,H] when x_layout==BY_TOKEN and impl==SIMT, else the
- * gathered [rows,H] matrix in sorted order (flymoe_gather_rows).  scale_x f32, element
+ * :1142-1157.  x e4m3: [T,H] when x_layout==BY_TOKEN (each sorted row's activations are
+ * fetched by token id inside the kernel, as the reference does, :401-427; meant for tile_m 16 or 32),
+ * or the [rows,H] matrix already in sorted order (x_layout==SORTED, one TMA box per K block; see
+ * flymoe_gather_rows).  scale_x f32, element
  * (kb, row) at kb*sx_stride + row*sx_row_stride: the reference's transposed layout
  * [H/128, rows] is (sx_stride = rows, sx_row_stride = 1), row-major [rows, H/128] is
  * (1, H/128); row = token (x_scale_layout BY_TOKEN) or sorted row.
@@ -145,7 +149,8 @@ int flymoe_moe_gemm1(void* out, float* out_scale, int64_t out_scale_stride, cons
 
 /* Stage 2: down-projection grouped FP8 GEMM + top-k-weighted scatter-reduce.
  * Replaces kernels/moe_blockscale_2stage.py:1189-1207 (builder) and the launcher
- * :2335-2350.  a2 e4m3 [rows,I] under a_layout (BY_PAIR for SIMT, else sorted rows);
+ * :2335-2350.  a2 e4m3 [rows,I] under a_layout (BY_PAIR: row t*topk+s, fetched by index inside the
+ * kernel as the reference does, :1576-1590; or SORTED);
  * scale_a f32 [I/128, sa_stride] indexed under a_scale_layout (BY_PAIR or SORTED).
  * w e4m3 [E,H,I], scale_w f32 [E,H/128,I/128].  accumulate!=0: out [T,H] of
  * out_dtype (F16/BF16/F32), pre-zeroed, receives atomic adds; accumulate==0: out
@@ -163,8 +168,8 @@ int flymoe_moe_gemm2(void* out, const void* a2, const float* scale_a, int64_t sa
  * Replace kernels/moe_gemm_2stage.py:90-108 (compile_moe_gemm1, launcher :1730-1745) and
  * :1780-1796 (compile_moe_gemm2, launcher :3151-3166) for in_dtype "fp8", "int8" and
  * "int8smooth".  in_dtype E4M3 or I8 (signed 8-bit operands, exact int32 accumulation).
- * Stage 1: x [T,H] (x_layout BY_TOKEN, SIMT only), [T*k,H] (BY_PAIR: "int8smooth", SIMT only) or
- * the gathered sorted rows (SORTED); scale_x f32 [T] (x_scale_layout BY_TOKEN), [T*k] (BY_PAIR)
+ * Stage 1: x [T,H] (x_layout BY_TOKEN), [T*k,H] (BY_PAIR: "int8smooth") or rows already in sorted
+ * order (SORTED); scale_x f32 [T] (x_scale_layout BY_TOKEN), [T*k] (BY_PAIR)
  * or per sorted row; w [E,2I,H] row-major, scale_w f32 [E*2I]; out F16/BF16 [T*k,I]
  * (out_layout BY_PAIR) or sorted rows.  Stage 2: a2 [T*k,I] / sorted rows, scale_a f32 [T*k] /
  * per sorted row, w [E,H,I], scale_w f32 [E*H]; out as flymoe_moe_gemm2.  The K range is
@@ -211,7 +216,8 @@ int flymoe_moe_gemm2_scatter_rows(const uint64_t* row_dst, const void* a2, const
  * dst_scale[e] + r*(model_dim/128)*4, e being the row's expert.  The two tables hold one
  * byte address per expert, usually in the memory of the GPU that owns the expert (mapped
  * into this process, peer access enabled), chosen so that a row lands at its final position
- * of the receiver's block-padded sorted layout; dst_x addresses must be 16-byte aligned.
+ * of the receiver's block-padded sorted layout; dst_x addresses must be 16-byte aligned (rows of an
+ * expert whose address is not are dropped and the status word reads FLYMOE_STATUS_ROW_DST_MISALIGNED).
  * Rows with ids outside [0, T) x [0, topk) or experts outside [0, experts) are skipped.
  * Optional bound for callers that size nothing on the host: with pos_base != NULL, row r
  * of expert e is dropped -- and the device status word set to 16

@@ -149,3 +149,34 @@ def test_stage2_no_atomic_and_reduce(cfg, tile_m, impl):
         s_e, s_w, nv, T, H, cfg.inter_dim, nblk)
     torch.cuda.synchronize()
     assert_close(out, orc.stage2(a2q, a2s, p.w2q, p.w2s, p.ids, p.tw, H), RTOL, ATOL, "stage2 reduce mode")
+
+
+@pytest.mark.parametrize("cfg,tile_m", [(SMALL, 128), (SMALL, 64), (MINI, 16), (wl.CONFIGS["c1"], 32)])
+def test_in_kernel_row_gather_through_the_c_abi(cfg, tile_m):
+    """x_layout BY_TOKEN / a_layout BY_PAIR on the tensor-core path: the kernel fetches every sorted row by
+    index itself (the launchers choose this only for 16- and 32-row blocks; any block size must be right)."""
+    from flydsl_b200 import _lib
+    lib = _lib.load()
+    p = problem(cfg)
+    T, k, H, I, E = cfg.tokens, cfg.topk, cfg.model_dim, cfg.inter_dim, cfg.experts
+    s_ids, s_w, s_e, nv, nblk = p.sort(tile_m)
+    st = torch.cuda.current_stream().cuda_stream
+    out1 = torch.full((T * k + 8, I), 77.0, dtype=torch.bfloat16, device="cuda")
+    _lib.check(lib.flymoe_moe_gemm1(
+        out1.data_ptr(), None, 0, p.d_xq.data_ptr(), p.d_xs_t.data_ptr(), T, 1, p.d_w1q.data_ptr(), p.d_w1s.data_ptr(),
+        s_ids.data_ptr(), s_e.data_ptr(), s_w.data_ptr(), nv.data_ptr(), T, I, H, nblk, E, k, tile_m, 0, _lib.BF16,
+        _lib.ROWS_BY_TOKEN, _lib.ROWS_BY_TOKEN, _lib.ROWS_BY_PAIR, _lib.IMPL_TCGEN05, st), "gemm1")
+    torch.cuda.synchronize()
+    ref1 = orc.stage1(p.xq, p.xs, p.w1q, p.w1s, p.ids, I)
+    assert bool((out1[T * k:] == 77.0).all())
+    assert_close(out1[: T * k].view(T, k, I), ref1, RTOL, ATOL, f"stage 1, rows gathered in the kernel, {cfg.name}")
+    a2q, a2s = orc.requant(ref1)
+    out2 = torch.zeros((T, H), dtype=torch.float32, device="cuda")
+    a2s_t = a2s.t().contiguous().cuda()
+    _lib.check(lib.flymoe_moe_gemm2(
+        out2.data_ptr(), a2q.cuda().data_ptr(), a2s_t.data_ptr(), T * k, p.d_w2q.data_ptr(), p.d_w2s.data_ptr(),
+        s_ids.data_ptr(), s_e.data_ptr(), s_w.data_ptr(), nv.data_ptr(), T, H, I, nblk, E, k, tile_m, 1, _lib.F32, 1,
+        _lib.ROWS_BY_PAIR, _lib.ROWS_BY_PAIR, _lib.IMPL_TCGEN05, st), "gemm2")
+    torch.cuda.synchronize()
+    ref2 = orc.stage2(a2q, a2s, p.w2q, p.w2s, p.ids, p.tw, H)
+    assert_close(out2, ref2, 1e-4, 1e-5 * float(ref2.abs().max()), f"stage 2, rows gathered in the kernel, {cfg.name}")

@@ -64,3 +64,28 @@ def test_misaligned_row_destination_is_dropped_and_reported():
     assert torch.equal(got[keep], plain.cpu()[keep])
     assert bool((target[5] == -7.0).all()), "the misaligned row was dropped, nothing was written"
     assert bool((target[T] == -7.0).all())
+
+
+def test_dispatch_rows_drops_rows_of_a_misaligned_destination():
+    """flymoe_dispatch_rows with one expert's destination address off by 4 bytes: that expert's rows are
+    not stored (the 16-byte stores would fault), the others are, and the status word reports it once."""
+    lib = _lib.load()
+    T, k, H, E = 8, 1, 256, 2
+    dev = "cuda"
+    x = torch.arange(T * H, dtype=torch.int32).remainder(251).to(torch.uint8).view(T, H).to(dev)
+    xs = torch.arange(T * (H // 128), dtype=torch.float32).view(T, H // 128).to(dev)
+    s_ids = torch.arange(T, dtype=torch.int32, device=dev)                 # slot 0 of token r
+    s_e = torch.tensor([0, 0, 0, 0, 1, 1, 1, 1], dtype=torch.int32, device=dev)
+    nv = torch.tensor([T, T], dtype=torch.int32, device=dev)
+    out_x = torch.full((T + 1, H), 0xEE, dtype=torch.uint8, device=dev)
+    out_s = torch.full((T + 1, H // 128), -1.0, dtype=torch.float32, device=dev)
+    dst_x = torch.tensor([out_x.data_ptr(), out_x.data_ptr() + 4], dtype=torch.int64, device=dev)   # expert 1: misaligned
+    dst_s = torch.tensor([out_s.data_ptr(), out_s.data_ptr()], dtype=torch.int64, device=dev)
+    _lib.check(lib.flymoe_dispatch_rows(x.data_ptr(), xs.data_ptr(), s_ids.data_ptr(), s_e.data_ptr(), nv.data_ptr(),
+                                        dst_x.data_ptr(), dst_s.data_ptr(), None, 0, T, k, H, E, T,
+                                        torch.cuda.current_stream().cuda_stream), "dispatch_rows")
+    torch.cuda.synchronize()
+    assert _lib.device_status() == _lib.STATUS_ROW_DST_MISALIGNED
+    assert _lib.device_status() == 0
+    assert torch.equal(out_x[:4].cpu(), x[:4].cpu()) and torch.equal(out_s[:4].cpu(), xs[:4].cpu())
+    assert bool((out_x[4:] == 0xEE).all()) and bool((out_s[4:] == -1.0).all())
