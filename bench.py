@@ -439,16 +439,27 @@ def run_pertoken(args, cfg) -> dict:
     lib = _lib.load()
     T, k, H, I, E, U = cfg.tokens, cfg.topk, cfg.model_dim, cfg.inter_dim, cfg.experts, args.tile_m
     g = torch.Generator(device=dev).manual_seed(cfg.seed)
-    w1q = torch.empty((E, 2 * I, H), dtype=torch.float8_e4m3fn, device=dev)
-    w2q = torch.empty((E, H, I), dtype=torch.float8_e4m3fn, device=dev)
+    half = args.in_dtype == "bf16"          # 16-bit operands: no scales at all, twice the operand bytes
+    wdt = torch.bfloat16 if half else torch.float8_e4m3fn
+    in_code, ebytes = (_lib.BF16, 2) if half else (_lib.E4M3, 1)
+    w1q = torch.empty((E, 2 * I, H), dtype=wdt, device=dev)
+    w2q = torch.empty((E, H, I), dtype=wdt, device=dev)
     sw1 = torch.empty((E, 2 * I), dtype=torch.float32, device=dev)
     sw2 = torch.empty((E, H), dtype=torch.float32, device=dev)
     for e in range(E):
+        if half:
+            w1q[e] = (torch.randn((2 * I, H), generator=g, device=dev) * 0.02).to(wdt)
+            w2q[e] = (torch.randn((H, I), generator=g, device=dev) * 0.02).to(wdt)
+            continue
         q, sc = wl.quant_groups(torch.randn((2 * I, H), generator=g, device=dev) * 0.02)
         w1q[e], sw1[e] = q, sc.view(-1)
         q, sc = wl.quant_groups(torch.randn((H, I), generator=g, device=dev) * 0.02)
         w2q[e], sw2[e] = q, sc.view(-1)
-    xq, sx = wl.quant_groups(torch.randn((T, H), generator=g, device=dev))
+    if half:
+        xq, sx = torch.randn((T, H), generator=g, device=dev).to(wdt), None
+    else:
+        xq, sx = wl.quant_groups(torch.randn((T, H), generator=g, device=dev))
+    scale_ptr = (lambda t: None) if half else (lambda t: t.data_ptr())
     logits = wl.make_logits(cfg).to(dev)
     i32, f32 = torch.int32, torch.float32
     tw, ids, tei = (torch.empty((T, k), dtype=dt, device=dev) for dt in (f32, i32, i32))
@@ -463,25 +474,28 @@ def run_pertoken(args, cfg) -> dict:
                                               T, E, k, 1, st), "gating")
     _lib.check(lib.flymoe_moe_sorting(ids.data_ptr(), tw.data_ptr(), s_ids.data_ptr(), s_w.data_ptr(), s_e.data_ptr(),
                                       nv.data_ptr(), None, 0, None, ws.data_ptr(), ws.numel(), T, E, k, U, st), "sorting")
-    xs = torch.empty((rows, H), dtype=torch.uint8, device=dev)
-    _lib.check(lib.flymoe_gather_rows(xq.data_ptr(), xs.data_ptr(), s_ids.data_ptr(), nv.data_ptr(), T, k, H,
+    xs = torch.empty((rows, H * ebytes), dtype=torch.uint8, device=dev)
+    _lib.check(lib.flymoe_gather_rows(xq.data_ptr(), xs.data_ptr(), s_ids.data_ptr(), nv.data_ptr(), T, k, H * ebytes,
                                       _lib.ROWS_BY_TOKEN, rows, st), "gather")
     out1 = torch.zeros((rows, I), dtype=torch.bfloat16, device=dev)
     out2 = torch.zeros((T, H), dtype=torch.bfloat16, device=dev)
 
     def stage1():
         _lib.check(lib.flymoe_moe_gemm1_pertoken(
-            out1.data_ptr(), xs.data_ptr(), sx.data_ptr(), w1q.data_ptr(), sw1.data_ptr(), s_ids.data_ptr(),
-            s_e.data_ptr(), s_w.data_ptr(), nv.data_ptr(), T, I, H, blocks, E, k, U, 0, _lib.E4M3, _lib.BF16,
+            out1.data_ptr(), xs.data_ptr(), scale_ptr(sx), w1q.data_ptr(), scale_ptr(sw1), s_ids.data_ptr(),
+            s_e.data_ptr(), s_w.data_ptr(), nv.data_ptr(), T, I, H, blocks, E, k, U, 0, in_code, _lib.BF16,
             _lib.ROWS_SORTED, _lib.ROWS_BY_TOKEN, _lib.ROWS_SORTED, _lib.IMPL_TCGEN05, st), "gemm1_pertoken")
     stage1()
-    a2q, sa2 = wl.quant_groups(out1.float())
-    sa2 = sa2.view(-1).contiguous()
+    if half:
+        a2q, sa2 = out1, None
+    else:
+        a2q, sa2 = wl.quant_groups(out1.float())
+        sa2 = sa2.view(-1).contiguous()
 
     def stage2():
         _lib.check(lib.flymoe_moe_gemm2_pertoken(
-            out2.data_ptr(), a2q.data_ptr(), sa2.data_ptr(), w2q.data_ptr(), sw2.data_ptr(), s_ids.data_ptr(),
-            s_e.data_ptr(), s_w.data_ptr(), nv.data_ptr(), T, H, I, blocks, E, k, U, 1, _lib.E4M3, _lib.BF16, 1,
+            out2.data_ptr(), a2q.data_ptr(), scale_ptr(sa2), w2q.data_ptr(), scale_ptr(sw2), s_ids.data_ptr(),
+            s_e.data_ptr(), s_w.data_ptr(), nv.data_ptr(), T, H, I, blocks, E, k, U, 1, in_code, _lib.BF16, 1,
             _lib.ROWS_SORTED, _lib.ROWS_SORTED, _lib.IMPL_TCGEN05, st), "gemm2_pertoken")
     stream = torch.cuda.current_stream()
     for _ in range(args.warmup):
@@ -504,9 +518,24 @@ def run_pertoken(args, cfg) -> dict:
     s1 = statistics.mean(evs[2 * i].elapsed_time(evs[2 * i + 1]) for i in range(args.steps))
     s2 = statistics.mean(evs[2 * i + 1].elapsed_time(evs[2 * i + 2]) for i in range(args.steps))
     f1, f2 = 4.0 * T * k * I * H, 2.0 * T * k * H * I
-    fp8_peak = 2.0 * peaks["bf16_tflops"]
+    fp8_peak = (1.0 if half else 2.0) * peaks["bf16_tflops"]      # dense tensor peak of the operand type
     e_act = int(torch.unique(ids).numel())
-    wbytes1, wbytes2 = e_act * 2.0 * I * H, e_act * 1.0 * I * H
+    wbytes1, wbytes2 = e_act * 2.0 * I * H * ebytes, e_act * 1.0 * I * H * ebytes
+    if half:
+        return {"metric": "bf16_moe_gemm_tflops", "value": round((f1 + f2) / ((s1 + s2) * 1e-3) / 1e12, 2), "unit": UNIT,
+                "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(s1 + s2, 4),
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "bf16 (fp32 accumulate, no scales)", "data": "synthetic",
+                "config": {**wl.describe(cfg), "tile_m": U, "what": "stage 1 + stage 2 kernels of kernels.moe_gemm_2stage only"},
+                "stage1": {"ms": round(s1, 4), "tflops": round(f1 / (s1 * 1e-3) / 1e12, 1),
+                           "frac_of_bf16_peak": round(f1 / (s1 * 1e-3) / 1e12 / fp8_peak, 4)},
+                "stage2": {"ms": round(s2, 4), "tflops": round(f2 / (s2 * 1e-3) / 1e12, 1),
+                           "frac_of_bf16_peak": round(f2 / (s2 * 1e-3) / 1e12 / fp8_peak, 4)},
+                "roofline": {"bound": "tensor", "achieved": round((f1 + f2) / ((s1 + s2) * 1e-3) / 1e12, 1),
+                             "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                             "frac": round((f1 + f2) / ((s1 + s2) * 1e-3) / 1e12 / peaks["bf16_tflops"], 4), "traffic": None,
+                             "peak_source": peaks.get("source", "")},
+                "cpu_baseline": None, "e2e": None, "clocks": clocks, "gpu_launches": 2 * args.steps}
     return {"metric": "fp8_pertoken_moe_gemm_tflops", "value": round((f1 + f2) / ((s1 + s2) * 1e-3) / 1e12, 2), "unit": UNIT,
             "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(s1 + s2, 4),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -550,6 +579,8 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--scaling", default="block", choices=["block", "pertoken"],
                     help="'pertoken': time the per-token-scale GEMM stages (kernels.moe_gemm_2stage) on the workload's shapes")
+    ap.add_argument("--in-dtype", default="fp8", choices=["fp8", "bf16"],
+                    help="operand type of --scaling pertoken (bf16: 16-bit operands and weights, no scales)")
     ap.add_argument("--no-parity", action="store_true", help="skip the post-run check against the CPU oracle")
     ap.add_argument("--no-same-work", action="store_true",
                     help="multi-GPU: skip timing the same per-GPU work on one GPU (weak_scaling_eff)")

@@ -183,19 +183,21 @@ quant_act_1x128_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* 
 }
 
 // ---------------------------------------------------------------------------- shuffle
-// Preshuffle order of a [rows, cols] byte matrix: element (n, k) lives at
-// (((n/16) * (cols/32) + k/32) * 2 + (k%32)/16) * 256 + (n%16) * 16 + k%16.
+// Preshuffle order of a [rows, cols] matrix of 1- or 2-byte elements: 16 rows x 32 elements form a group,
+// stored as (32 * elem_bytes / 16) 16-byte chunks of 16 rows each, i.e. element (n, k) lives in 16-byte
+// vector (((n/16) * (cols/32) + k/32) * cpg + (k%32) / (16/elem_bytes)) * 16 + n%16, cpg = 2 * elem_bytes.
 // One thread moves 16 bytes.
 __global__ void __launch_bounds__(256)
-shuffle_weight_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long long rows, int cols,
-                      int to_plain) {
-  const long long nvec = rows * (cols / 16);
-  const int kv = cols / 16;  // 16-byte vectors per row
+shuffle_weight_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long long rows, int row_bytes,
+                      int cpg, int to_plain) {
+  const int kv = row_bytes / 16;  // 16-byte vectors per row
+  const long long nvec = rows * kv;
+  const int groups = kv / cpg;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
        i += (long long)gridDim.x * blockDim.x) {
     const long long n = i / kv;
     const int kc = int(i - n * kv);              // 16-byte chunk index along k
-    const long long shuf = (((n / 16) * (cols / 32) + kc / 2) * 2 + (kc & 1)) * 16 + (n % 16);
+    const long long shuf = (((n / 16) * groups + kc / cpg) * cpg + (kc % cpg)) * 16 + (n % 16);
     if (to_plain) dst[i] = __ldg(src + shuf);
     else dst[shuf] = __ldg(src + i);
   }
@@ -330,17 +332,24 @@ extern "C" int flymoe_quant_act_1x128(const void* x, int x_dtype, void* q, float
   return FLYMOE_OK;
 }
 
-extern "C" int flymoe_shuffle_weight(const void* src, void* dst, int64_t rows, int cols, int to_plain,
-                                     void* stream) {
+extern "C" int flymoe_shuffle_weight_elems(const void* src, void* dst, int64_t rows, int cols, int elem_bytes,
+                                           int to_plain, void* stream) {
   using namespace flymoe;
   FLYMOE_REQUIRE(src && dst && src != dst, "shuffle_weight: src and dst must be distinct non-null pointers");
+  FLYMOE_REQUIRE(elem_bytes == 1 || elem_bytes == 2, "shuffle_weight: elem_bytes must be 1 or 2");
   FLYMOE_REQUIRE(rows > 0 && rows % 16 == 0 && cols > 0 && cols % 32 == 0,
                  "shuffle_weight: rows must be a multiple of 16 and cols of 32");
   FLYMOE_REQUIRE(aligned16(src) && aligned16(dst), "shuffle_weight: pointers must be 16-byte aligned");
-  const long long nvec = rows * (cols / 16);
+  const int row_bytes = cols * elem_bytes;
+  const long long nvec = rows * (row_bytes / 16);
   const int blocks = int(std::min<long long>((nvec + 255) / 256, (long long)sm_count() * 32));
   shuffle_weight_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint4*>(src), static_cast<uint4*>(dst), rows, cols, to_plain);
+      static_cast<const uint4*>(src), static_cast<uint4*>(dst), rows, row_bytes, 2 * elem_bytes, to_plain);
   FLYMOE_CUDA_CHECK(cudaGetLastError());
   return FLYMOE_OK;
+}
+
+extern "C" int flymoe_shuffle_weight(const void* src, void* dst, int64_t rows, int cols, int to_plain,
+                                     void* stream) {
+  return flymoe_shuffle_weight_elems(src, dst, rows, cols, 1, to_plain, stream);
 }

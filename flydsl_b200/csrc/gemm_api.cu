@@ -8,6 +8,8 @@ static bool layout_ok(int l) {
   return l == FLYMOE_ROWS_BY_TOKEN || l == FLYMOE_ROWS_BY_PAIR || l == FLYMOE_ROWS_SORTED;
 }
 
+static bool is_half(int dtype) { return dtype == FLYMOE_F16 || dtype == FLYMOE_BF16; }
+
 static long long layout_rows(int layout, int num_tokens, int topk, int size_expert_ids, int tile_m) {
   if (layout == FLYMOE_ROWS_BY_TOKEN) return num_tokens;
   if (layout == FLYMOE_ROWS_BY_PAIR) return (long long)num_tokens * topk;
@@ -29,8 +31,9 @@ static int gemm1_impl(void* out, float* out_scale, int64_t out_scale_stride, con
   FLYMOE_REQUIRE(tile_m >= 1 && size_expert_ids >= 0, "gemm1: tile_m/size_expert_ids out of range");
   FLYMOE_REQUIRE(out_dtype == FLYMOE_F16 || out_dtype == FLYMOE_BF16 || (out_dtype == FLYMOE_E4M3 && !per_token),
                  "gemm1: out_dtype must be F16, BF16 or (block-scaled only) E4M3");
-  FLYMOE_REQUIRE(in_dtype == FLYMOE_E4M3 || (in_dtype == FLYMOE_I8 && per_token),
-                 "gemm1: in_dtype must be E4M3 or (per-token scaling only) I8");
+  FLYMOE_REQUIRE(in_dtype == FLYMOE_E4M3 || ((in_dtype == FLYMOE_I8 || is_half(in_dtype)) && per_token),
+                 "gemm1: in_dtype must be E4M3 or (per-token scaling only) I8, F16, BF16");
+  FLYMOE_REQUIRE(!is_half(in_dtype) || impl == FLYMOE_IMPL_TCGEN05, "gemm1: 16-bit operands need the tcgen05 kernel");
   FLYMOE_REQUIRE(layout_ok(x_layout) && (x_layout != FLYMOE_ROWS_BY_PAIR || per_token),
                  "gemm1: x_layout must be BY_TOKEN or SORTED (BY_PAIR with per-token scaling)");
   FLYMOE_REQUIRE(layout_ok(x_scale_layout) && (x_scale_layout != FLYMOE_ROWS_BY_PAIR || per_token),
@@ -38,8 +41,8 @@ static int gemm1_impl(void* out, float* out_scale, int64_t out_scale_stride, con
   FLYMOE_REQUIRE(out_layout == FLYMOE_ROWS_BY_PAIR || out_layout == FLYMOE_ROWS_SORTED,
                  "gemm1: out_layout must be BY_PAIR or SORTED");
   if (num_tokens == 0 || size_expert_ids == 0) return FLYMOE_OK;
-  FLYMOE_REQUIRE(out && x && scale_x && w && scale_w && sorted_ids && sorted_expert_ids && num_valid_ids,
-                 "gemm1: null pointer");
+  FLYMOE_REQUIRE(out && x && w && sorted_ids && sorted_expert_ids && num_valid_ids, "gemm1: null pointer");
+  FLYMOE_REQUIRE((scale_x && scale_w) || is_half(in_dtype), "gemm1: scales may be null only with 16-bit operands");
   FLYMOE_REQUIRE(!doweight || sorted_weights, "gemm1: doweight needs sorted_weights");
   FLYMOE_REQUIRE(out_dtype != FLYMOE_E4M3 || out_scale, "gemm1: e4m3 output needs out_scale");
   FLYMOE_REQUIRE(aligned16(out) && aligned16(x) && aligned16(w), "gemm1: out/x/w must be 16-byte aligned");
@@ -79,7 +82,7 @@ static int gemm1_impl(void* out, float* out_scale, int64_t out_scale_stride, con
   a.topk = topk;
   a.experts = experts;
   a.n_dim = inter_dim;
-  a.k_dim = model_dim;
+  a.k_dim = is_half(in_dtype) ? 2 * model_dim : model_dim;      // the kernels count K in bytes
   a.size_expert_ids = size_expert_ids;
   a.tile_m = tile_m;
   a.status = status;
@@ -131,14 +134,15 @@ static int gemm2_impl(void* out, const unsigned long long* row_dst, const void* 
   FLYMOE_REQUIRE(tile_m >= 1 && size_expert_ids >= 0, "gemm2: tile_m/size_expert_ids out of range");
   FLYMOE_REQUIRE(out_dtype == FLYMOE_F16 || out_dtype == FLYMOE_BF16 || (out_dtype == FLYMOE_F32 && accumulate),
                  "gemm2: out_dtype must be F16 or BF16 (F32 only with accumulate)");
-  FLYMOE_REQUIRE(in_dtype == FLYMOE_E4M3 || (in_dtype == FLYMOE_I8 && per_token),
-                 "gemm2: in_dtype must be E4M3 or (per-token scaling only) I8");
+  FLYMOE_REQUIRE(in_dtype == FLYMOE_E4M3 || ((in_dtype == FLYMOE_I8 || is_half(in_dtype)) && per_token),
+                 "gemm2: in_dtype must be E4M3 or (per-token scaling only) I8, F16, BF16");
+  FLYMOE_REQUIRE(!is_half(in_dtype) || impl == FLYMOE_IMPL_TCGEN05, "gemm2: 16-bit operands need the tcgen05 kernel");
   FLYMOE_REQUIRE((a_layout == FLYMOE_ROWS_BY_PAIR || a_layout == FLYMOE_ROWS_SORTED) &&
                      (a_scale_layout == FLYMOE_ROWS_BY_PAIR || a_scale_layout == FLYMOE_ROWS_SORTED),
                  "gemm2: a_layout/a_scale_layout must be BY_PAIR or SORTED");
   if (num_tokens == 0 || size_expert_ids == 0) return FLYMOE_OK;
-  FLYMOE_REQUIRE((out || row_dst) && a2 && scale_a && w && scale_w && sorted_ids && sorted_expert_ids && num_valid_ids,
-                 "gemm2: null pointer");
+  FLYMOE_REQUIRE((out || row_dst) && a2 && w && sorted_ids && sorted_expert_ids && num_valid_ids, "gemm2: null pointer");
+  FLYMOE_REQUIRE((scale_a && scale_w) || is_half(in_dtype), "gemm2: scales may be null only with 16-bit operands");
   FLYMOE_REQUIRE(!row_dst || (!accumulate && out_dtype != FLYMOE_F32 && impl == FLYMOE_IMPL_TCGEN05 && !per_token),
                  "gemm2: per-row destinations need accumulate == 0, a 16-bit out_dtype and the block-scaled tcgen05 kernel");
   FLYMOE_REQUIRE(!doweight || sorted_weights, "gemm2: doweight needs sorted_weights");
@@ -175,7 +179,7 @@ static int gemm2_impl(void* out, const unsigned long long* row_dst, const void* 
   a.topk = topk;
   a.experts = experts;
   a.n_dim = model_dim;
-  a.k_dim = inter_dim;
+  a.k_dim = is_half(in_dtype) ? 2 * inter_dim : inter_dim;
   a.size_expert_ids = size_expert_ids;
   a.tile_m = tile_m;
   a.status = status;

@@ -35,7 +35,7 @@ struct GemmArgs {
   // FLYMOE_SCALE_BLOCK128: scale_a [k_dim/128, rows] (strided as above), scale_w [experts, wrows/128, k_dim/128];
   // FLYMOE_SCALE_PER_TOKEN: scale_a [rows] (one per activation row), scale_w [experts, wrows] (one per weight row)
   int scaling;
-  int in_dtype;                // FLYMOE_E4M3, or FLYMOE_I8 (per-token scaling only)
+  int in_dtype;                // FLYMOE_E4M3, or (per-token scaling only) FLYMOE_I8 / F16 / BF16
   // sizes
   int num_tokens, topk, experts;
   int n_dim;                   // stage 1: inter_dim; stage 2: model_dim

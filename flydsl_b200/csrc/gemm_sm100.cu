@@ -211,6 +211,14 @@ __device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t adesc, uint64_
       "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                : "memory");
@@ -263,10 +271,14 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
   return d;
 }
 // Instruction descriptors, both operands K-major, M=128, N=256:
-// kind::f8f6f4 with A=B=e4m3 (format 0) and D=f32 (format 1); kind::i8 with A=B=s8 (format 1) and D=s32 (format 2).
+// kind::f8f6f4 with A=B=e4m3 (format 0) and D=f32 (format 1); kind::i8 with A=B=s8 (format 1) and D=s32 (format 2);
+// kind::f16 with A=B=f16 (format 0) or bf16 (format 1) and D=f32.  One instruction covers 32 bytes of K in
+// every kind (32 one-byte or 16 two-byte elements), so a 128-byte K block is four instructions in all of them.
 constexpr uint32_t kInstrDescShape = (uint32_t(BN >> 3) << 17) | (uint32_t(BM >> 4) << 24);
 constexpr uint32_t kInstrDescF8 = (1u << 4) | (0u << 7) | (0u << 10) | kInstrDescShape;
 constexpr uint32_t kInstrDescI8 = (2u << 4) | (1u << 7) | (1u << 10) | kInstrDescShape;
+constexpr uint32_t kInstrDescF16 = (1u << 4) | (0u << 7) | (0u << 10) | kInstrDescShape;
+constexpr uint32_t kInstrDescBF16 = (1u << 4) | (1u << 7) | (1u << 10) | kInstrDescShape;
 
 // Bulk operations from a staging slot to a contiguous global row segment (16-byte aligned, size % 16 == 0).
 __device__ __forceinline__ void bulk_reduce_add_bf16(void* g, uint32_t s, uint32_t bytes) {
@@ -404,6 +416,8 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       bool ok = true;
       PROF_DECL
       const bool int8_ops = SCALING == kScalePerToken && a.in_dtype == FLYMOE_I8;
+      const bool half_ops = SCALING == kScalePerToken && (a.in_dtype == FLYMOE_F16 || a.in_dtype == FLYMOE_BF16);
+      const uint32_t half_desc = a.in_dtype == FLYMOE_BF16 ? kInstrDescBF16 : kInstrDescF16;
       int mb_next = 0, n_next = 0, e_next = -1;
       if (int(blockIdx.x) < sched.total) {
         sched.decode(blockIdx.x, mb_next, n_next);
@@ -440,6 +454,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           for (int k = 0; k < BK / 32; ++k) {
             const uint32_t accumulate = (k > 0 || (SCALING == kScalePerToken && kb > 0)) ? 1u : 0u;
             if (int8_ops) umma_i8(d_tmem, adesc + uint64_t(k * 2), bdesc + uint64_t(k * 2), kInstrDescI8, accumulate);
+            else if (half_ops) umma_f16(d_tmem, adesc + uint64_t(k * 2), bdesc + uint64_t(k * 2), half_desc, accumulate);
             else umma_f8(d_tmem, adesc + uint64_t(k * 2), bdesc + uint64_t(k * 2), kInstrDescF8, accumulate);
           }
           umma_commit(smem_u32(&ctrl->empty[stage]));
@@ -708,7 +723,8 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         acc_phase ^= uint32_t(acc);
         acc ^= 1;
         if (work) {
-          const float sa = valid ? __ldg(a.scale_a + sidx) : 0.f;
+          // 16-bit operands come without scales (null pointers): every factor is 1
+          const float sa = valid ? (a.scale_a ? __ldg(a.scale_a + sidx) : 1.f) : 0.f;
           const long long wrows = STAGE == 1 ? 2LL * a.n_dim : (long long)a.n_dim;
           // weight-row scales of this thread's two 64-column halves (the same addresses in every lane)
           const float* sw0 = a.scale_w + (long long)e * wrows + (STAGE == 1 ? n * 128 + wg * 64 : n * BN + wg * 128);
@@ -719,7 +735,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             const float* sw = h == 0 ? sw0 : sw1;
 #pragma unroll
             for (int j = 0; j < 64; j += 4) {
-              const float4 s4 = __ldg(reinterpret_cast<const float4*>(sw + j));
+              const float4 s4 = a.scale_w ? __ldg(reinterpret_cast<const float4*>(sw + j)) : make_float4(1.f, 1.f, 1.f, 1.f);
               const float c[4] = {s4.x, s4.y, s4.z, s4.w};
 #pragma unroll
               for (int u = 0; u < 4; ++u) {

@@ -62,24 +62,26 @@ _GATHER_IN_KERNEL_MAX = 32
 _plain_cache: dict = {}
 
 
-def unshuffle_weight(w: torch.Tensor, rows: int, cols: int, stream=None) -> torch.Tensor:
-    """Return a row-major copy of a 16x16-preshuffled one-byte weight ([rows, cols] bytes)."""
-    _lib.require_cuda("w", w, _BYTE_DTYPES, rows * cols)
+_WEIGHT_DTYPES = _BYTE_DTYPES + (torch.float16, torch.bfloat16)
+
+
+def _reorder_weight(w: torch.Tensor, rows: int, cols: int, to_plain: int, stream) -> torch.Tensor:
+    _lib.require_cuda("w", w, _WEIGHT_DTYPES, rows * cols)
     out = torch.empty(rows * cols, dtype=w.dtype, device=w.device)
     _order_after_current_stream(stream, w.device)
-    _lib.check(_lib.load().flymoe_shuffle_weight(_lib.ptr(w), _lib.ptr(out), rows, cols, 1,
-                                                 _lib.stream_handle(stream)), "shuffle_weight")
+    _lib.check(_lib.load().flymoe_shuffle_weight_elems(_lib.ptr(w), _lib.ptr(out), rows, cols, w.element_size(),
+                                                       to_plain, _lib.stream_handle(stream)), "shuffle_weight")
     return out
+
+
+def unshuffle_weight(w: torch.Tensor, rows: int, cols: int, stream=None) -> torch.Tensor:
+    """Return a row-major copy of a 16x16-preshuffled weight ([rows, cols] one- or two-byte elements)."""
+    return _reorder_weight(w, rows, cols, 1, stream)
 
 
 def shuffle_weight(w: torch.Tensor, rows: int, cols: int, stream=None) -> torch.Tensor:
-    """Row-major one-byte weight -> the reference's 16x16 preshuffle order."""
-    _lib.require_cuda("w", w, _BYTE_DTYPES, rows * cols)
-    out = torch.empty(rows * cols, dtype=w.dtype, device=w.device)
-    _order_after_current_stream(stream, w.device)
-    _lib.check(_lib.load().flymoe_shuffle_weight(_lib.ptr(w), _lib.ptr(out), rows, cols, 0,
-                                                 _lib.stream_handle(stream)), "shuffle_weight")
-    return out
+    """Row-major weight (one- or two-byte elements) -> the reference's 16x16 preshuffle order."""
+    return _reorder_weight(w, rows, cols, 0, stream)
 
 
 def _order_after_current_stream(stream, device) -> None:
@@ -110,7 +112,7 @@ def _plain_weight(w: torch.Tensor, rows: int, cols: int, layout: str, stream) ->
     # An entry is only valid for the allocation it was made from: a freed weight's address is reused
     # by the allocator, so the storage object itself (weakly referenced) is part of the check.
     storage = w.untyped_storage()
-    key = (w.data_ptr(), w.numel(), w.device.index, rows, cols)
+    key = (w.data_ptr(), w.numel(), w.element_size(), w.device.index, rows, cols)
     hit = _plain_cache.get(key)
     if hit is not None and hit[0] == w._version and hit[2]() is storage:
         return hit[1]

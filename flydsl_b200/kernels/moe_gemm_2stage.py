@@ -1,6 +1,6 @@
 """Two-stage MoE GEMMs with per-token / per-channel scales for B200.
 
-Mirrors ``kernels/moe_gemm_2stage.py`` of the reference for its 8-bit variants:
+Mirrors ``kernels/moe_gemm_2stage.py`` of the reference for its 8-bit and 16-bit variants:
 
 * ``compile_moe_gemm1`` (:90-108) -> launcher with the positional order of :1730-1745
   ``(out, x, w, scale_x, scale_w, sorted_token_ids, expert_ids, sorted_weights,
@@ -16,12 +16,14 @@ slot) pair ([tokens*topk, K], [tokens*topk]).  Stage 1 writes ``silu(gate)*up`` 
 ``t*topk + s`` of a [tokens, topk, inter] f16/bf16 tensor; stage 2 reads that layout (e4m3/int8
 plus one scale per row) and accumulates ``sorted_weight * (a2 . W2^T)`` into ``out[t]``
 (pre-zeroed; f16/bf16/f32) or, with ``accumulate=False``, stores per-pair rows.
+``"fp16"`` / ``"bf16"``: x, the weights and the stage-2 input are 16-bit floats and there are no
+scales (the scale arguments are ignored; the reference passes empty tensors, :569-579 of its test).
 
 With one scale per row and column the whole K range is accumulated inside the tensor cores'
 accumulator memory and every tile is scaled once, ``(sum_k a*w) * scale_a[row] * scale_w[col]``.
 
-Not built here: the 16-bit (``fp16``/``bf16``), packed-int4 (``int4``, ``int4_bf16``), group-wise
-and split-K variants of the reference raise ``ValueError`` at build time.
+Not built here: the packed-int4 (``int4``, ``int4_bf16``), group-wise and split-K variants of the
+reference raise ``ValueError`` at build time.
 Additions (keyword-only): ``w_layout`` ("preshuffle16x16" default, or "plain") and ``impl``
 ("tcgen05" default, "simt" cross-check) as in ``moe_blockscale_2stage``.
 """
@@ -37,8 +39,10 @@ from .moe_blockscale_2stage import (MoeGemm2Mode, _GATHER_IN_KERNEL_MAX, _IMPL, 
                                     _plain_weight, _resolve_scratch, compile_moe_reduction, logger)
 
 _VALID_IN = ("fp8", "fp16", "bf16", "int8", "int8smooth", "int4", "int4_bf16")
-_BUILT_IN = ("fp8", "int8", "int8smooth")
-_IN_TORCH = {"fp8": (torch.float8_e4m3fn, torch.uint8), "int8": (torch.int8,), "int8smooth": (torch.int8,)}
+_BUILT_IN = ("fp8", "int8", "int8smooth", "fp16", "bf16")
+_IN_TORCH = {"fp8": (torch.float8_e4m3fn, torch.uint8), "int8": (torch.int8,), "int8smooth": (torch.int8,),
+             "fp16": (torch.float16,), "bf16": (torch.bfloat16,)}
+_IN_CODE = {"fp8": _lib.E4M3, "int8": _lib.I8, "int8smooth": _lib.I8, "fp16": _lib.F16, "bf16": _lib.BF16}
 _TILE_M = (16, 32, 64, 128)
 
 
@@ -46,7 +50,7 @@ def _check(in_dtype, group_size, k_batch, tile_m, tile_k, model_dim, inter_dim, 
     if in_dtype not in _VALID_IN:
         raise ValueError(f"in_dtype must be one of {_VALID_IN}, got {in_dtype!r}")
     if in_dtype not in _BUILT_IN:
-        raise ValueError(f"in_dtype={in_dtype!r} is not built on this implementation (8-bit operands only: {_BUILT_IN})")
+        raise ValueError(f"in_dtype={in_dtype!r} is not built on this implementation (built: {_BUILT_IN})")
     if group_size > 0:
         raise ValueError("group-wise weight scales belong to the packed-int4 variants, which are not built here")
     if k_batch != 1:
@@ -63,6 +67,8 @@ def _check(in_dtype, group_size, k_batch, tile_m, tile_k, model_dim, inter_dim, 
         raise ValueError(f"w_layout must be 'preshuffle16x16' or 'plain', got {w_layout!r}")
     if impl not in _IMPL:
         raise ValueError(f"impl must be one of {sorted(_IMPL)}, got {impl!r}")
+    if impl != "tcgen05" and in_dtype in ("fp16", "bf16"):
+        raise ValueError("16-bit operands are built for the tensor-core path only (impl='tcgen05')")
     if impl == "tcgen05" and tile_m not in _TILE_M:
         raise ValueError(f"tile_m must be one of {_TILE_M} for the tensor-core path, got {tile_m}")
 
@@ -79,8 +85,10 @@ def compile_moe_gemm1(*, model_dim: int, inter_dim: int, experts: int, topk: int
     if use_cshuffle_epilog is not None or scale_is_bf16:
         logger.debug("stage 1: use_cshuffle_epilog / scale_is_bf16 do not apply here and are ignored")
     impl_code = _IMPL[impl]
-    in_code = _lib.E4M3 if in_dtype == "fp8" else _lib.I8
+    in_code = _IN_CODE[in_dtype]
     in_torch = _IN_TORCH[in_dtype]
+    unscaled = in_dtype in ("fp16", "bf16")
+    ebytes = 2 if unscaled else 1
     out_torch = _OUT16[out_dtype]
     out_code = _lib.DTYPE_CODE[out_torch]
     by_pair = in_dtype == "int8smooth"          # x and scale_x indexed by t*topk + s
@@ -100,8 +108,11 @@ def compile_moe_gemm1(*, model_dim: int, inter_dim: int, experts: int, topk: int
         _lib.require_cuda("arg_out", arg_out, (out_torch,), pairs * inter_dim)
         _lib.require_cuda("arg_x", arg_x, in_torch, x_rows * model_dim)
         _lib.require_cuda("arg_w", arg_w, in_torch, wrows * model_dim)
-        _lib.require_cuda("arg_scale_x", arg_scale_x, (torch.float32,), x_rows)
-        _lib.require_cuda("arg_scale_w", arg_scale_w, (torch.float32,), wrows)
+        if not unscaled:
+            _lib.require_cuda("arg_scale_x", arg_scale_x, (torch.float32,), x_rows)
+            _lib.require_cuda("arg_scale_w", arg_scale_w, (torch.float32,), wrows)
+        sx_ptr = 0 if unscaled else _lib.ptr(arg_scale_x)
+        sw_ptr = 0 if unscaled else _lib.ptr(arg_scale_w)
         _lib.require_cuda("arg_sorted_token_ids", arg_sorted_token_ids, (torch.int32,), max(0, cap_rows - tile_m + 1))
         _lib.require_cuda("arg_expert_ids", arg_expert_ids, (torch.int32,), blocks)
         _lib.require_cuda("arg_sorted_weights", arg_sorted_weights, (torch.float32,), max(0, cap_rows - tile_m + 1))
@@ -112,13 +123,14 @@ def compile_moe_gemm1(*, model_dim: int, inter_dim: int, experts: int, topk: int
         row_layout = _lib.ROWS_BY_PAIR if by_pair else _lib.ROWS_BY_TOKEN
         x_ptr, x_layout = _lib.ptr(arg_x), row_layout
         if impl_code == _lib.IMPL_TCGEN05 and tile_m > _GATHER_IN_KERNEL_MAX:
-            gbuf = _resolve_scratch(scratch, gather_buffer, "gather_buffer", arg_x.device, h, cap_rows * model_dim)
+            gbuf = _resolve_scratch(scratch, gather_buffer, "gather_buffer", arg_x.device, h,
+                                    cap_rows * model_dim * ebytes)
             _lib.check(lib.flymoe_gather_rows(x_ptr, _lib.ptr(gbuf), _lib.ptr(arg_sorted_token_ids),
-                                              _lib.ptr(arg_max_token_ids), tokens, topk, model_dim, row_layout,
+                                              _lib.ptr(arg_max_token_ids), tokens, topk, model_dim * ebytes, row_layout,
                                               cap_rows, h), "gather_rows")
             x_ptr, x_layout = _lib.ptr(gbuf), _lib.ROWS_SORTED
         _lib.check(lib.flymoe_moe_gemm1_pertoken(
-            _lib.ptr(arg_out), x_ptr, _lib.ptr(arg_scale_x), _lib.ptr(w_plain), _lib.ptr(arg_scale_w),
+            _lib.ptr(arg_out), x_ptr, sx_ptr, _lib.ptr(w_plain), sw_ptr,
             _lib.ptr(arg_sorted_token_ids), _lib.ptr(arg_expert_ids), _lib.ptr(arg_sorted_weights),
             _lib.ptr(arg_max_token_ids), tokens, inter_dim, model_dim, blocks, experts, topk, tile_m,
             1 if doweight_stage1 else 0, in_code, out_code, x_layout, row_layout, _lib.ROWS_BY_PAIR, impl_code, h),
@@ -144,8 +156,10 @@ def compile_moe_gemm2(*, model_dim: int, inter_dim: int, experts: int, topk: int
     if use_cshuffle_epilog is not None or scale_is_bf16:
         logger.debug("stage 2: use_cshuffle_epilog / scale_is_bf16 do not apply here and are ignored")
     impl_code = _IMPL[impl]
-    in_code = _lib.E4M3 if in_dtype == "fp8" else _lib.I8
+    in_code = _IN_CODE[in_dtype]
     in_torch = _IN_TORCH[in_dtype]
+    unscaled = in_dtype in ("fp16", "bf16")
+    ebytes = 2 if unscaled else 1
     out_torch = torch.float32 if out_is_f32 else (torch.bfloat16 if out_is_bf16 else torch.float16)
     out_code = _lib.DTYPE_CODE[out_torch]
     wrows = experts * model_dim
@@ -165,8 +179,11 @@ def compile_moe_gemm2(*, model_dim: int, inter_dim: int, experts: int, topk: int
         _lib.require_cuda("arg_out", arg_out, (out_torch,), out_rows * model_dim)
         _lib.require_cuda("arg_x", arg_x, in_torch, pairs * inter_dim)
         _lib.require_cuda("arg_w", arg_w, in_torch, wrows * inter_dim)
-        _lib.require_cuda("arg_scale_x", arg_scale_x, (torch.float32,), pairs)
-        _lib.require_cuda("arg_scale_w", arg_scale_w, (torch.float32,), wrows)
+        if not unscaled:
+            _lib.require_cuda("arg_scale_x", arg_scale_x, (torch.float32,), pairs)
+            _lib.require_cuda("arg_scale_w", arg_scale_w, (torch.float32,), wrows)
+        sx_ptr = 0 if unscaled else _lib.ptr(arg_scale_x)
+        sw_ptr = 0 if unscaled else _lib.ptr(arg_scale_w)
         _lib.require_cuda("arg_sorted_token_ids", arg_sorted_token_ids, (torch.int32,), max(0, cap_rows - tile_m + 1))
         _lib.require_cuda("arg_expert_ids", arg_expert_ids, (torch.int32,), blocks)
         _lib.require_cuda("arg_sorted_weights", arg_sorted_weights, (torch.float32,), max(0, cap_rows - tile_m + 1))
@@ -176,13 +193,14 @@ def compile_moe_gemm2(*, model_dim: int, inter_dim: int, experts: int, topk: int
         w_plain = _plain_weight(arg_w, wrows, inter_dim, w_layout, h)
         a_ptr, a_layout = _lib.ptr(arg_x), _lib.ROWS_BY_PAIR
         if impl_code == _lib.IMPL_TCGEN05 and tile_m > _GATHER_IN_KERNEL_MAX:
-            gbuf = _resolve_scratch(scratch, gather_buffer, "gather_buffer", arg_x.device, h, cap_rows * inter_dim)
+            gbuf = _resolve_scratch(scratch, gather_buffer, "gather_buffer", arg_x.device, h,
+                                    cap_rows * inter_dim * ebytes)
             _lib.check(lib.flymoe_gather_rows(a_ptr, _lib.ptr(gbuf), _lib.ptr(arg_sorted_token_ids),
-                                              _lib.ptr(arg_num_valid_ids), tokens, topk, inter_dim,
+                                              _lib.ptr(arg_num_valid_ids), tokens, topk, inter_dim * ebytes,
                                               _lib.ROWS_BY_PAIR, cap_rows, h), "gather_rows")
             a_ptr, a_layout = _lib.ptr(gbuf), _lib.ROWS_SORTED
         _lib.check(lib.flymoe_moe_gemm2_pertoken(
-            _lib.ptr(arg_out), a_ptr, _lib.ptr(arg_scale_x), _lib.ptr(w_plain), _lib.ptr(arg_scale_w),
+            _lib.ptr(arg_out), a_ptr, sx_ptr, _lib.ptr(w_plain), sw_ptr,
             _lib.ptr(arg_sorted_token_ids), _lib.ptr(arg_expert_ids), _lib.ptr(arg_sorted_weights),
             _lib.ptr(arg_num_valid_ids), tokens, model_dim, inter_dim, blocks, experts, topk, tile_m,
             1 if doweight_stage2 else 0, in_code, out_code, acc, a_layout, _lib.ROWS_BY_PAIR, impl_code, h),

@@ -166,8 +166,10 @@ int flymoe_moe_gemm2(void* out, const void* a2, const float* scale_a, int64_t sa
 /* The two stages with ONE scale per activation row and ONE per weight row (output column)
  * instead of 128-wide blocks: the per-token / per-channel family.
  * Replace kernels/moe_gemm_2stage.py:90-108 (compile_moe_gemm1, launcher :1730-1745) and
- * :1780-1796 (compile_moe_gemm2, launcher :3151-3166) for in_dtype "fp8", "int8" and
- * "int8smooth".  in_dtype E4M3 or I8 (signed 8-bit operands, exact int32 accumulation).
+ * :1780-1796 (compile_moe_gemm2, launcher :3151-3166) for in_dtype "fp8", "int8", "int8smooth",
+ * "fp16" and "bf16".  in_dtype E4M3, I8 (signed 8-bit operands, exact int32 accumulation), or
+ * F16 / BF16 (16-bit operands and weights, tcgen05 kernel only; their scale pointers may be null,
+ * which means every scale is 1, as in the reference where these variants carry no scales).
  * Stage 1: x [T,H] (x_layout BY_TOKEN), [T*k,H] (BY_PAIR: "int8smooth") or rows already in sorted
  * order (SORTED); scale_x f32 [T] (x_scale_layout BY_TOKEN), [T*k] (BY_PAIR)
  * or per sorted row; w [E,2I,H] row-major, scale_w f32 [E*2I]; out F16/BF16 [T*k,I]
@@ -309,6 +311,10 @@ int flymoe_quant_act_1x128(const void* x, int x_dtype, void* q, float* scale, in
  * row-major [E*N, K]; to_plain!=0 undoes the shuffle.  src != dst. */
 int flymoe_shuffle_weight(const void* src, void* dst, int64_t rows, int cols, int to_plain,
                           void* stream);
+/* The same for elements of elem_bytes (1 or 2) bytes: the reference's order keeps 16 bytes of one row
+ * together, i.e. 16 one-byte or 8 two-byte elements (tests/utils.py:84), cols counts elements. */
+int flymoe_shuffle_weight_elems(const void* src, void* dst, int64_t rows, int cols, int elem_bytes,
+                                int to_plain, void* stream);
 
 #ifdef __cplusplus
 }

@@ -29,7 +29,8 @@ Reference locations each function follows (paths inside the reference project):
 * per-token-scale family (one scale per activation row / weight row)
                   tests/kernels/test_ref.py:91-165 (stage 1), :168-239 (stage 2),
                   quantisation of its inputs tests/kernels/test_moe_gemm.py:446-450,
-                  :463-488 (fp8, int8, per-(token, slot) "int8smooth")
+                  :463-488 (fp8, int8, per-(token, slot) "int8smooth"), :451-462 (fp16 / bf16:
+                  cast, no scales)
 
 Differences from the reference text, all value-preserving: weights are
 dequantised one expert at a time (the reference expands every expert to fp32
@@ -153,19 +154,24 @@ def quant_weight_128x128(w: torch.Tensor):
 
 
 def shuffle_weight(w: torch.Tensor) -> torch.Tensor:
-    """[..., N, K] one-byte elements -> 16x16 preshuffle order (same shape)."""
-    assert w.element_size() == 1
+    """[..., N, K] one- or two-byte elements -> 16x16 preshuffle order (same shape): groups of 16 rows x
+    32 elements, inside which 16 bytes of one row (16 or 8 elements) stay together."""
+    assert w.element_size() in (1, 2)
+    kk = 16 // w.element_size()
     N, K = w.shape[-2], w.shape[-1]
-    v = w.view(torch.uint8).reshape(-1, N // 16, 16, K // 32, 2, 16)
+    carrier = torch.uint8 if w.element_size() == 1 else torch.int16
+    v = w.view(carrier).reshape(-1, N // 16, 16, K // 32, 32 // kk, kk)
     v = v.permute(0, 1, 3, 4, 2, 5).contiguous()
     return v.view(*w.shape).view(w.dtype)
 
 
 def unshuffle_weight(w: torch.Tensor) -> torch.Tensor:
     """Inverse of shuffle_weight."""
-    assert w.element_size() == 1
+    assert w.element_size() in (1, 2)
+    kk = 16 // w.element_size()
     N, K = w.shape[-2], w.shape[-1]
-    v = w.view(torch.uint8).reshape(-1, N // 16, K // 32, 2, 16, 16)
+    carrier = torch.uint8 if w.element_size() == 1 else torch.int16
+    v = w.view(carrier).reshape(-1, N // 16, K // 32, 32 // kk, 16, kk)
     v = v.permute(0, 1, 4, 2, 3, 5).contiguous()
     return v.view(*w.shape).view(w.dtype)
 
@@ -263,17 +269,18 @@ def pertoken_stage1(x_q, scale_x, w1_q, scale_w1, topk_ids, topk_weights, inter_
     """silu(x W1g^T) * (x W1u^T) with x = x_q * scale_x (per row) and W = w_q * scale_w (per row).
 
     x_q [T,K] (or [T,k,K] when every (token, slot) pair brings its own row) of e4m3/int8, scale_x
-    [T,1] ([T,k,1]); w1_q [E,2I,K], scale_w1 [E,2I,1].  Returns f32 [T,k,I]."""
+    [T,1] ([T,k,1]); w1_q [E,2I,K], scale_w1 [E,2I,1].  f16/bf16 operands come with ``None`` scales
+    (no dequantisation, tests/kernels/test_ref.py:57-69 of the reference).  Returns f32 [T,k,I]."""
     ids = torch.as_tensor(topk_ids).to(torch.int64)
     T, k = ids.shape
     E = w1_q.shape[0]
-    x = x_q.to(torch.float32) * scale_x
+    x = x_q.to(torch.float32) if scale_x is None else x_q.to(torch.float32) * scale_x
     out = torch.zeros((T, k, inter_dim), dtype=torch.float32)
     for e in range(E):
         tok, slot = (ids == e).nonzero(as_tuple=True)
         if tok.numel() == 0:
             continue
-        w = w1_q[e].to(torch.float32) * scale_w1[e]
+        w = w1_q[e].to(torch.float32) if scale_w1 is None else w1_q[e].to(torch.float32) * scale_w1[e]
         rows = x[tok] if x.dim() == 2 else x[tok, slot]
         y2 = F.linear(rows, w)
         y = F.silu(y2[:, :inter_dim]) * y2[:, inter_dim:]
@@ -290,13 +297,14 @@ def pertoken_stage2(a2_q, scale_a2, w2_q, scale_w2, topk_ids, topk_weights, mode
     ids = torch.as_tensor(topk_ids).to(torch.int64)
     T, k = ids.shape
     E = w2_q.shape[0]
-    a2 = a2_q.to(torch.float32) * scale_a2
+    a2 = a2_q.to(torch.float32) if scale_a2 is None else a2_q.to(torch.float32) * scale_a2
     out = torch.zeros((T, k, model_dim), dtype=torch.float32)
     for e in range(E):
         tok, slot = (ids == e).nonzero(as_tuple=True)
         if tok.numel() == 0:
             continue
-        y = F.linear(a2[tok, slot], w2_q[e].to(torch.float32) * scale_w2[e])
+        w = w2_q[e].to(torch.float32) if scale_w2 is None else w2_q[e].to(torch.float32) * scale_w2[e]
+        y = F.linear(a2[tok, slot], w)
         if doweight_stage2:
             y = y * torch.as_tensor(topk_weights)[tok, slot].unsqueeze(-1)
         out[tok, slot] = y

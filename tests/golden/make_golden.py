@@ -112,8 +112,11 @@ def main() -> None:
     q, s = pertoken_quant(xs.view(24, 3, 128), quant_dtype=FP8)
     wq_small = (torch.randn((2, 64, 128), generator=g) * 50).to(FP8)
     shuf = shuffle_weight(wq_small.clone(), layout=(16, 16))
+    w16 = torch.randn((2, 32, 64), generator=g).to(torch.bfloat16)          # two-byte elements: 8 per 16-byte chunk
+    shuf16 = shuffle_weight(w16.clone(), layout=(16, 16))
     save("quant_shuffle.npz", x=xs.numpy(), q=u8(q.view(24, 384)),
-                        scale=s.view(24, 3).numpy(), w=u8(wq_small), w_shuffled=u8(shuf))
+                        scale=s.view(24, 3).numpy(), w=u8(wq_small), w_shuffled=u8(shuf),
+                        w16=bf16_bits(w16), w16_shuffled=bf16_bits(shuf16))
 
     # ------------------------------------------------------------------ sorting
     sort_cases = [(1, 8, 2, 32, False), (7, 32, 5, 32, False), (31, 64, 6, 16, False), (64, 256, 8, 32, False),
@@ -227,18 +230,28 @@ def main() -> None:
     from tests.helpers import pertoken_inputs
     out = {}
     cases = [("fp8", 64, 256, 128, 4, 2, False), ("int8", 64, 256, 128, 4, 2, False),
-             ("int8smooth", 33, 256, 128, 4, 2, False), ("fp8", 129, 512, 256, 8, 2, True)]
+             ("int8smooth", 33, 256, 128, 4, 2, False), ("fp8", 129, 512, 256, 8, 2, True),
+             ("bf16", 64, 256, 128, 4, 2, False), ("fp16", 40, 256, 128, 4, 2, True)]
+    half = {"fp16": torch.float16, "bf16": torch.bfloat16}
     for i, (in_dtype, T, H, I, E, k, doweight1) in enumerate(cases):
         qd = FP8 if in_dtype == "fp8" else torch.int8
         xq, sx, w1q, sw1, w2q, sw2, ti, tw = pertoken_inputs(in_dtype, T, H, I, E, k, 900 + i, pertoken_quant)
-        o1 = pt["torch_moe_gemm1"](xq, w1q.view(E * 2 * I, H), sx, sw1.view(E * 2 * I, 1), ti, tw, I, doweight1)
-        a2q, sa2 = pertoken_quant(o1, quant_dtype=qd)
-        o2 = pt["torch_moe_gemm2"](a2q, w2q, sa2, sw2.view(E, H, 1), ti, tw, H, not doweight1)
+        if in_dtype in half:          # no scales; the stage-2 input is stage 1's output in the same 16-bit type
+            o1 = pt["torch_moe_gemm1"](xq, w1q.view(E * 2 * I, H), None, None, ti, tw, I, doweight1)
+            a2q, sa2 = o1.to(half[in_dtype]), None
+            o2 = pt["torch_moe_gemm2"](a2q, w2q, None, None, ti, tw, H, not doweight1)
+            digest = sha(u8(xq), u8(w1q), u8(w2q), ti.numpy(), tw.numpy())
+        else:
+            o1 = pt["torch_moe_gemm1"](xq, w1q.view(E * 2 * I, H), sx, sw1.view(E * 2 * I, 1), ti, tw, I, doweight1)
+            a2q, sa2 = pertoken_quant(o1, quant_dtype=qd)
+            o2 = pt["torch_moe_gemm2"](a2q, w2q, sa2, sw2.view(E, H, 1), ti, tw, H, not doweight1)
+            digest = sha(u8(xq), sx.numpy(), u8(w1q), sw1.numpy(), u8(w2q), sw2.numpy(), ti.numpy(), tw.numpy())
         out.update({f"p{i}_cfg": np.array([T, H, I, E, k, int(doweight1), 900 + i], dtype=np.int32),
                     f"p{i}_dtype": np.array([in_dtype]),
-                    f"p{i}_input_sha": np.array([sha(u8(xq), sx.numpy(), u8(w1q), sw1.numpy(), u8(w2q), sw2.numpy(),
-                                                     ti.numpy(), tw.numpy())]),
-                    f"p{i}_out1": o1.numpy(), f"p{i}_a2q": u8(a2q), f"p{i}_sa2": sa2.numpy(), f"p{i}_out2": o2.numpy()})
+                    f"p{i}_input_sha": np.array([digest]),
+                    f"p{i}_out1": o1.numpy(), f"p{i}_a2q": u8(a2q), f"p{i}_out2": o2.numpy()})
+        if sa2 is not None:
+            out[f"p{i}_sa2"] = sa2.numpy()
         if i == 0:     # the first case also carries its inputs; the others are regenerated from their seeds
             out.update({f"p{i}_xq": u8(xq), f"p{i}_sx": sx.numpy(), f"p{i}_w1q": u8(w1q), f"p{i}_sw1": sw1.numpy(),
                         f"p{i}_w2q": u8(w2q), f"p{i}_sw2": sw2.numpy(), f"p{i}_ids": ti.numpy(), f"p{i}_tw": tw.numpy()})

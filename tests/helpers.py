@@ -56,6 +56,7 @@ def pertoken_inputs(in_dtype, T, H, I, E, k, seed, quant):
     (tests/kernels/test_moe_gemm.py:380-400, :446-488 in the reference project): randn activations,
     randn/10 weights, routing = top-k of a softmax of random scores.  ``quant(x, quant_dtype=...)`` is
     the row quantiser (the reference's own when the fixtures are generated, the oracle's in the tests).
+    "fp16" / "bf16" cast instead of quantising and have ``None`` scales (:451-462 there).
     Returns xq ([T,H], or [T,k,H] for "int8smooth"), sx, w1q [E,2I,H], sw1, w2q [E,H,I], sw2, ids, weights."""
     g = torch.Generator().manual_seed(seed)
     qd = FP8 if in_dtype == "fp8" else torch.int8
@@ -65,6 +66,9 @@ def pertoken_inputs(in_dtype, T, H, I, E, k, seed, quant):
     score = torch.softmax(torch.randn((T, E), generator=g), dim=1)
     tw, ti = torch.topk(score, k, dim=1)
     tw = tw.to(torch.float32)
+    if in_dtype in ("fp16", "bf16"):
+        dt = torch.float16 if in_dtype == "fp16" else torch.bfloat16
+        return x.to(dt), None, w1.to(dt), None, w2.to(dt), None, ti.to(torch.int32), tw
     if in_dtype == "int8smooth":
         smooth = 0.75 + 0.5 * torch.rand((E, H), generator=g)
         xr = x[:, None, :] * smooth[ti.to(torch.int64)]

@@ -126,9 +126,12 @@ def test_dense_blockscale_gemm_argument_rules():
 
 def test_pertoken_builder_rules(lib):
     base = dict(model_dim=256, inter_dim=128, experts=4, topk=2, tile_m=16, tile_n=64, tile_k=128)
-    for bad in ("fp16", "bf16", "int4", "int4_bf16"):
+    for bad in ("int4", "int4_bf16"):
         with pytest.raises(ValueError, match="not built"):
             pt.compile_moe_gemm1(doweight_stage1=False, in_dtype=bad, **base)
+    with pytest.raises(ValueError, match="tensor-core path only"):
+        pt.compile_moe_gemm1(doweight_stage1=False, in_dtype="bf16", impl="simt", **base)
+    assert callable(pt.compile_moe_gemm1(doweight_stage1=False, in_dtype="fp16", **base))
     with pytest.raises(ValueError, match="in_dtype must be one of"):
         pt.compile_moe_gemm2(doweight_stage2=True, in_dtype="fp6", **base)
     with pytest.raises(ValueError, match="only supports out_dtype"):
@@ -143,8 +146,11 @@ def test_pertoken_builder_rules(lib):
                                        4, 128, 256, 1, 2, 2, 16, 0, _lib.I8, _lib.E4M3, 2, 0, 1, 0, None)
     assert rc == -1 and b"out_dtype" in lib.flymoe_last_error()
     rc = lib.flymoe_moe_gemm2_pertoken(None, None, None, None, None, None, None, None, None,
-                                       4, 256, 128, 1, 2, 2, 16, 1, _lib.F16, _lib.F16, 1, 2, 1, 0, None)
+                                       4, 256, 128, 1, 2, 2, 16, 1, _lib.F32, _lib.F16, 1, 2, 1, 0, None)
     assert rc == -1 and b"in_dtype" in lib.flymoe_last_error()
+    rc = lib.flymoe_moe_gemm2_pertoken(None, None, None, None, None, None, None, None, None,          # 16-bit operands:
+                                       4, 256, 128, 1, 2, 2, 16, 1, _lib.BF16, _lib.F16, 1, 2, 1, 1, None)   # not in the SIMT kernel
+    assert rc == -1 and b"tcgen05" in lib.flymoe_last_error()
     rc = lib.flymoe_selftest_bounded_wait(0, None)
     assert rc == -1 and b"limit_ns" in lib.flymoe_last_error()
 

@@ -22,6 +22,15 @@ def test_shuffle_weight_matches_reference_layout():
     s2 = bs.shuffle_weight(big.cuda(), 3 * 256, 1024)
     assert torch.equal(s2.cpu().view(3, 256, 1024), orc.shuffle_weight(big))
     assert torch.equal(bs.unshuffle_weight(s2, 3 * 256, 1024).cpu().view(3, 256, 1024), big)
+    # two-byte elements (fixture made by the reference's own shuffle on bf16 weights)
+    w16 = torch.from_numpy(g["w16"]).view(torch.bfloat16).cuda()
+    E, N, K = w16.shape
+    shuf16 = bs.shuffle_weight(w16, E * N, K)
+    assert np.array_equal(shuf16.view(torch.int16).cpu().numpy().reshape(E, N, K), g["w16_shuffled"])
+    assert torch.equal(bs.unshuffle_weight(shuf16, E * N, K).view(E, N, K).view(torch.int16), w16.view(torch.int16))
+    big16 = torch.randint(-30000, 30000, (2, 128, 512), dtype=torch.int16).view(torch.float16)
+    s3 = bs.shuffle_weight(big16.cuda(), 2 * 128, 512)
+    assert torch.equal(s3.cpu().view(2, 128, 512).view(torch.int16), orc.shuffle_weight(big16).view(torch.int16))
 
 
 @pytest.mark.parametrize("T,k,D,dt,masked", [(1, 6, 5120, "f16", False), (5, 8, 7168, "bf16", False),

@@ -44,6 +44,14 @@ def sort(ids, tw, E, unit):
     return s_ids, s_w, s_e, nv, nblk
 
 
+HALF = {"fp16": torch.float16, "bf16": torch.bfloat16}
+
+
+def scale_arg(s):
+    """Scales as the launcher takes them; the 16-bit variants have none and get the reference's empty tensor."""
+    return torch.empty(0, dtype=torch.float32, device="cuda") if s is None else s.cuda().view(-1)
+
+
 def dev_weight(wq, layout):
     E, N, K = wq.shape
     w = wq.cuda()
@@ -59,8 +67,8 @@ def run_stage1(shape, in_dtype, out_dtype, impl, w_layout, doweight):
                                impl=impl)
     dt = {"f16": torch.float16, "bf16": torch.bfloat16}[out_dtype]
     out = torch.full((T * k + 16, I), 77.0, dtype=dt, device="cuda")
-    exe(out.view(-1)[: T * k * I], xq.cuda().view(-1, H), dev_weight(w1q, w_layout), sx.cuda().view(-1),
-        sw1.cuda().view(-1), s_ids, s_e, s_w, nv, T, I, H, nblk, torch.cuda.current_stream())
+    exe(out.view(-1)[: T * k * I], xq.cuda().view(-1, H), dev_weight(w1q, w_layout), scale_arg(sx),
+        scale_arg(sw1), s_ids, s_e, s_w, nv, T, I, H, nblk, torch.cuda.current_stream())
     torch.cuda.synchronize()
     assert bool((out[T * k:] == 77.0).all()), "stage 1 wrote past its output rows"
     ref = orc.pertoken_stage1(xq, sx, w1q, sw1, ids, tw, I, doweight)
@@ -85,13 +93,14 @@ def run_stage2(shape, in_dtype, out_dtype, impl, w_layout, mode, doweight=True):
     T, H, I, E, k, tile_m = SHAPES[shape]
     xq, sx, w1q, sw1, w2q, sw2, ids, tw = inputs(shape, in_dtype)
     qd = hp.FP8 if in_dtype == "fp8" else torch.int8
-    a2q, sa2 = orc.quant_rows(orc.pertoken_stage1(xq, sx, w1q, sw1, ids, tw, I, False), qd)
+    o1 = orc.pertoken_stage1(xq, sx, w1q, sw1, ids, tw, I, False)
+    a2q, sa2 = (o1.to(HALF[in_dtype]), None) if in_dtype in HALF else orc.quant_rows(o1, qd)
     s_ids, s_w, s_e, nv, nblk = sort(ids, tw, E, tile_m)
     common = dict(model_dim=H, inter_dim=I, experts=E, topk=k, tile_m=tile_m, tile_n=256, tile_k=128,
                   doweight_stage2=doweight, in_dtype=in_dtype, out_dtype=out_dtype, w_layout=w_layout, impl=impl)
     dt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}[out_dtype]
     w = dev_weight(w2q, w_layout)
-    args = (a2q.cuda().view(-1, I), w, sa2.cuda().view(-1), sw2.cuda().view(-1), s_ids, s_e, s_w, nv, T, H, I, nblk)
+    args = (a2q.cuda().view(-1, I), w, scale_arg(sa2), scale_arg(sw2), s_ids, s_e, s_w, nv, T, H, I, nblk)
     if mode == "rows":
         exe = pt.compile_moe_gemm2(accumulate=False, **common)
         out = torch.zeros((T * k + 8, H), dtype=dt, device="cuda")
@@ -129,6 +138,61 @@ def test_pertoken_stage2(shape, in_dtype, out_dtype, w_layout, mode, impl):
     assert_close(out, ref, RTOL, ATOL + step, f"per-token stage 2 {shape} {in_dtype} {mode} {impl}")
     if out_dtype == "f32":
         assert_close(out, ref, 1e-4, 1e-5 * pair_peak, f"per-token stage 2 tight {shape} {in_dtype} {impl}")
+
+
+@pytest.mark.parametrize("shape,in_dtype,out_dtype,w_layout,doweight", [
+    ("S", "bf16", "bf16", "preshuffle16x16", False), ("S", "fp16", "f16", "plain", True),
+    ("M", "bf16", "f16", "plain", False), ("M", "fp16", "f16", "preshuffle16x16", False),
+    ("T128", "bf16", "bf16", "preshuffle16x16", False), ("T128", "fp16", "bf16", "plain", True),
+])
+def test_pertoken_stage1_16bit_operands(shape, in_dtype, out_dtype, w_layout, doweight):
+    """fp16 / bf16 activations and weights, no scales (tests/kernels/test_moe_gemm.py:451-462, :569-579 of
+    the reference): the same launcher, the scale arguments are the reference's empty tensors."""
+    out, ref = run_stage1(shape, in_dtype, out_dtype, "tcgen05", w_layout, doweight)
+    assert_close(out, ref, RTOL, ATOL, f"16-bit stage 1 {shape} {in_dtype}")
+    eps = 2.0 ** -8 if out_dtype == "bf16" else 2.0 ** -11
+    assert_close(out, ref, 2 * eps, 1e-3, f"16-bit stage 1 tight {shape} {in_dtype}")
+
+
+@pytest.mark.parametrize("shape,in_dtype,out_dtype,w_layout,mode", [
+    ("S", "bf16", "f32", "plain", "atomic"), ("S", "fp16", "f16", "preshuffle16x16", "rows"),
+    ("M", "bf16", "bf16", "preshuffle16x16", "reduce"), ("M", "fp16", "f32", "plain", "atomic"),
+    ("T128", "bf16", "bf16", "plain", "atomic"), ("T128", "fp16", "f16", "preshuffle16x16", "reduce"),
+])
+def test_pertoken_stage2_16bit_operands(shape, in_dtype, out_dtype, w_layout, mode):
+    out, ref, pair_peak = run_stage2(shape, in_dtype, out_dtype, "tcgen05", w_layout, mode)
+    step = 0.0 if out_dtype == "f32" or mode == "rows" else 2.0 ** (-7 if out_dtype == "bf16" else -10) * pair_peak
+    assert_close(out, ref, RTOL, ATOL + step, f"16-bit stage 2 {shape} {in_dtype} {mode}")
+    if out_dtype == "f32":
+        assert_close(out, ref, 1e-4, 1e-5 * pair_peak, f"16-bit stage 2 tight {shape} {in_dtype}")
+
+
+def test_pertoken_16bit_golden_fixture():
+    """The two 16-bit cases of the fixture generated from the reference's own torch_moe_gemm1/2."""
+    g = hp.load("moe_pertoken.npz")
+    seen = 0
+    for i in range(int(g["n"][0])):
+        in_dtype = str(g[f"p{i}_dtype"][0])
+        if in_dtype not in HALF:
+            continue
+        seen += 1
+        T, H, I, E, k, doweight1, seed = (int(v) for v in g[f"p{i}_cfg"])
+        xq, _, w1q, _, w2q, _, ids, tw = hp.pertoken_inputs(in_dtype, T, H, I, E, k, seed, orc.quant_rows)
+        s_ids, s_w, s_e, nv, nblk = sort(ids, tw, E, 16)
+        common = dict(model_dim=H, inter_dim=I, experts=E, topk=k, tile_m=16, tile_n=128, tile_k=128, in_dtype=in_dtype)
+        none = scale_arg(None)
+        out1 = torch.zeros((T * k, I), dtype=HALF[in_dtype], device="cuda")
+        pt.compile_moe_gemm1(doweight_stage1=bool(doweight1), out_dtype="f16" if in_dtype == "fp16" else "bf16", **common)(
+            out1.view(-1), xq.cuda(), dev_weight(w1q, "preshuffle16x16"), none, none, s_ids, s_e, s_w, nv, T, I, H, nblk)
+        ref1 = torch.from_numpy(g[f"p{i}_out1"])
+        assert_close(out1.cpu().view(T, k, I), ref1, RTOL, ATOL, f"fixture case {i} stage 1")
+        a2 = torch.from_numpy(g[f"p{i}_a2q"]).view(HALF[in_dtype]).cuda()          # the reference's own stage-2 input
+        out2 = torch.zeros((T, H), dtype=torch.float32, device="cuda")
+        pt.compile_moe_gemm2(doweight_stage2=not bool(doweight1), out_dtype="f32", **common)(
+            out2.view(-1), a2.view(-1, I), dev_weight(w2q, "preshuffle16x16"), none, none, s_ids, s_e, s_w, nv, T, H, I, nblk)
+        torch.cuda.synchronize()
+        assert_close(out2.cpu(), torch.from_numpy(g[f"p{i}_out2"]), RTOL, ATOL, f"fixture case {i} stage 2")
+    assert seen == 2
 
 
 @pytest.mark.parametrize("in_dtype", ["fp8", "int8"])

@@ -20,6 +20,11 @@ def test_pertoken_quant_and_shuffle_match_reference():
     shuf = orc.shuffle_weight(w)
     assert np.array_equal(hp.u8(shuf), g["w_shuffled"])
     assert np.array_equal(hp.u8(orc.unshuffle_weight(shuf)), g["w"])
+    # two-byte elements keep 8 of a row together (16 bytes), so the pattern differs from the one-byte one
+    w16 = torch.from_numpy(g["w16"]).view(torch.bfloat16)
+    shuf16 = orc.shuffle_weight(w16)
+    assert np.array_equal(shuf16.view(torch.int16).numpy(), g["w16_shuffled"])
+    assert torch.equal(orc.unshuffle_weight(shuf16).view(torch.int16), w16.view(torch.int16))
 
 
 def test_sorting_matches_reference():
@@ -125,16 +130,24 @@ def test_pertoken_family_matches_reference_functions():
         T, H, I, E, k, doweight1, seed = (int(v) for v in g[f"p{i}_cfg"])
         in_dtype = str(g[f"p{i}_dtype"][0])
         qd = hp.FP8 if in_dtype == "fp8" else torch.int8
+        half = {"fp16": torch.float16, "bf16": torch.bfloat16}.get(in_dtype)
         xq, sx, w1q, sw1, w2q, sw2, ids, tw = hp.pertoken_inputs(in_dtype, T, H, I, E, k, seed, orc.quant_rows)
-        got_sha = hp.sha(hp.u8(xq), sx.numpy(), hp.u8(w1q), sw1.numpy(), hp.u8(w2q), sw2.numpy(), ids.numpy(), tw.numpy())
+        if half is not None:
+            got_sha = hp.sha(hp.u8(xq), hp.u8(w1q), hp.u8(w2q), ids.numpy(), tw.numpy())
+        else:
+            got_sha = hp.sha(hp.u8(xq), sx.numpy(), hp.u8(w1q), sw1.numpy(), hp.u8(w2q), sw2.numpy(), ids.numpy(), tw.numpy())
         assert got_sha == str(g[f"p{i}_input_sha"][0]), f"case {i}: regenerated inputs differ from the fixture's"
         if i == 0:
             assert np.array_equal(hp.u8(xq), g["p0_xq"]) and np.array_equal(sw1.numpy(), g["p0_sw1"])
         o1 = orc.pertoken_stage1(xq, sx, w1q, sw1, ids, tw, I, bool(doweight1))
         ref1 = torch.from_numpy(g[f"p{i}_out1"])
         assert torch.allclose(o1, ref1, rtol=1e-5, atol=1e-5 * float(ref1.abs().max())), f"case {i} stage 1"
-        a2q, sa2 = orc.quant_rows(ref1, qd)
-        assert np.array_equal(hp.u8(a2q), g[f"p{i}_a2q"]) and np.array_equal(sa2.numpy(), g[f"p{i}_sa2"])
+        if half is not None:
+            a2q, sa2 = ref1.to(half), None
+            assert np.array_equal(hp.u8(a2q), g[f"p{i}_a2q"])
+        else:
+            a2q, sa2 = orc.quant_rows(ref1, qd)
+            assert np.array_equal(hp.u8(a2q), g[f"p{i}_a2q"]) and np.array_equal(sa2.numpy(), g[f"p{i}_sa2"])
         o2 = orc.pertoken_stage2(a2q, sa2, w2q, sw2, ids, tw, H, not bool(doweight1))
         ref2 = torch.from_numpy(g[f"p{i}_out2"])
         assert torch.allclose(o2, ref2, rtol=1e-5, atol=1e-5 * float(ref2.abs().max())), f"case {i} stage 2"
