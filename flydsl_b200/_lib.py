@@ -70,6 +70,8 @@ _SIGNATURES = {
     "flymoe_quant_act_1x128": (c_int, [_P, c_int, _P, _P, c_int64, c_int, c_int, _P]),
     "flymoe_shuffle_weight": (c_int, [_P, _P, c_int64, c_int, c_int, _P]),
     "flymoe_shuffle_weight_elems": (c_int, [_P, _P, c_int64, c_int, c_int, c_int, _P]),
+    "flymoe_unpack_int4_weight": (c_int, [_P, _P, c_int64, c_int, c_int, _P]),
+    "flymoe_unpack_int4_weight_grouped": (c_int, [_P, _P, c_int64, c_int, c_int, _P, c_int, c_int, c_int, _P]),
 }
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)
 

@@ -203,6 +203,57 @@ shuffle_weight_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, lo
   }
 }
 
+// Packed int4 weights of the reference (tests/kernels/test_moe_gemm.py:49-65 there): the signed 4-bit values
+// of the 16x16-preshuffled one-byte layout, eight consecutive ones v0..v7 in four bytes b_i = (v_{i+4} << 4) | v_i.
+// One thread unpacks four bytes to eight row-major values (the eight lie in one 16-byte chunk of one row).
+// With gscale (bf16 output only) every value is multiplied by the scale of its 32-wide K group before it is
+// rounded: scale[e][k/32][n] as f32 [E, K/32, N], or as bf16 pairs [E, K/64, N, 2] (two adjacent groups of one
+// weight row in one 32-bit word: tests/utils.py:99-129 of the reference).
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+unpack_int4_weight_kernel(const uint32_t* __restrict__ packed, OutT* __restrict__ dst, long long rows, int cols,
+                          const void* __restrict__ gscale, int gscale_is_bf16, int rows_per_expert) {
+  const long long nquads = rows * cols / 8;
+  const int groups = cols / 32;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nquads;
+       i += (long long)gridDim.x * blockDim.x) {
+    const uint32_t w = __ldg(packed + i);
+    const long long chunk = i >> 1;                  // 16-byte chunk of the preshuffled one-byte layout
+    const int off = int(i & 1) * 8;
+    const int n16 = int(chunk & 15);
+    long long rest = chunk >> 4;
+    const int kcl = int(rest & 1);
+    rest >>= 1;
+    const int kg = int(rest % groups);
+    const long long nb = rest / groups;
+    const long long n = nb * 16 + n16;
+    const int k = (kg * 2 + kcl) * 16 + off;
+    float sc = 1.f;
+    if (sizeof(OutT) == 2 && gscale != nullptr) {
+      const long long e = n / rows_per_expert;
+      const long long nl = n - e * rows_per_expert;
+      if (gscale_is_bf16)
+        sc = __bfloat162float(__ldg(static_cast<const __nv_bfloat16*>(gscale) +
+                                    ((e * (groups / 2) + kg / 2) * rows_per_expert + nl) * 2 + (kg & 1)));
+      else
+        sc = __ldg(static_cast<const float*>(gscale) + (e * groups + kg) * rows_per_expert + nl);
+    }
+    OutT* out = dst + n * cols + k;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int b = int((w >> (8 * j)) & 0xFFu);
+      const int lo = ((b & 0xF) ^ 8) - 8, hi = ((b >> 4) ^ 8) - 8;
+      if constexpr (sizeof(OutT) == 1) {
+        out[j] = OutT(lo);
+        out[j + 4] = OutT(hi);
+      } else {
+        out[j] = __float2bfloat16(float(lo) * sc);
+        out[j + 4] = __float2bfloat16(float(hi) * sc);
+      }
+    }
+  }
+}
+
 }  // namespace flymoe
 
 extern "C" int flymoe_gather_rows(const void* src, void* dst, const int32_t* sorted_ids,
@@ -352,4 +403,43 @@ extern "C" int flymoe_shuffle_weight_elems(const void* src, void* dst, int64_t r
 extern "C" int flymoe_shuffle_weight(const void* src, void* dst, int64_t rows, int cols, int to_plain,
                                      void* stream) {
   return flymoe_shuffle_weight_elems(src, dst, rows, cols, 1, to_plain, stream);
+}
+
+extern "C" int flymoe_unpack_int4_weight_grouped(const void* packed, void* dst, int64_t rows, int cols, int out_dtype,
+                                                 const void* group_scale, int group_scale_dtype, int group_size,
+                                                 int rows_per_expert, void* stream) {
+  using namespace flymoe;
+  FLYMOE_REQUIRE(packed && dst && packed != dst, "unpack_int4_weight: packed and dst must be distinct non-null pointers");
+  FLYMOE_REQUIRE(rows > 0 && rows % 16 == 0 && cols > 0 && cols % 32 == 0,
+                 "unpack_int4_weight: rows must be a multiple of 16 and cols of 32");
+  FLYMOE_REQUIRE(out_dtype == FLYMOE_I8 || out_dtype == FLYMOE_BF16, "unpack_int4_weight: out_dtype must be I8 or BF16");
+  FLYMOE_REQUIRE(aligned16(packed) && aligned16(dst), "unpack_int4_weight: pointers must be 16-byte aligned");
+  if (group_scale != nullptr) {
+    FLYMOE_REQUIRE(out_dtype == FLYMOE_BF16, "unpack_int4_weight: group scales need BF16 output");
+    FLYMOE_REQUIRE(group_size == 32, "unpack_int4_weight: group_size must be 32");
+    FLYMOE_REQUIRE(group_scale_dtype == FLYMOE_F32 || group_scale_dtype == FLYMOE_BF16,
+                   "unpack_int4_weight: group scales must be F32 or BF16");
+    FLYMOE_REQUIRE(rows_per_expert > 0 && rows % rows_per_expert == 0,
+                   "unpack_int4_weight: rows must be a multiple of rows_per_expert");
+    FLYMOE_REQUIRE(group_scale_dtype != FLYMOE_BF16 || cols % 64 == 0,
+                   "unpack_int4_weight: bf16 group scales come in pairs, cols must be a multiple of 64");
+  }
+  const long long nquads = rows * cols / 8;
+  const int blocks = int(std::min<long long>((nquads + 255) / 256, (long long)sm_count() * 32));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int sbf = group_scale_dtype == FLYMOE_BF16 ? 1 : 0;
+  if (out_dtype == FLYMOE_I8)
+    unpack_int4_weight_kernel<int8_t><<<blocks, 256, 0, s>>>(static_cast<const uint32_t*>(packed),
+                                                           static_cast<int8_t*>(dst), rows, cols, nullptr, 0, 1);
+  else
+    unpack_int4_weight_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(
+        static_cast<const uint32_t*>(packed), static_cast<__nv_bfloat16*>(dst), rows, cols, group_scale, sbf,
+        group_scale ? rows_per_expert : 1);
+  FLYMOE_CUDA_CHECK(cudaGetLastError());
+  return FLYMOE_OK;
+}
+
+extern "C" int flymoe_unpack_int4_weight(const void* packed, void* dst, int64_t rows, int cols, int out_dtype,
+                                         void* stream) {
+  return flymoe_unpack_int4_weight_grouped(packed, dst, rows, cols, out_dtype, nullptr, 0, 0, 0, stream);
 }

@@ -106,17 +106,49 @@ def prepare_weight(w: torch.Tensor, rows: int, cols: int, stream=None) -> torch.
     return _plain_weight(w, rows, cols, "preshuffle16x16", stream)
 
 
-def _plain_weight(w: torch.Tensor, rows: int, cols: int, layout: str, stream) -> torch.Tensor:
+def unpack_int4_weight(w: torch.Tensor, rows: int, cols: int, dtype=torch.int8, stream=None, *,
+                       group_scale: torch.Tensor | None = None, rows_per_expert: int = 0) -> torch.Tensor:
+    """The reference's packed-int4 weights (signed 4-bit values of the 16x16-preshuffled one-byte layout,
+    eight per four bytes; ``rows*cols/2`` bytes) -> row-major ``[rows*cols]`` int8 or bfloat16.
+    ``group_scale`` (bfloat16 output only): group-wise scales of 32-wide K groups in the reference's kernel
+    layout (f32 ``[E, cols/32, rows_per_expert]`` or bf16 ``[E, cols/64, rows_per_expert, 2]``), multiplied
+    in before the value is rounded to bfloat16."""
+    if dtype not in (torch.int8, torch.bfloat16):
+        raise ValueError(f"unpack_int4_weight: dtype must be torch.int8 or torch.bfloat16, got {dtype}")
+    _lib.require_cuda("w", w, (torch.int8, torch.uint8), rows * cols // 2)
+    gs_ptr, gs_code = None, 0
+    if group_scale is not None:
+        if rows_per_expert <= 0 or rows % rows_per_expert:
+            raise ValueError("unpack_int4_weight: rows must be a multiple of rows_per_expert")
+        _lib.require_cuda("group_scale", group_scale, (torch.float32, torch.bfloat16), rows * (cols // 32))
+        gs_ptr, gs_code = _lib.ptr(group_scale), _lib.DTYPE_CODE[group_scale.dtype]
+    out = torch.empty(rows * cols, dtype=dtype, device=w.device)
+    _order_after_current_stream(stream, w.device)
+    _lib.check(_lib.load().flymoe_unpack_int4_weight_grouped(
+        _lib.ptr(w), _lib.ptr(out), rows, cols, _lib.DTYPE_CODE[dtype], gs_ptr, gs_code, 32 if gs_ptr else 0,
+        rows_per_expert, _lib.stream_handle(stream)), "unpack_int4_weight")
+    return out
+
+
+def _plain_weight(w: torch.Tensor, rows: int, cols: int, layout: str, stream, int4_to=None,
+                  group_scale: torch.Tensor | None = None, rows_per_expert: int = 0) -> torch.Tensor:
+    """Row-major operand of a weight tensor, converted once per tensor.  ``int4_to`` (torch.int8 or
+    torch.bfloat16): ``w`` holds packed int4 values and is unpacked to that type instead, with the
+    group-wise scales folded in when given (the copy is then tied to that scale tensor as well)."""
     if layout == "plain":
         return w
     # An entry is only valid for the allocation it was made from: a freed weight's address is reused
     # by the allocator, so the storage object itself (weakly referenced) is part of the check.
     storage = w.untyped_storage()
-    key = (w.data_ptr(), w.numel(), w.element_size(), w.device.index, rows, cols)
+    gkey = None if group_scale is None else (group_scale.data_ptr(), group_scale._version, group_scale.dtype)
+    key = (w.data_ptr(), w.numel(), w.element_size(), w.device.index, rows, cols, int4_to, gkey)
     hit = _plain_cache.get(key)
     if hit is not None and hit[0] == w._version and hit[2]() is storage:
         return hit[1]
-    plain = unshuffle_weight(w, rows, cols, stream)
+    if int4_to is None:
+        plain = unshuffle_weight(w, rows, cols, stream)
+    else:
+        plain = unpack_int4_weight(w, rows, cols, int4_to, stream, group_scale=group_scale, rows_per_expert=rows_per_expert)
     _plain_cache[key] = (w._version, plain, weakref.ref(storage))
     weakref.finalize(storage, _drop_plain, key, id(plain))
     return plain

@@ -22,8 +22,20 @@ scales (the scale arguments are ignored; the reference passes empty tensors, :56
 With one scale per row and column the whole K range is accumulated inside the tensor cores'
 accumulator memory and every tile is scaled once, ``(sum_k a*w) * scale_a[row] * scale_w[col]``.
 
-Not built here: the packed-int4 (``int4``, ``int4_bf16``), group-wise and split-K variants of the
-reference raise ``ValueError`` at build time.
+``"int4"`` (W4A8) / ``"int4_bf16"`` (W4A16): the weights arrive as the reference's packed int4 bytes
+(its test's ``_pack_shuffled_int8_to_packed_int4_no_perm`` over the preshuffled values, ``N*K/2`` bytes)
+with one fp32 scale per weight row; x is int8 with per-token scales, or bf16 without.  The packed
+tensor is unpacked once per weight tensor (like the preshuffle conversion) to int8 or bf16 and the
+int8 / bf16 kernels run on the copy: same results, without the memory saving of 4-bit weights.
+
+``"int4_bf16"`` with ``group_size=32``: ``arg_scale_w`` holds group-wise scales in the reference's kernel
+layout (f32 ``[E, K/32, N]``, or with ``scale_is_bf16`` bf16 ``[E, K/64, N, 2]``) instead of one per weight
+row; they are multiplied in while unpacking (``bf16(value * scale)``), after which the scale-less bf16 kernel
+runs.
+
+Not built here: split-K (``k_batch > 1``) and group-wise scales with int8 activations (``in_dtype="int4"``
+with ``group_size > 0``) raise ``ValueError`` at build time; ``group_size`` other than 32 is rejected as in
+the reference and ignored for the variants without packed weights.
 Additions (keyword-only): ``w_layout`` ("preshuffle16x16" default, or "plain") and ``impl``
 ("tcgen05" default, "simt" cross-check) as in ``moe_blockscale_2stage``.
 """
@@ -39,10 +51,14 @@ from .moe_blockscale_2stage import (MoeGemm2Mode, _GATHER_IN_KERNEL_MAX, _IMPL, 
                                     _plain_weight, _resolve_scratch, compile_moe_reduction, logger)
 
 _VALID_IN = ("fp8", "fp16", "bf16", "int8", "int8smooth", "int4", "int4_bf16")
-_BUILT_IN = ("fp8", "int8", "int8smooth", "fp16", "bf16")
+_BUILT_IN = _VALID_IN
+# activation dtypes; the weights have the same type except for the packed-int4 variants (int8/uint8 bytes)
 _IN_TORCH = {"fp8": (torch.float8_e4m3fn, torch.uint8), "int8": (torch.int8,), "int8smooth": (torch.int8,),
-             "fp16": (torch.float16,), "bf16": (torch.bfloat16,)}
-_IN_CODE = {"fp8": _lib.E4M3, "int8": _lib.I8, "int8smooth": _lib.I8, "fp16": _lib.F16, "bf16": _lib.BF16}
+             "fp16": (torch.float16,), "bf16": (torch.bfloat16,), "int4": (torch.int8,), "int4_bf16": (torch.bfloat16,)}
+_IN_CODE = {"fp8": _lib.E4M3, "int8": _lib.I8, "int8smooth": _lib.I8, "fp16": _lib.F16, "bf16": _lib.BF16,
+            "int4": _lib.I8, "int4_bf16": _lib.BF16}
+_INT4_TO = {"int4": torch.int8, "int4_bf16": torch.bfloat16}          # what the packed weights are unpacked to
+_PACKED_W = (torch.int8, torch.uint8)
 _TILE_M = (16, 32, 64, 128)
 
 
@@ -51,8 +67,15 @@ def _check(in_dtype, group_size, k_batch, tile_m, tile_k, model_dim, inter_dim, 
         raise ValueError(f"in_dtype must be one of {_VALID_IN}, got {in_dtype!r}")
     if in_dtype not in _BUILT_IN:
         raise ValueError(f"in_dtype={in_dtype!r} is not built on this implementation (built: {_BUILT_IN})")
-    if group_size > 0:
-        raise ValueError("group-wise weight scales belong to the packed-int4 variants, which are not built here")
+    # group_size only means something with packed int4 weights (the reference ignores it otherwise)
+    if group_size > 0 and in_dtype == "int4":
+        raise ValueError("group-wise weight scales are built for in_dtype='int4_bf16' only: with int8 activations "
+                         "the scales cannot be folded into the unpacked weights")
+    if group_size > 0 and in_dtype == "int4_bf16" and group_size != 32:
+        raise ValueError(f"FlyDSL groupwise scale only supports group_size=32, got {group_size}. "
+                         "This is due to int4 preshuffle layout constraints.")
+    if in_dtype in _INT4_TO and w_layout != "preshuffle16x16":
+        raise ValueError("packed int4 weights are defined on the preshuffled order: w_layout must be 'preshuffle16x16'")
     if k_batch != 1:
         raise ValueError("split-K (k_batch > 1) is not built here: one CTA owns the whole K range of its tile")
     if tile_k % 64 != 0:
@@ -67,7 +90,7 @@ def _check(in_dtype, group_size, k_batch, tile_m, tile_k, model_dim, inter_dim, 
         raise ValueError(f"w_layout must be 'preshuffle16x16' or 'plain', got {w_layout!r}")
     if impl not in _IMPL:
         raise ValueError(f"impl must be one of {sorted(_IMPL)}, got {impl!r}")
-    if impl != "tcgen05" and in_dtype in ("fp16", "bf16"):
+    if impl != "tcgen05" and in_dtype in ("fp16", "bf16", "int4_bf16"):
         raise ValueError("16-bit operands are built for the tensor-core path only (impl='tcgen05')")
     if impl == "tcgen05" and tile_m not in _TILE_M:
         raise ValueError(f"tile_m must be one of {_TILE_M} for the tensor-core path, got {tile_m}")
@@ -82,13 +105,18 @@ def compile_moe_gemm1(*, model_dim: int, inter_dim: int, experts: int, topk: int
     if out_dtype not in ("f16", "bf16"):
         raise ValueError(f"out_dtype must be 'f16' or 'bf16', got {out_dtype!r}")
     _check(in_dtype, group_size, k_batch, tile_m, tile_k, model_dim, inter_dim, experts, topk, w_layout, impl)
-    if use_cshuffle_epilog is not None or scale_is_bf16:
-        logger.debug("stage 1: use_cshuffle_epilog / scale_is_bf16 do not apply here and are ignored")
+    if use_cshuffle_epilog is not None:
+        logger.debug("stage 1: use_cshuffle_epilog does not apply here and is ignored")
     impl_code = _IMPL[impl]
     in_code = _IN_CODE[in_dtype]
     in_torch = _IN_TORCH[in_dtype]
-    unscaled = in_dtype in ("fp16", "bf16")
-    ebytes = 2 if unscaled else 1
+    grouped = group_size > 0 and in_dtype == "int4_bf16"     # group-wise weight scales, folded in while unpacking
+    no_x_scale = in_dtype in ("fp16", "bf16", "int4_bf16")
+    no_w_scale = in_dtype in ("fp16", "bf16") or grouped
+    ebytes = 2 if no_x_scale else 1
+    int4_to = _INT4_TO.get(in_dtype)
+    w_torch = _PACKED_W if int4_to is not None else in_torch
+    gs_torch = (torch.bfloat16,) if scale_is_bf16 else (torch.float32,)
     out_torch = _OUT16[out_dtype]
     out_code = _lib.DTYPE_CODE[out_torch]
     by_pair = in_dtype == "int8smooth"          # x and scale_x indexed by t*topk + s
@@ -107,19 +135,23 @@ def compile_moe_gemm1(*, model_dim: int, inter_dim: int, experts: int, topk: int
         x_rows = pairs if by_pair else tokens
         _lib.require_cuda("arg_out", arg_out, (out_torch,), pairs * inter_dim)
         _lib.require_cuda("arg_x", arg_x, in_torch, x_rows * model_dim)
-        _lib.require_cuda("arg_w", arg_w, in_torch, wrows * model_dim)
-        if not unscaled:
+        _lib.require_cuda("arg_w", arg_w, w_torch, wrows * model_dim // (2 if int4_to is not None else 1))
+        if not no_x_scale:
             _lib.require_cuda("arg_scale_x", arg_scale_x, (torch.float32,), x_rows)
+        if not no_w_scale:
             _lib.require_cuda("arg_scale_w", arg_scale_w, (torch.float32,), wrows)
-        sx_ptr = 0 if unscaled else _lib.ptr(arg_scale_x)
-        sw_ptr = 0 if unscaled else _lib.ptr(arg_scale_w)
+        sx_ptr = 0 if no_x_scale else _lib.ptr(arg_scale_x)
+        sw_ptr = 0 if no_w_scale else _lib.ptr(arg_scale_w)
         _lib.require_cuda("arg_sorted_token_ids", arg_sorted_token_ids, (torch.int32,), max(0, cap_rows - tile_m + 1))
         _lib.require_cuda("arg_expert_ids", arg_expert_ids, (torch.int32,), blocks)
         _lib.require_cuda("arg_sorted_weights", arg_sorted_weights, (torch.float32,), max(0, cap_rows - tile_m + 1))
         _lib.require_cuda("arg_max_token_ids", arg_max_token_ids, (torch.int32,), 1)
         h = _lib.stream_handle(stream)
         lib = _lib.load()
-        w_plain = _plain_weight(arg_w, wrows, model_dim, w_layout, h)
+        if grouped:
+            _lib.require_cuda("arg_scale_w", arg_scale_w, gs_torch, wrows * (model_dim // 32))
+        w_plain = _plain_weight(arg_w, wrows, model_dim, w_layout, h, int4_to, arg_scale_w if grouped else None,
+                                2 * inter_dim)
         row_layout = _lib.ROWS_BY_PAIR if by_pair else _lib.ROWS_BY_TOKEN
         x_ptr, x_layout = _lib.ptr(arg_x), row_layout
         if impl_code == _lib.IMPL_TCGEN05 and tile_m > _GATHER_IN_KERNEL_MAX:
@@ -153,13 +185,18 @@ def compile_moe_gemm2(*, model_dim: int, inter_dim: int, experts: int, topk: int
     if (not bool(accumulate)) and out_is_f32:
         raise ValueError("compile_moe_gemm2(accumulate=False) only supports out_dtype in {'f16','bf16'}")
     _check(in_dtype, group_size, 1, tile_m, tile_k, model_dim, inter_dim, experts, topk, w_layout, impl)
-    if use_cshuffle_epilog is not None or scale_is_bf16:
-        logger.debug("stage 2: use_cshuffle_epilog / scale_is_bf16 do not apply here and are ignored")
+    if use_cshuffle_epilog is not None:
+        logger.debug("stage 2: use_cshuffle_epilog does not apply here and is ignored")
     impl_code = _IMPL[impl]
     in_code = _IN_CODE[in_dtype]
     in_torch = _IN_TORCH[in_dtype]
-    unscaled = in_dtype in ("fp16", "bf16")
-    ebytes = 2 if unscaled else 1
+    grouped = group_size > 0 and in_dtype == "int4_bf16"
+    no_x_scale = in_dtype in ("fp16", "bf16", "int4_bf16")
+    no_w_scale = in_dtype in ("fp16", "bf16") or grouped
+    ebytes = 2 if no_x_scale else 1
+    int4_to = _INT4_TO.get(in_dtype)
+    w_torch = _PACKED_W if int4_to is not None else in_torch
+    gs_torch = (torch.bfloat16,) if scale_is_bf16 else (torch.float32,)
     out_torch = torch.float32 if out_is_f32 else (torch.bfloat16 if out_is_bf16 else torch.float16)
     out_code = _lib.DTYPE_CODE[out_torch]
     wrows = experts * model_dim
@@ -178,19 +215,23 @@ def compile_moe_gemm2(*, model_dim: int, inter_dim: int, experts: int, topk: int
         out_rows = tokens if accumulate else pairs
         _lib.require_cuda("arg_out", arg_out, (out_torch,), out_rows * model_dim)
         _lib.require_cuda("arg_x", arg_x, in_torch, pairs * inter_dim)
-        _lib.require_cuda("arg_w", arg_w, in_torch, wrows * inter_dim)
-        if not unscaled:
+        _lib.require_cuda("arg_w", arg_w, w_torch, wrows * inter_dim // (2 if int4_to is not None else 1))
+        if not no_x_scale:
             _lib.require_cuda("arg_scale_x", arg_scale_x, (torch.float32,), pairs)
+        if not no_w_scale:
             _lib.require_cuda("arg_scale_w", arg_scale_w, (torch.float32,), wrows)
-        sx_ptr = 0 if unscaled else _lib.ptr(arg_scale_x)
-        sw_ptr = 0 if unscaled else _lib.ptr(arg_scale_w)
+        sx_ptr = 0 if no_x_scale else _lib.ptr(arg_scale_x)
+        sw_ptr = 0 if no_w_scale else _lib.ptr(arg_scale_w)
         _lib.require_cuda("arg_sorted_token_ids", arg_sorted_token_ids, (torch.int32,), max(0, cap_rows - tile_m + 1))
         _lib.require_cuda("arg_expert_ids", arg_expert_ids, (torch.int32,), blocks)
         _lib.require_cuda("arg_sorted_weights", arg_sorted_weights, (torch.float32,), max(0, cap_rows - tile_m + 1))
         _lib.require_cuda("arg_num_valid_ids", arg_num_valid_ids, (torch.int32,), 1)
         h = _lib.stream_handle(stream)
         lib = _lib.load()
-        w_plain = _plain_weight(arg_w, wrows, inter_dim, w_layout, h)
+        if grouped:
+            _lib.require_cuda("arg_scale_w", arg_scale_w, gs_torch, wrows * (inter_dim // 32))
+        w_plain = _plain_weight(arg_w, wrows, inter_dim, w_layout, h, int4_to, arg_scale_w if grouped else None,
+                                model_dim)
         a_ptr, a_layout = _lib.ptr(arg_x), _lib.ROWS_BY_PAIR
         if impl_code == _lib.IMPL_TCGEN05 and tile_m > _GATHER_IN_KERNEL_MAX:
             gbuf = _resolve_scratch(scratch, gather_buffer, "gather_buffer", arg_x.device, h,

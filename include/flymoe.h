@@ -316,6 +316,21 @@ int flymoe_shuffle_weight(const void* src, void* dst, int64_t rows, int cols, in
 int flymoe_shuffle_weight_elems(const void* src, void* dst, int64_t rows, int cols, int elem_bytes,
                                 int to_plain, void* stream);
 
+/* Unpacks the reference's packed-int4 weights (tests/kernels/test_moe_gemm.py:49-65: signed 4-bit
+ * values of the 16x16-preshuffled one-byte layout, eight per four bytes, b_i = (v_{i+4} << 4) | v_i)
+ * to row-major [rows, cols] I8 or BF16, which the per-token-scale stages take as their weight
+ * operand ("int4": W4A8 with int8 activations; "int4_bf16": W4A16 with bf16 activations).
+ * packed holds rows * cols / 2 bytes. */
+int flymoe_unpack_int4_weight(const void* packed, void* dst, int64_t rows, int cols, int out_dtype,
+                              void* stream);
+/* The same with group-wise weight scales folded in (W4A16 with group_size 32,
+ * kernels/moe_gemm_2stage.py:90-108 `group_size`; scale layout tests/utils.py:99-129): BF16 output
+ * = bf16(value * scale[e][k/32][n]), rows = E * rows_per_expert.  group_scale is F32 [E, cols/32,
+ * rows_per_expert] or BF16 [E, cols/64, rows_per_expert, 2]; null = no scaling. */
+int flymoe_unpack_int4_weight_grouped(const void* packed, void* dst, int64_t rows, int cols, int out_dtype,
+                                      const void* group_scale, int group_scale_dtype, int group_size,
+                                      int rows_per_expert, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -30,7 +30,8 @@ Reference locations each function follows (paths inside the reference project):
                   tests/kernels/test_ref.py:91-165 (stage 1), :168-239 (stage 2),
                   quantisation of its inputs tests/kernels/test_moe_gemm.py:446-450,
                   :463-488 (fp8, int8, per-(token, slot) "int8smooth"), :451-462 (fp16 / bf16:
-                  cast, no scales)
+                  cast, no scales), :489-499 (int4 weights: int8 values quantised to +-7, packed by
+                  :49-65 after the preshuffle; activations int8 or bf16)
 
 Differences from the reference text, all value-preserving: weights are
 dequantised one expert at a time (the reference expands every expert to fp32
@@ -258,19 +259,35 @@ def moe_layer(logits, xq, x_scale, w1q, w1_scale, w2q, w2_scale, topk: int,
 
 
 # --------------------------------------------------------------------------- per-token-scale family
-def quant_rows(x: torch.Tensor, quant_dtype=FP8):
-    """One scale per row of the last dim: (q, scale [..., 1]); int8 uses dtype max 127."""
-    dmax = 127.0 if quant_dtype == torch.int8 else None
+def quant_rows(x: torch.Tensor, quant_dtype=FP8, dtypeMax=None):
+    """One scale per row of the last dim: (q, scale [..., 1]); int8 uses dtype max 127, or ``dtypeMax``
+    (7 for the values that are packed to int4; the keyword is spelled as in tests/utils.py:35)."""
+    dmax = float(dtypeMax) if dtypeMax is not None else (127.0 if quant_dtype == torch.int8 else None)
     return pertoken_quant(x, quant_dtype=quant_dtype, dtype_max=dmax)
 
 
+def pack_int4_preshuffled(w_int8: torch.Tensor) -> torch.Tensor:
+    """[..., N, K] int8 values in [-8, 7] -> the packed bytes the int4 variants take (N*K/2 int8, flat):
+    the 16x16 preshuffle of the one-byte tensor, then every eight consecutive values v0..v7 become the four
+    bytes (v4<<4)|v0, (v5<<4)|v1, (v6<<4)|v2, (v7<<4)|v3 (tests/kernels/test_moe_gemm.py:49-65)."""
+    u = (shuffle_weight(w_int8).contiguous().view(-1).to(torch.int16) & 0xF).to(torch.uint8).view(-1, 8)
+    return (u[:, :4] | (u[:, 4:] << 4)).contiguous().view(-1).view(torch.int8)
+
+
+def _group_dequant(w_q: torch.Tensor, group_scale: torch.Tensor, group_size: int) -> torch.Tensor:
+    """w[n, k] * scale[k // group_size, n] for one expert (tests/kernels/test_ref.py:133-141)."""
+    return w_q.to(torch.float32) * group_scale.to(torch.float32).t().repeat_interleave(group_size, dim=1)
+
+
 def pertoken_stage1(x_q, scale_x, w1_q, scale_w1, topk_ids, topk_weights, inter_dim: int,
-                    doweight_stage1: bool = False):
+                    doweight_stage1: bool = False, group_size: int = -1, scale_w1_groups=None):
     """silu(x W1g^T) * (x W1u^T) with x = x_q * scale_x (per row) and W = w_q * scale_w (per row).
 
     x_q [T,K] (or [T,k,K] when every (token, slot) pair brings its own row) of e4m3/int8, scale_x
     [T,1] ([T,k,1]); w1_q [E,2I,K], scale_w1 [E,2I,1].  f16/bf16 operands come with ``None`` scales
-    (no dequantisation, tests/kernels/test_ref.py:57-69 of the reference).  Returns f32 [T,k,I]."""
+    (no dequantisation, tests/kernels/test_ref.py:57-69 of the reference).  ``group_size > 0``: the weights
+    are scaled per K group with ``scale_w1_groups`` [E, K/group_size, 2I] instead of per row.
+    Returns f32 [T,k,I]."""
     ids = torch.as_tensor(topk_ids).to(torch.int64)
     T, k = ids.shape
     E = w1_q.shape[0]
@@ -280,7 +297,10 @@ def pertoken_stage1(x_q, scale_x, w1_q, scale_w1, topk_ids, topk_weights, inter_
         tok, slot = (ids == e).nonzero(as_tuple=True)
         if tok.numel() == 0:
             continue
-        w = w1_q[e].to(torch.float32) if scale_w1 is None else w1_q[e].to(torch.float32) * scale_w1[e]
+        if group_size > 0 and scale_w1_groups is not None:
+            w = _group_dequant(w1_q[e], scale_w1_groups[e], group_size)
+        else:
+            w = w1_q[e].to(torch.float32) if scale_w1 is None else w1_q[e].to(torch.float32) * scale_w1[e]
         rows = x[tok] if x.dim() == 2 else x[tok, slot]
         y2 = F.linear(rows, w)
         y = F.silu(y2[:, :inter_dim]) * y2[:, inter_dim:]
@@ -291,7 +311,7 @@ def pertoken_stage1(x_q, scale_x, w1_q, scale_w1, topk_ids, topk_weights, inter_
 
 
 def pertoken_stage2(a2_q, scale_a2, w2_q, scale_w2, topk_ids, topk_weights, model_dim: int,
-                    doweight_stage2: bool = True, reduce: bool = True):
+                    doweight_stage2: bool = True, reduce: bool = True, group_size: int = -1, scale_w2_groups=None):
     """out[t] = sum_s (w[t,s]) * (a2[t,s] W2_e^T); a2_q [T,k,I] with scale_a2 [T,k,1], w2_q [E,H,I]
     with scale_w2 [E,H,1].  Returns f32 [T,H] (or [T,k,H] with ``reduce=False``)."""
     ids = torch.as_tensor(topk_ids).to(torch.int64)
@@ -303,7 +323,10 @@ def pertoken_stage2(a2_q, scale_a2, w2_q, scale_w2, topk_ids, topk_weights, mode
         tok, slot = (ids == e).nonzero(as_tuple=True)
         if tok.numel() == 0:
             continue
-        w = w2_q[e].to(torch.float32) if scale_w2 is None else w2_q[e].to(torch.float32) * scale_w2[e]
+        if group_size > 0 and scale_w2_groups is not None:
+            w = _group_dequant(w2_q[e], scale_w2_groups[e], group_size)      # scale_w2_groups [E, I/group_size, H]
+        else:
+            w = w2_q[e].to(torch.float32) if scale_w2 is None else w2_q[e].to(torch.float32) * scale_w2[e]
         y = F.linear(a2[tok, slot], w)
         if doweight_stage2:
             y = y * torch.as_tensor(topk_weights)[tok, slot].unsqueeze(-1)

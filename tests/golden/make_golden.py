@@ -231,27 +231,50 @@ def main() -> None:
     out = {}
     cases = [("fp8", 64, 256, 128, 4, 2, False), ("int8", 64, 256, 128, 4, 2, False),
              ("int8smooth", 33, 256, 128, 4, 2, False), ("fp8", 129, 512, 256, 8, 2, True),
-             ("bf16", 64, 256, 128, 4, 2, False), ("fp16", 40, 256, 128, 4, 2, True)]
+             ("bf16", 64, 256, 128, 4, 2, False), ("fp16", 40, 256, 128, 4, 2, True),
+             ("int4", 48, 256, 128, 4, 2, False), ("int4_bf16", 48, 256, 128, 4, 2, False),
+             ("int4_bf16_g32", 48, 256, 128, 4, 2, False)]
     half = {"fp16": torch.float16, "bf16": torch.bfloat16}
+    pack4 = lift(REF / "tests" / "kernels" / "test_moe_gemm.py", ["_pack_shuffled_int8_to_packed_int4_no_perm"],
+                 {"torch": torch})["_pack_shuffled_int8_to_packed_int4_no_perm"]
     for i, (in_dtype, T, H, I, E, k, doweight1) in enumerate(cases):
         qd = FP8 if in_dtype == "fp8" else torch.int8
+        grouped = in_dtype.endswith("_g32")      # W4A16 with one weight scale per 32-wide K group instead of per row
+        in_dtype = in_dtype[:-4] if grouped else in_dtype
         xq, sx, w1q, sw1, w2q, sw2, ti, tw = pertoken_inputs(in_dtype, T, H, I, E, k, 900 + i, pertoken_quant)
-        if in_dtype in half:          # no scales; the stage-2 input is stage 1's output in the same 16-bit type
+        if grouped:
+            gg = torch.Generator().manual_seed(7000 + i)         # test_moe_gemm.py:512-514 of the reference
+            g1 = torch.rand((E, H // 32, 2 * I), generator=gg) * 0.05 + 0.005
+            g2 = torch.rand((E, I // 32, H), generator=gg) * 0.05 + 0.005
+            o1 = pt["torch_moe_gemm1"](xq, w1q.view(E * 2 * I, H), None, None, ti, tw, I, doweight1, 32, g1)
+            a2q, sa2 = o1.to(torch.bfloat16), None
+            o2 = pt["torch_moe_gemm2"](a2q, w2q, None, None, ti, tw, H, not doweight1, 32, g2)
+            digest = sha(u8(xq), u8(w1q), u8(w2q), g1.numpy(), g2.numpy(), ti.numpy(), tw.numpy())
+            out[f"p{i}_group_seed"] = np.array([7000 + i], dtype=np.int32)
+        elif in_dtype in half:          # no scales; the stage-2 input is stage 1's output in the same 16-bit type
             o1 = pt["torch_moe_gemm1"](xq, w1q.view(E * 2 * I, H), None, None, ti, tw, I, doweight1)
             a2q, sa2 = o1.to(half[in_dtype]), None
             o2 = pt["torch_moe_gemm2"](a2q, w2q, None, None, ti, tw, H, not doweight1)
             digest = sha(u8(xq), u8(w1q), u8(w2q), ti.numpy(), tw.numpy())
+        elif in_dtype == "int4_bf16":  # W4A16: bf16 activations without scales, int8 weight values with row scales
+            o1 = pt["torch_moe_gemm1"](xq, w1q.view(E * 2 * I, H), None, sw1.view(E * 2 * I, 1), ti, tw, I, doweight1)
+            a2q, sa2 = o1.to(torch.bfloat16), None
+            o2 = pt["torch_moe_gemm2"](a2q, w2q, None, sw2.view(E, H, 1), ti, tw, H, not doweight1)
+            digest = sha(u8(xq), u8(w1q), sw1.numpy(), u8(w2q), sw2.numpy(), ti.numpy(), tw.numpy())
         else:
             o1 = pt["torch_moe_gemm1"](xq, w1q.view(E * 2 * I, H), sx, sw1.view(E * 2 * I, 1), ti, tw, I, doweight1)
             a2q, sa2 = pertoken_quant(o1, quant_dtype=qd)
             o2 = pt["torch_moe_gemm2"](a2q, w2q, sa2, sw2.view(E, H, 1), ti, tw, H, not doweight1)
             digest = sha(u8(xq), sx.numpy(), u8(w1q), sw1.numpy(), u8(w2q), sw2.numpy(), ti.numpy(), tw.numpy())
         out.update({f"p{i}_cfg": np.array([T, H, I, E, k, int(doweight1), 900 + i], dtype=np.int32),
-                    f"p{i}_dtype": np.array([in_dtype]),
+                    f"p{i}_dtype": np.array([in_dtype]), f"p{i}_grouped": np.array([int(grouped)], dtype=np.int32),
                     f"p{i}_input_sha": np.array([digest]),
                     f"p{i}_out1": o1.numpy(), f"p{i}_a2q": u8(a2q), f"p{i}_out2": o2.numpy()})
         if sa2 is not None:
             out[f"p{i}_sa2"] = sa2.numpy()
+        if in_dtype in ("int4", "int4_bf16"):   # the bytes the kernels receive: the reference's shuffle, then its packer
+            out[f"p{i}_w1_packed"] = u8(pack4(shuffle_weight(w1q.clone(), layout=(16, 16)).view(E * 2 * I, H)))
+            out[f"p{i}_w2_packed"] = u8(pack4(shuffle_weight(w2q.clone(), layout=(16, 16)).view(E * H, I)))
         if i == 0:     # the first case also carries its inputs; the others are regenerated from their seeds
             out.update({f"p{i}_xq": u8(xq), f"p{i}_sx": sx.numpy(), f"p{i}_w1q": u8(w1q), f"p{i}_sw1": sw1.numpy(),
                         f"p{i}_w2q": u8(w2q), f"p{i}_sw2": sw2.numpy(), f"p{i}_ids": ti.numpy(), f"p{i}_tw": tw.numpy()})

@@ -56,7 +56,9 @@ def pertoken_inputs(in_dtype, T, H, I, E, k, seed, quant):
     (tests/kernels/test_moe_gemm.py:380-400, :446-488 in the reference project): randn activations,
     randn/10 weights, routing = top-k of a softmax of random scores.  ``quant(x, quant_dtype=...)`` is
     the row quantiser (the reference's own when the fixtures are generated, the oracle's in the tests).
-    "fp16" / "bf16" cast instead of quantising and have ``None`` scales (:451-462 there).
+    "fp16" / "bf16" cast instead of quantising and have ``None`` scales (:451-462 there); "int4" / "int4_bf16"
+    quantise the weights to int8 values in [-7, 7] (``dtypeMax=7``, :489-499; returned unpacked) with int8
+    per-token or bf16 unscaled activations.
     Returns xq ([T,H], or [T,k,H] for "int8smooth"), sx, w1q [E,2I,H], sw1, w2q [E,H,I], sw2, ids, weights."""
     g = torch.Generator().manual_seed(seed)
     qd = FP8 if in_dtype == "fp8" else torch.int8
@@ -69,6 +71,14 @@ def pertoken_inputs(in_dtype, T, H, I, E, k, seed, quant):
     if in_dtype in ("fp16", "bf16"):
         dt = torch.float16 if in_dtype == "fp16" else torch.bfloat16
         return x.to(dt), None, w1.to(dt), None, w2.to(dt), None, ti.to(torch.int32), tw
+    if in_dtype in ("int4", "int4_bf16"):
+        if in_dtype == "int4":
+            xq, sx = quant(x, quant_dtype=torch.int8)
+        else:
+            xq, sx = x.to(torch.bfloat16), None
+        w1q, sw1 = quant(w1, quant_dtype=torch.int8, dtypeMax=7)
+        w2q, sw2 = quant(w2, quant_dtype=torch.int8, dtypeMax=7)
+        return xq, sx, w1q, sw1, w2q, sw2, ti.to(torch.int32), tw
     if in_dtype == "int8smooth":
         smooth = 0.75 + 0.5 * torch.rand((E, H), generator=g)
         xr = x[:, None, :] * smooth[ti.to(torch.int64)]
@@ -81,3 +91,12 @@ def pertoken_inputs(in_dtype, T, H, I, E, k, seed, quant):
     w1q, sw1 = quant(w1, quant_dtype=qd)
     w2q, sw2 = quant(w2, quant_dtype=qd)
     return xq, sx, w1q, sw1, w2q, sw2, ti.to(torch.int32), tw
+
+
+def group_scales(E, H, I, seed):
+    """Group-wise weight scales of the W4A16 variant (one per 32-wide K group and weight row), as the reference's
+    test draws them (tests/kernels/test_moe_gemm.py:512-514 there): f32 [E, H/32, 2I] and [E, I/32, H]."""
+    g = torch.Generator().manual_seed(seed)
+    g1 = torch.rand((E, H // 32, 2 * I), generator=g) * 0.05 + 0.005
+    g2 = torch.rand((E, I // 32, H), generator=g) * 0.05 + 0.005
+    return g1, g2

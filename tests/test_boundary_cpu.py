@@ -126,9 +126,14 @@ def test_dense_blockscale_gemm_argument_rules():
 
 def test_pertoken_builder_rules(lib):
     base = dict(model_dim=256, inter_dim=128, experts=4, topk=2, tile_m=16, tile_n=64, tile_k=128)
-    for bad in ("int4", "int4_bf16"):
-        with pytest.raises(ValueError, match="not built"):
-            pt.compile_moe_gemm1(doweight_stage1=False, in_dtype=bad, **base)
+    with pytest.raises(ValueError, match="group-wise"):
+        pt.compile_moe_gemm1(doweight_stage1=False, in_dtype="int4", group_size=32, **base)
+    with pytest.raises(ValueError, match="only supports group_size=32"):
+        pt.compile_moe_gemm1(doweight_stage1=False, in_dtype="int4_bf16", group_size=64, **base)
+    assert callable(pt.compile_moe_gemm1(doweight_stage1=False, in_dtype="int4_bf16", group_size=32, **base))
+    with pytest.raises(ValueError, match="preshuffled order"):
+        pt.compile_moe_gemm1(doweight_stage1=False, in_dtype="int4", w_layout="plain", **base)
+    assert callable(pt.compile_moe_gemm2(doweight_stage2=True, in_dtype="int4", **base))
     with pytest.raises(ValueError, match="tensor-core path only"):
         pt.compile_moe_gemm1(doweight_stage1=False, in_dtype="bf16", impl="simt", **base)
     assert callable(pt.compile_moe_gemm1(doweight_stage1=False, in_dtype="fp16", **base))

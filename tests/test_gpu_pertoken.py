@@ -52,8 +52,10 @@ def scale_arg(s):
     return torch.empty(0, dtype=torch.float32, device="cuda") if s is None else s.cuda().view(-1)
 
 
-def dev_weight(wq, layout):
+def dev_weight(wq, layout, in_dtype="fp8"):
     E, N, K = wq.shape
+    if in_dtype in ("int4", "int4_bf16"):          # the reference's packed bytes (preshuffled order only)
+        return orc.pack_int4_preshuffled(wq).cuda()
     w = wq.cuda()
     return w if layout == "plain" else shuffle_weight(w, E * N, K).view(-1)
 
@@ -67,7 +69,7 @@ def run_stage1(shape, in_dtype, out_dtype, impl, w_layout, doweight):
                                impl=impl)
     dt = {"f16": torch.float16, "bf16": torch.bfloat16}[out_dtype]
     out = torch.full((T * k + 16, I), 77.0, dtype=dt, device="cuda")
-    exe(out.view(-1)[: T * k * I], xq.cuda().view(-1, H), dev_weight(w1q, w_layout), scale_arg(sx),
+    exe(out.view(-1)[: T * k * I], xq.cuda().view(-1, H), dev_weight(w1q, w_layout, in_dtype), scale_arg(sx),
         scale_arg(sw1), s_ids, s_e, s_w, nv, T, I, H, nblk, torch.cuda.current_stream())
     torch.cuda.synchronize()
     assert bool((out[T * k:] == 77.0).all()), "stage 1 wrote past its output rows"
@@ -94,12 +96,15 @@ def run_stage2(shape, in_dtype, out_dtype, impl, w_layout, mode, doweight=True):
     xq, sx, w1q, sw1, w2q, sw2, ids, tw = inputs(shape, in_dtype)
     qd = hp.FP8 if in_dtype == "fp8" else torch.int8
     o1 = orc.pertoken_stage1(xq, sx, w1q, sw1, ids, tw, I, False)
-    a2q, sa2 = (o1.to(HALF[in_dtype]), None) if in_dtype in HALF else orc.quant_rows(o1, qd)
+    if in_dtype in HALF or in_dtype == "int4_bf16":
+        a2q, sa2 = o1.to(HALF.get(in_dtype, torch.bfloat16)), None
+    else:
+        a2q, sa2 = orc.quant_rows(o1, qd)
     s_ids, s_w, s_e, nv, nblk = sort(ids, tw, E, tile_m)
     common = dict(model_dim=H, inter_dim=I, experts=E, topk=k, tile_m=tile_m, tile_n=256, tile_k=128,
                   doweight_stage2=doweight, in_dtype=in_dtype, out_dtype=out_dtype, w_layout=w_layout, impl=impl)
     dt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}[out_dtype]
-    w = dev_weight(w2q, w_layout)
+    w = dev_weight(w2q, w_layout, in_dtype)
     args = (a2q.cuda().view(-1, I), w, scale_arg(sa2), scale_arg(sw2), s_ids, s_e, s_w, nv, T, H, I, nblk)
     if mode == "rows":
         exe = pt.compile_moe_gemm2(accumulate=False, **common)
@@ -165,6 +170,89 @@ def test_pertoken_stage2_16bit_operands(shape, in_dtype, out_dtype, w_layout, mo
     assert_close(out, ref, RTOL, ATOL + step, f"16-bit stage 2 {shape} {in_dtype} {mode}")
     if out_dtype == "f32":
         assert_close(out, ref, 1e-4, 1e-5 * pair_peak, f"16-bit stage 2 tight {shape} {in_dtype}")
+
+
+@pytest.mark.parametrize("shape,in_dtype,out_dtype,doweight", [
+    ("S", "int4", "f16", False), ("S", "int4_bf16", "bf16", True), ("M", "int4", "bf16", True),
+    ("M", "int4_bf16", "f16", False), ("T128", "int4", "bf16", False), ("T128", "int4_bf16", "bf16", False),
+])
+def test_pertoken_stage1_packed_int4_weights(shape, in_dtype, out_dtype, doweight):
+    """W4A8 / W4A16 (tests/kernels/test_moe_gemm.py:489-499 of the reference): the weights arrive as its packed
+    int4 bytes; the launcher unpacks them once and runs the int8 / bf16 kernels."""
+    out, ref = run_stage1(shape, in_dtype, out_dtype, "tcgen05", "preshuffle16x16", doweight)
+    assert_close(out, ref, RTOL, ATOL, f"int4 stage 1 {shape} {in_dtype}")
+    eps = 2.0 ** -8 if out_dtype == "bf16" else 2.0 ** -11
+    assert_close(out, ref, 2 * eps, 1e-3, f"int4 stage 1 tight {shape} {in_dtype}")
+
+
+@pytest.mark.parametrize("shape,in_dtype,out_dtype,mode", [
+    ("S", "int4", "f32", "atomic"), ("S", "int4_bf16", "f32", "atomic"), ("M", "int4", "bf16", "reduce"),
+    ("M", "int4_bf16", "f16", "rows"), ("T128", "int4", "f32", "atomic"), ("T128", "int4_bf16", "bf16", "reduce"),
+])
+def test_pertoken_stage2_packed_int4_weights(shape, in_dtype, out_dtype, mode):
+    out, ref, pair_peak = run_stage2(shape, in_dtype, out_dtype, "tcgen05", "preshuffle16x16", mode)
+    step = 0.0 if out_dtype == "f32" or mode == "rows" else 2.0 ** (-7 if out_dtype == "bf16" else -10) * pair_peak
+    assert_close(out, ref, RTOL, ATOL + step, f"int4 stage 2 {shape} {in_dtype} {mode}")
+    if out_dtype == "f32":
+        assert_close(out, ref, 1e-4, 1e-5 * pair_peak, f"int4 stage 2 tight {shape} {in_dtype}")
+
+
+@pytest.mark.parametrize("shape,scale_is_bf16", [("S", False), ("M", True), ("T128", False)])
+def test_pertoken_groupwise_int4_weights(shape, scale_is_bf16):
+    """W4A16 with one weight scale per 32-wide K group (group_size=32; the reference's layouts: f32 [E, K/32, N],
+    or bf16 [E, K/64, N, 2] from tests/utils.py:99-129): both stages against the oracle's group-wise dequantisation.
+    The scales are folded into the bf16 weights while unpacking, hence one bf16 rounding per weight on top of
+    the reference's fp32 dequantisation -- far inside the bar."""
+    T, H, I, E, k, tile_m = SHAPES[shape]
+    xq, _, w1q, _, w2q, _, ids, tw = inputs(shape, "int4_bf16")
+    g1, g2 = hp.group_scales(E, H, I, 4242)
+    if scale_is_bf16:
+        g1, g2 = g1.to(torch.bfloat16), g2.to(torch.bfloat16)
+
+    def prepared(gs):          # the layout the launcher takes
+        if gs.dtype == torch.bfloat16:
+            e, g, n = gs.shape
+            gs = gs.view(e, g // 2, 2, n).permute(0, 1, 3, 2)
+        return gs.contiguous().cuda().view(-1)
+    s_ids, s_w, s_e, nv, nblk = sort(ids, tw, E, tile_m)
+    common = dict(model_dim=H, inter_dim=I, experts=E, topk=k, tile_m=tile_m, tile_n=128, tile_k=128,
+                  in_dtype="int4_bf16", group_size=32, scale_is_bf16=scale_is_bf16)
+    none = scale_arg(None)
+    out1 = torch.zeros((T * k, I), dtype=torch.bfloat16, device="cuda")
+    pt.compile_moe_gemm1(doweight_stage1=False, out_dtype="bf16", **common)(
+        out1.view(-1), xq.cuda(), dev_weight(w1q, "preshuffle16x16", "int4_bf16"), none, prepared(g1),
+        s_ids, s_e, s_w, nv, T, I, H, nblk)
+    ref1 = orc.pertoken_stage1(xq, None, w1q, None, ids, tw, I, False, group_size=32, scale_w1_groups=g1.float())
+    assert_close(out1.cpu().view(T, k, I), ref1, RTOL, ATOL, f"group-wise stage 1 {shape}")
+    a2 = ref1.to(torch.bfloat16)
+    out2 = torch.zeros((T, H), dtype=torch.float32, device="cuda")
+    pt.compile_moe_gemm2(doweight_stage2=True, out_dtype="f32", **common)(
+        out2.view(-1), a2.cuda().view(-1, I), dev_weight(w2q, "preshuffle16x16", "int4_bf16"), none, prepared(g2),
+        s_ids, s_e, s_w, nv, T, H, I, nblk)
+    torch.cuda.synchronize()
+    ref2 = orc.pertoken_stage2(a2, None, w2q, None, ids, tw, H, True, group_size=32, scale_w2_groups=g2.float())
+    assert_close(out2.cpu(), ref2, RTOL, ATOL, f"group-wise stage 2 {shape}")
+
+
+def test_int4_unpack_matches_reference_packing():
+    """flymoe_unpack_int4_weight inverts the reference's shuffle + packer (bytes stored in the fixture)."""
+    from flydsl_b200.kernels.moe_blockscale_2stage import unpack_int4_weight
+    g = hp.load("moe_pertoken.npz")
+    seen = 0
+    for i in range(int(g["n"][0])):
+        in_dtype = str(g[f"p{i}_dtype"][0])
+        if in_dtype not in ("int4", "int4_bf16"):
+            continue
+        seen += 1
+        T, H, I, E, k, _, seed = (int(v) for v in g[f"p{i}_cfg"])
+        _, _, w1q, _, w2q, _, _, _ = hp.pertoken_inputs(in_dtype, T, H, I, E, k, seed, orc.quant_rows)
+        for wq, key, rows, cols in ((w1q, "w1_packed", E * 2 * I, H), (w2q, "w2_packed", E * H, I)):
+            packed = torch.from_numpy(g[f"p{i}_{key}"]).cuda()
+            as_i8 = unpack_int4_weight(packed, rows, cols, torch.int8)
+            assert torch.equal(as_i8.cpu().view(rows, cols), wq.view(rows, cols))
+            as_bf = unpack_int4_weight(packed, rows, cols, torch.bfloat16)
+            assert torch.equal(as_bf.cpu().float().view(rows, cols), wq.view(rows, cols).float())
+    assert seen == 2
 
 
 def test_pertoken_16bit_golden_fixture():

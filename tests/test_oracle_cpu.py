@@ -131,15 +131,25 @@ def test_pertoken_family_matches_reference_functions():
         in_dtype = str(g[f"p{i}_dtype"][0])
         qd = hp.FP8 if in_dtype == "fp8" else torch.int8
         half = {"fp16": torch.float16, "bf16": torch.bfloat16}.get(in_dtype)
+        grouped = bool(int(g[f"p{i}_grouped"][0]))
         xq, sx, w1q, sw1, w2q, sw2, ids, tw = hp.pertoken_inputs(in_dtype, T, H, I, E, k, seed, orc.quant_rows)
-        if half is not None:
+        gkw1, gkw2 = {}, {}
+        if grouped:
+            g1, g2 = hp.group_scales(E, H, I, int(g[f"p{i}_group_seed"][0]))
+            got_sha = hp.sha(hp.u8(xq), hp.u8(w1q), hp.u8(w2q), g1.numpy(), g2.numpy(), ids.numpy(), tw.numpy())
+            half, sw1, sw2 = torch.bfloat16, None, None
+            gkw1, gkw2 = dict(group_size=32, scale_w1_groups=g1), dict(group_size=32, scale_w2_groups=g2)
+        elif half is not None:
             got_sha = hp.sha(hp.u8(xq), hp.u8(w1q), hp.u8(w2q), ids.numpy(), tw.numpy())
+        elif in_dtype == "int4_bf16":
+            got_sha = hp.sha(hp.u8(xq), hp.u8(w1q), sw1.numpy(), hp.u8(w2q), sw2.numpy(), ids.numpy(), tw.numpy())
+            half = torch.bfloat16                  # its stage-2 input is the bf16 cast of stage 1, too
         else:
             got_sha = hp.sha(hp.u8(xq), sx.numpy(), hp.u8(w1q), sw1.numpy(), hp.u8(w2q), sw2.numpy(), ids.numpy(), tw.numpy())
         assert got_sha == str(g[f"p{i}_input_sha"][0]), f"case {i}: regenerated inputs differ from the fixture's"
         if i == 0:
             assert np.array_equal(hp.u8(xq), g["p0_xq"]) and np.array_equal(sw1.numpy(), g["p0_sw1"])
-        o1 = orc.pertoken_stage1(xq, sx, w1q, sw1, ids, tw, I, bool(doweight1))
+        o1 = orc.pertoken_stage1(xq, sx, w1q, sw1, ids, tw, I, bool(doweight1), **gkw1)
         ref1 = torch.from_numpy(g[f"p{i}_out1"])
         assert torch.allclose(o1, ref1, rtol=1e-5, atol=1e-5 * float(ref1.abs().max())), f"case {i} stage 1"
         if half is not None:
@@ -148,6 +158,10 @@ def test_pertoken_family_matches_reference_functions():
         else:
             a2q, sa2 = orc.quant_rows(ref1, qd)
             assert np.array_equal(hp.u8(a2q), g[f"p{i}_a2q"]) and np.array_equal(sa2.numpy(), g[f"p{i}_sa2"])
-        o2 = orc.pertoken_stage2(a2q, sa2, w2q, sw2, ids, tw, H, not bool(doweight1))
+        o2 = orc.pertoken_stage2(a2q, sa2, w2q, sw2, ids, tw, H, not bool(doweight1), **gkw2)
         ref2 = torch.from_numpy(g[f"p{i}_out2"])
         assert torch.allclose(o2, ref2, rtol=1e-5, atol=1e-5 * float(ref2.abs().max())), f"case {i} stage 2"
+        if in_dtype in ("int4", "int4_bf16"):      # the oracle's packer against the reference's shuffle + packer
+            assert int(w1q.abs().max()) <= 7
+            assert np.array_equal(hp.u8(orc.pack_int4_preshuffled(w1q)), g[f"p{i}_w1_packed"])
+            assert np.array_equal(hp.u8(orc.pack_int4_preshuffled(w2q)), g[f"p{i}_w2_packed"])
