@@ -21,7 +21,7 @@ LIB_PATH = Path(os.environ.get("FLYMOE_LIB", Path(__file__).resolve().parent / L
 F32, F16, BF16, E4M3, I8 = 0, 1, 2, 3, 4
 SCALE_BLOCK128, SCALE_PER_TOKEN = 0, 1
 STATUS_DISPATCH_OVERFLOW, STATUS_ROW_DST_MISALIGNED, STATUS_SELFTEST_TIMEOUT = 16, 17, 99
-ROWS_BY_TOKEN, ROWS_BY_PAIR, ROWS_SORTED = 0, 1, 2
+ROWS_BY_TOKEN, ROWS_BY_PAIR, ROWS_SORTED, ROWS_BY_SLOT = 0, 1, 2, 3
 IMPL_TCGEN05, IMPL_SIMT = 0, 1
 
 DTYPE_CODE = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16,

@@ -21,7 +21,8 @@ gather_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
     const int t = id_token(id), s = id_slot(id);
     uint4* d = dst + size_t(r) * row_vec;
     if (t < num_tokens && s < topk) {
-      const size_t srow = (src_layout == FLYMOE_ROWS_BY_TOKEN) ? size_t(t) : size_t(t) * topk + s;
+      const size_t srow = src_layout == FLYMOE_ROWS_BY_TOKEN ? size_t(t)
+                        : src_layout == FLYMOE_ROWS_BY_SLOT ? size_t(s) * num_tokens + t : size_t(t) * topk + s;
       const uint4* p = src + srow * row_vec;
       for (int i = lane; i < row_vec; i += 32) d[i] = __ldg(p + i);
     } else {
@@ -263,8 +264,9 @@ extern "C" int flymoe_gather_rows(const void* src, void* dst, const int32_t* sor
   FLYMOE_REQUIRE(src && dst && sorted_ids && num_valid_ids, "gather_rows: null pointer");
   FLYMOE_REQUIRE(row_bytes > 0 && row_bytes % 16 == 0, "gather_rows: row_bytes must be a multiple of 16");
   FLYMOE_REQUIRE(aligned16(src) && aligned16(dst), "gather_rows: pointers must be 16-byte aligned");
-  FLYMOE_REQUIRE(src_layout == FLYMOE_ROWS_BY_TOKEN || src_layout == FLYMOE_ROWS_BY_PAIR,
-                 "gather_rows: src_layout must be BY_TOKEN or BY_PAIR");
+  FLYMOE_REQUIRE(src_layout == FLYMOE_ROWS_BY_TOKEN || src_layout == FLYMOE_ROWS_BY_PAIR ||
+                     src_layout == FLYMOE_ROWS_BY_SLOT,
+                 "gather_rows: src_layout must be BY_TOKEN, BY_PAIR or BY_SLOT");
   if (max_rows <= 0) return FLYMOE_OK;
   const int blocks = std::min(ceil_div(max_rows, 8), sm_count() * 8);
   gather_rows_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(

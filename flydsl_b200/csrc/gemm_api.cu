@@ -5,14 +5,14 @@
 using namespace flymoe;
 
 static bool layout_ok(int l) {
-  return l == FLYMOE_ROWS_BY_TOKEN || l == FLYMOE_ROWS_BY_PAIR || l == FLYMOE_ROWS_SORTED;
+  return l == FLYMOE_ROWS_BY_TOKEN || l == FLYMOE_ROWS_BY_PAIR || l == FLYMOE_ROWS_SORTED || l == FLYMOE_ROWS_BY_SLOT;
 }
 
 static bool is_half(int dtype) { return dtype == FLYMOE_F16 || dtype == FLYMOE_BF16; }
 
 static long long layout_rows(int layout, int num_tokens, int topk, int size_expert_ids, int tile_m) {
   if (layout == FLYMOE_ROWS_BY_TOKEN) return num_tokens;
-  if (layout == FLYMOE_ROWS_BY_PAIR) return (long long)num_tokens * topk;
+  if (layout == FLYMOE_ROWS_BY_PAIR || layout == FLYMOE_ROWS_BY_SLOT) return (long long)num_tokens * topk;
   return (long long)size_expert_ids * tile_m;
 }
 
@@ -34,10 +34,12 @@ static int gemm1_impl(void* out, float* out_scale, int64_t out_scale_stride, con
   FLYMOE_REQUIRE(in_dtype == FLYMOE_E4M3 || ((in_dtype == FLYMOE_I8 || is_half(in_dtype)) && per_token),
                  "gemm1: in_dtype must be E4M3 or (per-token scaling only) I8, F16, BF16");
   FLYMOE_REQUIRE(!is_half(in_dtype) || impl == FLYMOE_IMPL_TCGEN05, "gemm1: 16-bit operands need the tcgen05 kernel");
-  FLYMOE_REQUIRE(layout_ok(x_layout) && (x_layout != FLYMOE_ROWS_BY_PAIR || per_token),
-                 "gemm1: x_layout must be BY_TOKEN or SORTED (BY_PAIR with per-token scaling)");
-  FLYMOE_REQUIRE(layout_ok(x_scale_layout) && (x_scale_layout != FLYMOE_ROWS_BY_PAIR || per_token),
-                 "gemm1: x_scale_layout must be BY_TOKEN or SORTED (BY_PAIR with per-token scaling)");
+  const bool x_per_pair = x_layout == FLYMOE_ROWS_BY_PAIR || x_layout == FLYMOE_ROWS_BY_SLOT;
+  const bool sx_per_pair = x_scale_layout == FLYMOE_ROWS_BY_PAIR || x_scale_layout == FLYMOE_ROWS_BY_SLOT;
+  FLYMOE_REQUIRE(layout_ok(x_layout) && (!x_per_pair || per_token),
+                 "gemm1: x_layout must be BY_TOKEN or SORTED (BY_PAIR / BY_SLOT with per-token scaling)");
+  FLYMOE_REQUIRE(layout_ok(x_scale_layout) && (!sx_per_pair || per_token),
+                 "gemm1: x_scale_layout must be BY_TOKEN or SORTED (BY_PAIR / BY_SLOT with per-token scaling)");
   FLYMOE_REQUIRE(out_layout == FLYMOE_ROWS_BY_PAIR || out_layout == FLYMOE_ROWS_SORTED,
                  "gemm1: out_layout must be BY_PAIR or SORTED");
   if (num_tokens == 0 || size_expert_ids == 0) return FLYMOE_OK;

@@ -16,9 +16,10 @@ __device__ __forceinline__ void cvt16(const uint4& v, float* f, bool int8_ops) {
   for (int i = 0; i < 16; ++i) f[i] = int8_ops ? float(int(static_cast<int8_t>(b[i]))) : fp8_e4m3_to_float(b[i]);
 }
 
-__device__ __forceinline__ long long src_row(int layout, int r, int t, int s, int topk) {
+__device__ __forceinline__ long long src_row(int layout, int r, int t, int s, int topk, int num_tokens) {
   if (layout == FLYMOE_ROWS_BY_TOKEN) return t;
   if (layout == FLYMOE_ROWS_BY_PAIR) return (long long)t * topk + s;
+  if (layout == FLYMOE_ROWS_BY_SLOT) return (long long)s * num_tokens + t;
   return r;
 }
 
@@ -67,8 +68,8 @@ moe_gemm_simt_kernel(GemmArgs a) {
         rt[i] = id_token(id); rs[i] = id_slot(id);
         rok[i] = rt[i] < a.num_tokens && rs[i] < a.topk;
         if (rok[i]) {
-          srow[i] = src_row(a.a_layout, r, rt[i], rs[i], a.topk);
-          sidx[i] = src_row(a.a_scale_layout, r, rt[i], rs[i], a.topk);
+          srow[i] = src_row(a.a_layout, r, rt[i], rs[i], a.topk, a.num_tokens);
+          sidx[i] = src_row(a.a_scale_layout, r, rt[i], rs[i], a.topk, a.num_tokens);
         }
       }
     }

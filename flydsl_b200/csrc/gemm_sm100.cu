@@ -547,7 +547,9 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           const int id = (row < a.tile_m && r < valid_rows) ? __ldg(a.sorted_ids + r) : pad_id;
           const int tok = id_token(id), slot = id_slot(id);
           const bool valid = tok < a.num_tokens && slot < a.topk;
-          const long long srow = a.a_layout == FLYMOE_ROWS_BY_TOKEN ? (long long)tok : (long long)tok * a.topk + slot;
+          const long long srow = a.a_layout == FLYMOE_ROWS_BY_TOKEN ? (long long)tok
+                               : a.a_layout == FLYMOE_ROWS_BY_SLOT ? (long long)slot * a.num_tokens + tok
+                                                                   : (long long)tok * a.topk + slot;
           src[j] = a.a + (valid ? srow : 0) * a.k_dim;
           nbytes[j] = valid ? 16u : 0u;
         }
@@ -617,6 +619,7 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       if (valid) {
         sidx = a.a_scale_layout == FLYMOE_ROWS_BY_TOKEN ? (long long)tok
              : a.a_scale_layout == FLYMOE_ROWS_BY_PAIR ? (long long)tok * a.topk + slot : (long long)r;
+        if (SCALING == kScalePerToken && a.a_scale_layout == FLYMOE_ROWS_BY_SLOT) sidx = (long long)slot * a.num_tokens + tok;
       }
       // stage 2: a warpgroup whose 128 columns lie beyond n_dim (last tile of a row) has nothing to do
       const bool half_ok = STAGE == 1 ? true : (n * BN + wg * 128 < a.n_dim);
@@ -983,7 +986,8 @@ int launch_gemm_sm100(int stage, const GemmArgs& a, cudaStream_t stream) {
     set_last_error_msg("tcgen05 GEMM: tile_m must be 16, 32, 64 or 128");
     return FLYMOE_ERR_UNSUPPORTED;
   }
-  if (a.a_layout != FLYMOE_ROWS_SORTED && a.a_layout != FLYMOE_ROWS_BY_TOKEN && a.a_layout != FLYMOE_ROWS_BY_PAIR) {
+  if (a.a_layout != FLYMOE_ROWS_SORTED && a.a_layout != FLYMOE_ROWS_BY_TOKEN && a.a_layout != FLYMOE_ROWS_BY_PAIR &&
+      a.a_layout != FLYMOE_ROWS_BY_SLOT) {
     set_last_error_msg("tcgen05 GEMM: unknown activation row layout");
     return FLYMOE_ERR_UNSUPPORTED;
   }

@@ -12,7 +12,7 @@ Data contract (the reference's, tests/kernels/test_moe_gemm.py:446-450, :548-579
 ``in_dtype="fp8"``: x e4m3 [tokens, K] with ONE fp32 scale per token ([tokens]); weights e4m3
 [E, N, K] with ONE fp32 scale per weight row ([E*N]).  ``"int8"``: the same with signed 8-bit
 operands (exact int32 accumulation).  ``"int8smooth"``: x and its scales are given per (token,
-slot) pair ([tokens*topk, K], [tokens*topk]).  Stage 1 writes ``silu(gate)*up`` to row
+slot) pair in slot-major order ([topk*tokens, K], [topk*tokens]: row ``slot*tokens + token``, :546-555).  Stage 1 writes ``silu(gate)*up`` to row
 ``t*topk + s`` of a [tokens, topk, inter] f16/bf16 tensor; stage 2 reads that layout (e4m3/int8
 plus one scale per row) and accumulates ``sorted_weight * (a2 . W2^T)`` into ``out[t]``
 (pre-zeroed; f16/bf16/f32) or, with ``accumulate=False``, stores per-pair rows.
@@ -119,7 +119,7 @@ def compile_moe_gemm1(*, model_dim: int, inter_dim: int, experts: int, topk: int
     gs_torch = (torch.bfloat16,) if scale_is_bf16 else (torch.float32,)
     out_torch = _OUT16[out_dtype]
     out_code = _lib.DTYPE_CODE[out_torch]
-    by_pair = in_dtype == "int8smooth"          # x and scale_x indexed by t*topk + s
+    by_pair = in_dtype == "int8smooth"          # x and scale_x per (token, slot), slot-major: row s*tokens + t
     wrows = experts * 2 * inter_dim
     scratch = _LauncherScratch(torch.uint8)
 
@@ -152,7 +152,7 @@ def compile_moe_gemm1(*, model_dim: int, inter_dim: int, experts: int, topk: int
             _lib.require_cuda("arg_scale_w", arg_scale_w, gs_torch, wrows * (model_dim // 32))
         w_plain = _plain_weight(arg_w, wrows, model_dim, w_layout, h, int4_to, arg_scale_w if grouped else None,
                                 2 * inter_dim)
-        row_layout = _lib.ROWS_BY_PAIR if by_pair else _lib.ROWS_BY_TOKEN
+        row_layout = _lib.ROWS_BY_SLOT if by_pair else _lib.ROWS_BY_TOKEN
         x_ptr, x_layout = _lib.ptr(arg_x), row_layout
         if impl_code == _lib.IMPL_TCGEN05 and tile_m > _GATHER_IN_KERNEL_MAX:
             gbuf = _resolve_scratch(scratch, gather_buffer, "gather_buffer", arg_x.device, h,

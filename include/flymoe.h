@@ -51,6 +51,8 @@ extern "C" {
 #define FLYMOE_ROWS_BY_TOKEN 0 /* row = token id                     (stage-1 input)   */
 #define FLYMOE_ROWS_BY_PAIR 1  /* row = token*topk + slot            (reference layout) */
 #define FLYMOE_ROWS_SORTED 2   /* row = position in the sorted list  (fused layer)      */
+#define FLYMOE_ROWS_BY_SLOT 3  /* row = slot*num_tokens + token: the slot-major per-(token, slot) rows of the
+                                  reference's "int8smooth" stage-1 input (kernels/moe_gemm_2stage.py:546-555) */
 
 /* GEMM implementations */
 #define FLYMOE_IMPL_TCGEN05 0 /* TMA + tcgen05.mma + TMEM (the product path)             */
@@ -170,8 +172,8 @@ int flymoe_moe_gemm2(void* out, const void* a2, const float* scale_a, int64_t sa
  * "fp16" and "bf16".  in_dtype E4M3, I8 (signed 8-bit operands, exact int32 accumulation), or
  * F16 / BF16 (16-bit operands and weights, tcgen05 kernel only; their scale pointers may be null,
  * which means every scale is 1, as in the reference where these variants carry no scales).
- * Stage 1: x [T,H] (x_layout BY_TOKEN), [T*k,H] (BY_PAIR: "int8smooth") or rows already in sorted
- * order (SORTED); scale_x f32 [T] (x_scale_layout BY_TOKEN), [T*k] (BY_PAIR)
+ * Stage 1: x [T,H] (x_layout BY_TOKEN), [k*T,H] slot-major (BY_SLOT: "int8smooth"), [T*k,H] (BY_PAIR)
+ * or rows already in sorted order (SORTED); scale_x f32 [T] (x_scale_layout BY_TOKEN), [k*T] (BY_SLOT), [T*k] (BY_PAIR)
  * or per sorted row; w [E,2I,H] row-major, scale_w f32 [E*2I]; out F16/BF16 [T*k,I]
  * (out_layout BY_PAIR) or sorted rows.  Stage 2: a2 [T*k,I] / sorted rows, scale_a f32 [T*k] /
  * per sorted row, w [E,H,I], scale_w f32 [E*H]; out as flymoe_moe_gemm2.  The K range is

@@ -69,7 +69,11 @@ def run_stage1(shape, in_dtype, out_dtype, impl, w_layout, doweight):
                                impl=impl)
     dt = {"f16": torch.float16, "bf16": torch.bfloat16}[out_dtype]
     out = torch.full((T * k + 16, I), 77.0, dtype=dt, device="cuda")
-    exe(out.view(-1)[: T * k * I], xq.cuda().view(-1, H), dev_weight(w1q, w_layout, in_dtype), scale_arg(sx),
+    if in_dtype == "int8smooth":      # per-(token, slot) rows travel slot-major, as the reference's kernel reads them
+        x_arg, sx_arg = xq.permute(1, 0, 2).contiguous().cuda().view(-1, H), scale_arg(sx.permute(1, 0, 2).contiguous())
+    else:
+        x_arg, sx_arg = xq.cuda().view(-1, H), scale_arg(sx)
+    exe(out.view(-1)[: T * k * I], x_arg, dev_weight(w1q, w_layout, in_dtype), sx_arg,
         scale_arg(sw1), s_ids, s_e, s_w, nv, T, I, H, nblk, torch.cuda.current_stream())
     torch.cuda.synchronize()
     assert bool((out[T * k:] == 77.0).all()), "stage 1 wrote past its output rows"
