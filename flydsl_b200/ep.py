@@ -206,6 +206,14 @@ class ExpertParallelMoE:
         self.per_rank = len(self.local)
         self.chunks = max(1, int(chunks))
         self.last_plans: list = []
+        # a list here makes the peer-store step record one CUDA event per phase boundary: (name, event)
+        self.phase_marks = None
+
+    def _phase(self, name: str) -> None:
+        if self.phase_marks is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(torch.cuda.current_stream())
+            self.phase_marks.append((name, ev))
 
     @property
     def last_plan(self) -> DispatchPlan:
@@ -241,6 +249,7 @@ class ExpertParallelMoE:
         T = logits.shape[0]
         bounds = chunk_bounds(T, self.chunks)
         C = len(bounds)
+        self._phase("start")
         topk_w, topk_ids = ops.gate(logits)
         if getattr(ops, "direct_dispatch", False):
             return self._forward_direct(topk_w, topk_ids, xq, x_scale, T)
@@ -307,13 +316,18 @@ class ExpertParallelMoE:
         matrix = ops.counts_matrix(self.world) if hasattr(ops, "counts_matrix") else None
         gathered = (list(matrix.unbind(0)) if matrix is not None
                     else [torch.empty_like(mine) for _ in range(self.world)])
+        self._phase("gate_sort_count")
         dist.all_gather(gathered, mine, group=g)
+        self._phase("count_exchange")
         if getattr(ops, "device_plan", False):
             # the whole plan stays on the device: no host synchronisation in the step
             self._counts_dev = matrix if matrix is not None else torch.stack(gathered)
             self.last_plans = []
-            ops.run_direct_on_device(xq, x_scale, s_ids, s_eids, self._counts_dev, self.rank, T)
-            return ops.combine(ops.returned_rows(P), s_ids, topk_w, 0, T, T, 0)
+            extra = {} if self.phase_marks is None else {"phase": self._phase}
+            ops.run_direct_on_device(xq, x_scale, s_ids, s_eids, self._counts_dev, self.rank, T, **extra)
+            out = ops.combine(ops.returned_rows(P), s_ids, topk_w, 0, T, T, 0)
+            self._phase("reduce")
+            return out
         counts = torch.stack(gathered).cpu().numpy()                          # the step's host synchronisation
         if int(counts[self.rank].sum()) != P:
             raise RuntimeError(f"dispatch plan covers {int(counts[self.rank].sum())} rows, expected {P}")
@@ -500,7 +514,7 @@ class CudaOps:
                                               b["nvalid"].data_ptr(), tab[0].data_ptr(), tab[1].data_ptr(), None, 0,
                                               T, self.k, self.H, self.E, T * self.k, self._stream()), "dispatch_rows")
 
-    def run_direct_on_device(self, xq, x_scale, s_ids, s_eids, counts, rank: int, T: int) -> None:
+    def run_direct_on_device(self, xq, x_scale, s_ids, s_eids, counts, rank: int, T: int, phase=None) -> None:
         """Dispatch, local experts and the two rendezvous with the plan computed on the GPU
         (``flymoe_ep_plan_direct``: two small kernels, the arithmetic of ``plan_direct``).  Launch sizes use
         the buffers' capacity; the kernels read the real extents from device memory.  A step that does not
@@ -515,15 +529,21 @@ class CudaOps:
             inner.sorted_expert_ids.data_ptr(), inner.num_valid_ids.data_ptr(), self._plan_row_dst.data_ptr(),
             self._plan_ws.data_ptr(), self._plan_ws.numel(), counts.shape[0], rank, self.E, U, H, cap,
             self._stream()), "ep_plan_direct")
+        phase = phase or (lambda name: None)
+        phase("plan")
         L.check(self.lib.flymoe_dispatch_rows(xq.data_ptr(), x_scale.data_ptr(), s_ids.data_ptr(), s_eids.data_ptr(),
                                               b["nvalid"].data_ptr(), tab[0].data_ptr(), tab[1].data_ptr(),
                                               tab[2].data_ptr(), cap, T, self.k, H, self.E, T * self.k,
                                               self._stream()), "dispatch_rows")
+        phase("dispatch")
         self.peer_rendezvous()
+        phase("wait_for_peers_rows")
         base_ptr = self.peers.local.data_ptr()
         inner.experts_forward_sorted(base_ptr + self._off_xs, base_ptr + self._off_xsc, cap, cap // U,
                                      self._stream(), self._plan_row_dst)
+        phase("stage1_stage2_combine")
         self.peer_rendezvous()
+        phase("wait_for_peers_outputs")
 
     def local_experts_direct(self, dp: DirectPlan) -> None:
         inner, dev = self.inner, self.dev

@@ -92,6 +92,20 @@ def run_expert_parallel(args, cfg: wl.MoEConfig, parity_fn=None):
         clocks = sampler.stop() if sampler is not None else None
         g1 = [a.elapsed_time(b) for (n, a, b) in ev if n == "gemm1"]
         g2 = [a.elapsed_time(b) for (n, a, b) in ev if n == "gemm2"]
+        # where this rank's step goes, phase by phase (a few extra steps with one event per boundary; a wait
+        # for the peers also absorbs their lag, so these are this rank's view, not a sum every rank shares)
+        breakdown = None
+        if direct and getattr(ops, "device_plan", False):
+            acc, n_bd = {}, 3
+            for _ in range(n_bd):
+                layer.phase_marks = []
+                layer(logits, xq, xs)
+                torch.cuda.synchronize()
+                marks = layer.phase_marks
+                for (_, a), (name, b) in zip(marks[:-1], marks[1:]):
+                    acc[name] = acc.get(name, 0.0) + a.elapsed_time(b) / n_bd
+            layer.phase_marks = None
+            breakdown = {name: round(v, 4) for name, v in acc.items()}
         rows_in = layer.last_plan.rows_in
         imb = torch.tensor([float(rows_in)], device=dev, dtype=torch.float64)
         imb_max = imb.clone()
@@ -278,6 +292,7 @@ def run_expert_parallel(args, cfg: wl.MoEConfig, parity_fn=None):
                 "fused_stage2_roofline": fused_roofline,
                 "comm": {"dispatch_bytes_rank0": int(remote * (H + H // 128 * 4 + (0 if direct else 4))),
                          "combine_bytes_rank0": int(remote * H * 2), "load_imbalance_max_over_mean": round(imbalance, 3)},
+                "step_breakdown_ms_rank0": breakdown,
                 "parity_check": parity,
                 "same_work_1gpu_ms": None if same_work_ms is None else round(same_work_ms, 4),
                 "weak_scaling_eff": None if same_work_ms is None else round(same_work_ms / ms, 4),
