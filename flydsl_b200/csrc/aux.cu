@@ -47,8 +47,14 @@ dispatch_rows_kernel(const uint4* __restrict__ x, const float* __restrict__ x_sc
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
   const int valid = min(__ldg(num_valid_ids), max_rows);
-  for (int r = blockIdx.x * warps_per_block + (threadIdx.x >> 5); r < valid;
-       r += gridDim.x * warps_per_block) {
+  // Every warp takes one contiguous piece of the sorted list (the grid is sized to be resident at once), so
+  // at any moment the warps of a GPU store to all destination ranks alike.  With a grid-stride walk all GPUs
+  // would work through the ranks in the same order and pile onto one receiver's links at a time.
+  const int total_warps = gridDim.x * warps_per_block;
+  const int piece = (valid + total_warps - 1) / total_warps;
+  const int first = (blockIdx.x * warps_per_block + (threadIdx.x >> 5)) * piece;
+  const int last = min(valid, first + piece);
+  for (int r = first; r < last; ++r) {
     const int id = __ldg(sorted_ids + r);
     const int e = __ldg(sorted_expert_ids + r);
     const int t = id_token(id), s = id_slot(id);
@@ -64,7 +70,17 @@ dispatch_rows_kernel(const uint4* __restrict__ x, const float* __restrict__ x_sc
     }
     uint4* dx = reinterpret_cast<uint4*>(dst_base + (long long)r * row_vec * 16);
     const uint4* p = x + size_t(t) * row_vec;
-    for (int i = lane; i < row_vec; i += 32) dx[i] = __ldg(p + i);
+    // eight 16-byte loads in flight per lane before the first store: the stores cross NVLink and a loop of
+    // dependent load/store pairs would leave it mostly idle
+    for (int i0 = lane; i0 < row_vec; i0 += 32 * 8) {
+      uint4 v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (i0 + 32 * j < row_vec) v[j] = __ldg(p + i0 + 32 * j);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (i0 + 32 * j < row_vec) dx[i0 + 32 * j] = v[j];
+    }
     float* ds = reinterpret_cast<float*>(__ldg(dst_scale + e) + (long long)r * kblocks * 4);
     const float* ps = x_scale + size_t(t) * kblocks;
     for (int i = lane; i < kblocks; i += 32) ds[i] = __ldg(ps + i);
@@ -290,7 +306,7 @@ extern "C" int flymoe_dispatch_rows(const void* x, const float* x_scale, const i
   if (max_rows <= 0) return FLYMOE_OK;
   int* status = device_status_ptr();
   FLYMOE_REQUIRE(status != nullptr, "dispatch_rows: no CUDA device");
-  const int blocks = std::min(ceil_div(max_rows, 8), sm_count() * 8);
+  const int blocks = std::min(ceil_div(max_rows, 8), sm_count() * 4);     // 4 x 256 threads x 64 registers fit an SM
   dispatch_rows_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(x), x_scale, sorted_ids, sorted_expert_ids, num_valid_ids,
       reinterpret_cast<const long long*>(dst_x), reinterpret_cast<const long long*>(dst_scale),

@@ -131,7 +131,7 @@ def test_expert_parallel_matches_single_gpu(world, routing, chunks):
 @pytest.mark.parametrize("world,routing,direct", [(1, "zipf", False), (1, "uniform", "host"), (1, "zipf", "device"),
                                                   (2, "uniform", False), (2, "zipf", "host"), (4, "zipf", False),
                                                   (4, "uniform", "device"), (8, "uniform", False),
-                                                  (8, "zipf", "host")])
+                                                  (8, "zipf", "host"), (8, "uniform", "device")])
 def test_fused_combine_matches_single_gpu(world, routing, direct):
     """Stage 2 stores the expert outputs straight into the owning ranks' buffers (peer stores from the
     GEMM epilogue, no combine all-to-all); with ``direct`` the dispatch, too, is peer stores, into the
