@@ -196,6 +196,19 @@ def run_expert_parallel(args, cfg: wl.MoEConfig, parity_fn=None):
         h2d_gbs, h2d_ms = copy_rate(h2d_all, h2d_bytes_rank)
         d2h_gbs, d2h_ms = copy_rate(lambda: h_out.copy_(ops.out, non_blocking=True), d2h_bytes_rank)
 
+        # both directions at once, as in an end-to-end step (input of step i+1 in, result of step i out): on a
+        # host whose memory or root port is shared by all ranks the two directions slow each other down
+        def both_ways():
+            h2d_s.wait_stream(stream)
+            d2h_s.wait_stream(stream)
+            with torch.cuda.stream(h2d_s):
+                h2d_all()
+            with torch.cuda.stream(d2h_s):
+                h_out.copy_(ops.out, non_blocking=True)
+            stream.wait_stream(h2d_s)
+            stream.wait_stream(d2h_s)
+        _, both_ms = copy_rate(both_ways, h2d_bytes_rank + d2h_bytes_rank)
+
         # ---- checker: a few of this rank's own tokens against the CPU oracle
         parity = None
         if parity_fn is not None:
@@ -302,7 +315,8 @@ def run_expert_parallel(args, cfg: wl.MoEConfig, parity_fn=None):
                         "d2h_bytes_per_step": int(world * d2h_bytes_rank),
                         "h2d_gbs_per_rank_all_ranks_copying": round(h2d_gbs, 2),
                         "d2h_gbs_per_rank_all_ranks_copying": round(d2h_gbs, 2),
-                        "pcie_floor_ms": round(max(h2d_ms, d2h_ms), 4),
+                        "pcie_floor_ms": round(max(h2d_ms, d2h_ms, both_ms), 4),
+                        "pcie_ms_one_direction_at_a_time": [round(h2d_ms, 4), round(d2h_ms, 4)],
                         "bound": "pcie" if max(h2d_ms, d2h_ms) > ms else "device",
                         "how": "two input slots; the result's device-to-host copy overlaps the next step up to its reduce"},
                 "clocks": clocks,
