@@ -259,7 +259,7 @@ def test_int4_unpack_matches_reference_packing():
             assert torch.equal(as_i8.cpu().view(rows, cols), wq.view(rows, cols))
             as_bf = unpack_int4_weight(packed, rows, cols, torch.bfloat16)
             assert torch.equal(as_bf.cpu().float().view(rows, cols), wq.view(rows, cols).float())
-    assert seen == 2
+    assert seen == 3          # W4A8, W4A16 and the group-wise W4A16 case
 
 
 def test_pertoken_16bit_golden_fixture():
