@@ -300,3 +300,37 @@ def test_pertoken_large_reference_shape(in_dtype):
     out2r, _, _ = run_stage2("L", in_dtype, "bf16", "tcgen05", "plain", "reduce")
     assert_close(out2r, ref2, RTOL, ATOL + 2.0 ** -7 * pair_peak, f"per-token stage 2 L reduce {in_dtype}")
 
+
+
+@pytest.mark.parametrize("in_dtype", ["fp8", "bf16", "int4"])
+def test_pertoken_empty_batch_is_a_no_op(in_dtype):
+    """Zero tokens: both launchers return without touching their outputs (the reference's kernels exit early on
+    an empty sorted list, kernels/moe_gemm_2stage.py:441-460)."""
+    H, I, E, k, tile_m = 256, 128, 4, 2, 16
+    _, _, w1q, sw1, w2q, sw2, _, _ = hp.pertoken_inputs(in_dtype, 8, H, I, E, k, 5, orc.quant_rows)
+    d = "cuda"
+    s_ids = torch.full((E * tile_m,), (k << 24), dtype=torch.int32, device=d)
+    s_w = torch.zeros(E * tile_m, dtype=torch.float32, device=d)
+    s_e = torch.full((E,), -1, dtype=torch.int32, device=d)
+    nv = torch.zeros(2, dtype=torch.int32, device=d)
+    x_dt = {"fp8": hp.FP8, "bf16": torch.bfloat16, "int4": torch.int8}[in_dtype]
+    x = torch.empty((0, H), dtype=x_dt, device=d)
+    sx = torch.empty(0, dtype=torch.float32, device=d)
+    common = dict(model_dim=H, inter_dim=I, experts=E, topk=k, tile_m=tile_m, tile_n=128, tile_k=128, in_dtype=in_dtype)
+    out1 = torch.full((4, I), 3.0, dtype=torch.bfloat16, device=d)
+    pt.compile_moe_gemm1(doweight_stage1=False, out_dtype="bf16", **common)(
+        out1.view(-1)[:0], x, dev_weight(w1q, "preshuffle16x16", in_dtype), sx, scale_arg(sw1), s_ids, s_e, s_w, nv,
+        0, I, H, E)
+    out2 = torch.full((4, H), 3.0, dtype=torch.float32, device=d)
+    a2 = torch.empty((0, I), dtype=x_dt, device=d)
+    pt.compile_moe_gemm2(doweight_stage2=True, out_dtype="f32", **common)(
+        out2.view(-1)[:0], a2, dev_weight(w2q, "preshuffle16x16", in_dtype), sx, scale_arg(sw2), s_ids, s_e, s_w, nv,
+        0, H, I, E)
+    torch.cuda.synchronize()
+    assert bool((out1 == 3.0).all()) and bool((out2 == 3.0).all())
+    assert _lib_status() == 0
+
+
+def _lib_status():
+    from flydsl_b200 import _lib
+    return _lib.device_status()
