@@ -165,3 +165,33 @@ def test_sorting_rejects_topk_above_expert_count(lib):
     assert rc == -1 and b"topk" in lib.flymoe_last_error()
     # the pair count is formed in 64 bits: no wrap-around for a huge (tokens, topk) product
     assert lib.flymoe_moe_sorting_workspace_elems((1 << 24) - 1, 1024, 255, 32) > (1 << 31)
+
+
+def test_header_is_plain_c_and_a_c_program_links(tmp_path):
+    """include/flymoe.h compiles as C99 and a C caller can link the shared library and use its
+    host-only entry points (no torch, no Python in the call chain)."""
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler on this machine")
+    src = tmp_path / "caller.c"
+    src.write_text(
+        '#include <stdio.h>\n#include <string.h>\n#include "flymoe.h"\n'
+        "int main(void) {\n"
+        "  if (flymoe_abi_version() != 1) return 1;\n"
+        '  if (strcmp(flymoe_error_string(-4), "workspace too small") != 0) return 2;\n'
+        "  if (flymoe_moe_sorting_workspace_elems(4096, 256, 8, 128) != (4096 * 8 / 128) * 256 + 256) return 3;\n"
+        "  /* argument validation happens before any CUDA call: a null pointer is an error code, not a crash */\n"
+        "  if (flymoe_unpack_int4_weight(NULL, NULL, 16, 32, FLYMOE_I8, NULL) != -1) return 4;\n"
+        '  printf("%s\\n", flymoe_last_error());\n'
+        "  return 0;\n}\n")
+    exe = tmp_path / "caller"
+    lib_dir = Path(_lib.LIB_PATH).resolve().parent
+    r = subprocess.run([gcc, "-std=c99", "-Wall", "-Werror", "-I", str(ROOT / "include"), str(src), "-o", str(exe),
+                        "-L", str(lib_dir), "-l:" + Path(_lib.LIB_PATH).name, "-Wl,-rpath," + str(lib_dir)],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    run = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert run.returncode == 0, f"C caller returned {run.returncode}: {run.stderr}"
+    assert "unpack_int4_weight" in run.stdout
