@@ -29,8 +29,12 @@ static int gemm1_impl(void* out, float* out_scale, int64_t out_scale_stride, con
   FLYMOE_REQUIRE(model_dim > 0 && model_dim % 128 == 0, "gemm1: model_dim must be a positive multiple of 128");
   FLYMOE_REQUIRE(experts >= 1 && topk >= 1 && topk <= 255, "gemm1: experts/topk out of range");
   FLYMOE_REQUIRE(tile_m >= 1 && size_expert_ids >= 0, "gemm1: tile_m/size_expert_ids out of range");
-  FLYMOE_REQUIRE(out_dtype == FLYMOE_F16 || out_dtype == FLYMOE_BF16 || (out_dtype == FLYMOE_E4M3 && !per_token),
-                 "gemm1: out_dtype must be F16, BF16 or (block-scaled only) E4M3");
+  // F32 with per-token scaling: the raw gate|up sums of the reference's split-K contract, [T*k, 2I], added to out
+  const bool raw_sums = out_dtype == FLYMOE_F32 && per_token;
+  FLYMOE_REQUIRE(out_dtype == FLYMOE_F16 || out_dtype == FLYMOE_BF16 || (out_dtype == FLYMOE_E4M3 && !per_token) || raw_sums,
+                 "gemm1: out_dtype must be F16, BF16, (block-scaled only) E4M3 or (per-token only) F32");
+  FLYMOE_REQUIRE(!raw_sums || (impl == FLYMOE_IMPL_TCGEN05 && out_layout == FLYMOE_ROWS_BY_PAIR),
+                 "gemm1: fp32 gate|up sums need the tcgen05 kernel and out_layout BY_PAIR");
   FLYMOE_REQUIRE(in_dtype == FLYMOE_E4M3 || ((in_dtype == FLYMOE_I8 || is_half(in_dtype)) && per_token),
                  "gemm1: in_dtype must be E4M3 or (per-token scaling only) I8, F16, BF16");
   FLYMOE_REQUIRE(!is_half(in_dtype) || impl == FLYMOE_IMPL_TCGEN05, "gemm1: 16-bit operands need the tcgen05 kernel");

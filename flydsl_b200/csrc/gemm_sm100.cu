@@ -765,7 +765,21 @@ moe_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       // Kept short on purpose: this code runs once per tile between two main loops, and a long
       // straight-line tail (IEEE division, accurate exp) costs more in instruction fetch than in math.
       PROF_START
-      if (STAGE == 1) {
+      if (STAGE == 1 && SCALING == kScalePerToken && a.out_dtype == FLYMOE_F32) {
+        // The reference's split-K output contract (kernels/moe_gemm_2stage.py:121-122, :1345): the scaled gate
+        // and up sums are ADDED to out[t*topk+s][0:I | I:2I] (fp32, zeroed by the caller) -- no activation,
+        // no routing weight.  The whole K range is summed here, so every element receives one addition.
+        if (warp_active && valid) {
+          float* og = static_cast<float*>(a.out) + ((long long)tok * a.topk + slot) * (2LL * a.n_dim) +
+                      (long long)n * 128 + wg * 64;
+          float* ou = og + a.n_dim;
+#pragma unroll
+          for (int j = 0; j < 64; j += 4) red_add_v4_f32(og + j, accv[j], accv[j + 1], accv[j + 2], accv[j + 3]);
+#pragma unroll
+          for (int j = 0; j < 64; j += 4)
+            red_add_v4_f32(ou + j, accv[64 + j], accv[64 + j + 1], accv[64 + j + 2], accv[64 + j + 3]);
+        }
+      } else if (STAGE == 1) {
         // accv[0..63] = gate, accv[64..127] = up, columns n*128 + wg*64 + j
         float amax = 0.f;
 #pragma unroll

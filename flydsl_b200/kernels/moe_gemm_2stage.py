@@ -33,8 +33,13 @@ layout (f32 ``[E, K/32, N]``, or with ``scale_is_bf16`` bf16 ``[E, K/64, N, 2]``
 row; they are multiplied in while unpacking (``bf16(value * scale)``), after which the scale-less bf16 kernel
 runs.
 
-Not built here: split-K (``k_batch > 1``) and group-wise scales with int8 activations (``in_dtype="int4"``
-with ``group_size > 0``) raise ``ValueError`` at build time; ``group_size`` other than 32 is rejected as in
+``k_batch > 1`` (stage 1): the reference's split-K launches add the scaled gate and up sums, without
+activation and routing weight, to a caller-zeroed fp32 ``[tokens*topk, 2*inter]`` buffer and the caller
+finishes ``silu(gate)*up`` (:121-122; its test :582-587, :708-713).  The launcher built here keeps that
+output contract; K is not actually split (one CTA sums the whole K range and adds once per element).
+
+Not built here: ``k_batch > 1`` with bf16 activations (bf16 partial sums) and group-wise scales with int8
+activations (``in_dtype="int4"`` with ``group_size > 0``) raise ``ValueError`` at build time; ``group_size`` other than 32 is rejected as in
 the reference and ignored for the variants without packed weights.
 Additions (keyword-only): ``w_layout`` ("preshuffle16x16" default, or "plain") and ``impl``
 ("tcgen05" default, "simt" cross-check) as in ``moe_blockscale_2stage``.
@@ -76,8 +81,20 @@ def _check(in_dtype, group_size, k_batch, tile_m, tile_k, model_dim, inter_dim, 
                          "This is due to int4 preshuffle layout constraints.")
     if in_dtype in _INT4_TO and w_layout != "preshuffle16x16":
         raise ValueError("packed int4 weights are defined on the preshuffled order: w_layout must be 'preshuffle16x16'")
-    if k_batch != 1:
-        raise ValueError("split-K (k_batch > 1) is not built here: one CTA owns the whole K range of its tile")
+    if k_batch < 1:
+        raise ValueError(f"k_batch must be >= 1, got {k_batch}")
+    if k_batch > 1:
+        # split-K launches keep the reference's OUTPUT contract (raw fp32 gate|up sums added to a zeroed
+        # [tokens*topk, 2*inter] buffer); K itself is not split here, one CTA owns the whole K range of a tile
+        if in_dtype in ("bf16", "int4_bf16"):
+            raise ValueError("k_batch > 1 with bf16 activations accumulates bf16 partial sums in the reference; "
+                             "that output format is not built here")
+        if model_dim % k_batch:
+            raise ValueError(f"model_dim={model_dim} not divisible by k_batch={k_batch}")
+        if (model_dim // k_batch) % tile_k:
+            raise ValueError(f"K_per_batch={model_dim // k_batch} not divisible by tile_k={tile_k}")
+        if impl != "tcgen05":
+            raise ValueError("k_batch > 1 is built for the tensor-core path only (impl='tcgen05')")
     if tile_k % 64 != 0:
         raise ValueError(f"tile_k_bytes must be divisible by 64, got tile_k_bytes={tile_k} (tile_k={tile_k}, elem_bytes=1)")
     if (tile_m * tile_k) % 256 != 0:
@@ -117,7 +134,8 @@ def compile_moe_gemm1(*, model_dim: int, inter_dim: int, experts: int, topk: int
     int4_to = _INT4_TO.get(in_dtype)
     w_torch = _PACKED_W if int4_to is not None else in_torch
     gs_torch = (torch.bfloat16,) if scale_is_bf16 else (torch.float32,)
-    out_torch = _OUT16[out_dtype]
+    raw_sums = k_batch > 1                     # the split-K output contract: fp32 gate|up sums, [tokens*topk, 2*inter]
+    out_torch = torch.float32 if raw_sums else _OUT16[out_dtype]
     out_code = _lib.DTYPE_CODE[out_torch]
     by_pair = in_dtype == "int8smooth"          # x and scale_x per (token, slot), slot-major: row s*tokens + t
     wrows = experts * 2 * inter_dim
@@ -133,7 +151,7 @@ def compile_moe_gemm1(*, model_dim: int, inter_dim: int, experts: int, topk: int
         cap_rows = blocks * tile_m
         pairs = tokens * topk
         x_rows = pairs if by_pair else tokens
-        _lib.require_cuda("arg_out", arg_out, (out_torch,), pairs * inter_dim)
+        _lib.require_cuda("arg_out", arg_out, (out_torch,), pairs * inter_dim * (2 if raw_sums else 1))
         _lib.require_cuda("arg_x", arg_x, in_torch, x_rows * model_dim)
         _lib.require_cuda("arg_w", arg_w, w_torch, wrows * model_dim // (2 if int4_to is not None else 1))
         if not no_x_scale:

@@ -175,7 +175,10 @@ int flymoe_moe_gemm2(void* out, const void* a2, const float* scale_a, int64_t sa
  * Stage 1: x [T,H] (x_layout BY_TOKEN), [k*T,H] slot-major (BY_SLOT: "int8smooth"), [T*k,H] (BY_PAIR)
  * or rows already in sorted order (SORTED); scale_x f32 [T] (x_scale_layout BY_TOKEN), [k*T] (BY_SLOT), [T*k] (BY_PAIR)
  * or per sorted row; w [E,2I,H] row-major, scale_w f32 [E*2I]; out F16/BF16 [T*k,I]
- * (out_layout BY_PAIR) or sorted rows.  Stage 2: a2 [T*k,I] / sorted rows, scale_a f32 [T*k] /
+ * (out_layout BY_PAIR) or sorted rows; or out_dtype F32 (tcgen05 kernel, BY_PAIR): the scaled gate and
+ * up sums themselves are ADDED to out [T*k, 2I] (gate columns first), without activation or routing
+ * weight -- the output contract of the reference's split-K launches (k_batch > 1,
+ * kernels/moe_gemm_2stage.py:121-122), which finish SiLU(gate)*up outside the kernel.  Stage 2: a2 [T*k,I] / sorted rows, scale_a f32 [T*k] /
  * per sorted row, w [E,H,I], scale_w f32 [E*H]; out as flymoe_moe_gemm2.  The K range is
  * accumulated in TMEM and each tile is scaled once: out = (sum_k a*w) * scale_a[row] * scale_w[col].
  * scale_w must be 16-byte aligned. */

@@ -280,19 +280,20 @@ def _group_dequant(w_q: torch.Tensor, group_scale: torch.Tensor, group_size: int
 
 
 def pertoken_stage1(x_q, scale_x, w1_q, scale_w1, topk_ids, topk_weights, inter_dim: int,
-                    doweight_stage1: bool = False, group_size: int = -1, scale_w1_groups=None):
+                    doweight_stage1: bool = False, group_size: int = -1, scale_w1_groups=None, raw_sums: bool = False):
     """silu(x W1g^T) * (x W1u^T) with x = x_q * scale_x (per row) and W = w_q * scale_w (per row).
 
     x_q [T,K] (or [T,k,K] when every (token, slot) pair brings its own row) of e4m3/int8, scale_x
     [T,1] ([T,k,1]); w1_q [E,2I,K], scale_w1 [E,2I,1].  f16/bf16 operands come with ``None`` scales
     (no dequantisation, tests/kernels/test_ref.py:57-69 of the reference).  ``group_size > 0``: the weights
     are scaled per K group with ``scale_w1_groups`` [E, K/group_size, 2I] instead of per row.
-    Returns f32 [T,k,I]."""
+    Returns f32 [T,k,I]; with ``raw_sums`` the pre-activation sums [T,k,2I] (gate columns first) that the
+    reference's split-K launches leave to the caller (tests/kernels/test_moe_gemm.py:708-713)."""
     ids = torch.as_tensor(topk_ids).to(torch.int64)
     T, k = ids.shape
     E = w1_q.shape[0]
     x = x_q.to(torch.float32) if scale_x is None else x_q.to(torch.float32) * scale_x
-    out = torch.zeros((T, k, inter_dim), dtype=torch.float32)
+    out = torch.zeros((T, k, 2 * inter_dim if raw_sums else inter_dim), dtype=torch.float32)
     for e in range(E):
         tok, slot = (ids == e).nonzero(as_tuple=True)
         if tok.numel() == 0:
@@ -303,6 +304,9 @@ def pertoken_stage1(x_q, scale_x, w1_q, scale_w1, topk_ids, topk_weights, inter_
             w = w1_q[e].to(torch.float32) if scale_w1 is None else w1_q[e].to(torch.float32) * scale_w1[e]
         rows = x[tok] if x.dim() == 2 else x[tok, slot]
         y2 = F.linear(rows, w)
+        if raw_sums:
+            out[tok, slot] = y2
+            continue
         y = F.silu(y2[:, :inter_dim]) * y2[:, inter_dim:]
         if doweight_stage1:
             y = y * torch.as_tensor(topk_weights)[tok, slot].unsqueeze(-1)

@@ -141,8 +141,13 @@ def test_pertoken_builder_rules(lib):
         pt.compile_moe_gemm2(doweight_stage2=True, in_dtype="fp6", **base)
     with pytest.raises(ValueError, match="only supports out_dtype"):
         pt.compile_moe_gemm2(doweight_stage2=True, out_dtype="f32", accumulate=False, **base)
-    with pytest.raises(ValueError, match="split-K"):
-        pt.compile_moe_gemm1(doweight_stage1=False, k_batch=2, **base)
+    assert callable(pt.compile_moe_gemm1(doweight_stage1=False, k_batch=2, **base))     # split-K output contract
+    with pytest.raises(ValueError, match="not divisible by k_batch"):
+        pt.compile_moe_gemm1(doweight_stage1=False, k_batch=3, **base)
+    with pytest.raises(ValueError, match="not divisible by tile_k"):
+        pt.compile_moe_gemm1(doweight_stage1=False, k_batch=4, **base)
+    with pytest.raises(ValueError, match="bf16 partial sums"):
+        pt.compile_moe_gemm1(doweight_stage1=False, k_batch=2, in_dtype="bf16", **base)
     assert pt.compile_moe_gemm2_ex(doweight_stage2=True, mode=pt.MoeGemm2Mode.REDUCE, in_dtype="int8", **base).mode == "reduce"
     import kernels.moe_gemm_2stage as shim                      # the reference's import path
     assert shim.compile_moe_gemm1 is pt.compile_moe_gemm1

@@ -302,6 +302,39 @@ def test_pertoken_large_reference_shape(in_dtype):
 
 
 
+@pytest.mark.parametrize("shape,in_dtype,k_batch", [("S", "fp8", 2), ("M", "int8", 2), ("M", "fp16", 4), ("T128", "fp8", 2),
+                                                    ("S", "int8smooth", 2)])
+def test_pertoken_stage1_split_k_output_contract(shape, in_dtype, k_batch):
+    """k_batch > 1: the launcher adds the scaled gate|up sums (no activation, no routing weight, even with
+    doweight_stage1) to a zeroed fp32 [tokens*topk, 2*inter] buffer; the caller finishes silu(gate)*up
+    (tests/kernels/test_moe_gemm.py:582-587, :708-713 of the reference).  Launching twice doubles the sums."""
+    T, H, I, E, k, tile_m = SHAPES[shape]
+    xq, sx, w1q, sw1, _, _, ids, tw = inputs(shape, in_dtype)
+    s_ids, s_w, s_e, nv, nblk = sort(ids, tw, E, tile_m)
+    exe = pt.compile_moe_gemm1(model_dim=H, inter_dim=I, experts=E, topk=k, tile_m=tile_m, tile_n=128, tile_k=64,
+                               doweight_stage1=True, in_dtype=in_dtype, out_dtype="f16", k_batch=k_batch)
+    if in_dtype == "int8smooth":
+        x_arg, sx_arg = xq.permute(1, 0, 2).contiguous().cuda().view(-1, H), scale_arg(sx.permute(1, 0, 2).contiguous())
+    else:
+        x_arg, sx_arg = xq.cuda().view(-1, H), scale_arg(sx)
+    out = torch.zeros((T * k + 4, 2 * I), dtype=torch.float32, device="cuda")
+    args = (out.view(-1)[: T * k * 2 * I], x_arg, dev_weight(w1q, "preshuffle16x16", in_dtype), sx_arg, scale_arg(sw1),
+            s_ids, s_e, s_w, nv, T, I, H, nblk)
+    exe(*args)
+    torch.cuda.synchronize()
+    raw = out[: T * k].cpu().view(T, k, 2 * I)
+    assert float(out[T * k:].abs().sum()) == 0.0, "wrote past the output rows"
+    ref_raw = orc.pertoken_stage1(xq, sx, w1q, sw1, ids, tw, I, raw_sums=True)
+    peak = float(ref_raw.abs().max())
+    assert_close(raw, ref_raw, 1e-4, 1e-5 * peak + (2e-3 * peak if in_dtype == "fp16" else 0.0), f"raw sums {shape} {in_dtype}")
+    done = torch.nn.functional.silu(raw[..., :I]) * raw[..., I:]
+    assert_close(done, orc.pertoken_stage1(xq, sx, w1q, sw1, ids, tw, I, False), RTOL, ATOL, f"finished {shape} {in_dtype}")
+    exe(*args)                                  # the contract is accumulation: a second launch doubles every sum
+    torch.cuda.synchronize()
+    assert_close(out[: T * k].cpu().view(T, k, 2 * I), 2 * ref_raw, 1e-4, 2e-5 * peak + (4e-3 * peak if in_dtype == "fp16" else 0.0),
+                 f"accumulated {shape} {in_dtype}")
+
+
 @pytest.mark.parametrize("in_dtype", ["fp8", "bf16", "int4"])
 def test_pertoken_empty_batch_is_a_no_op(in_dtype):
     """Zero tokens: both launchers return without touching their outputs (the reference's kernels exit early on

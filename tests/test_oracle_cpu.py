@@ -165,3 +165,14 @@ def test_pertoken_family_matches_reference_functions():
             assert int(w1q.abs().max()) <= 7
             assert np.array_equal(hp.u8(orc.pack_int4_preshuffled(w1q)), g[f"p{i}_w1_packed"])
             assert np.array_equal(hp.u8(orc.pack_int4_preshuffled(w2q)), g[f"p{i}_w2_packed"])
+
+
+def test_pertoken_raw_sums_finish_to_stage1():
+    """The split-K output contract: silu(gate) * up of the raw sums is stage 1 (what the reference's test does
+    on the host, tests/kernels/test_moe_gemm.py:708-713)."""
+    T, H, I, E, k = 24, 256, 128, 4, 2
+    xq, sx, w1q, sw1, _, _, ids, tw = hp.pertoken_inputs("fp8", T, H, I, E, k, 31, orc.quant_rows)
+    raw = orc.pertoken_stage1(xq, sx, w1q, sw1, ids, tw, I, raw_sums=True)
+    assert raw.shape == (T, k, 2 * I)
+    done = torch.nn.functional.silu(raw[..., :I]) * raw[..., I:]
+    assert torch.allclose(done, orc.pertoken_stage1(xq, sx, w1q, sw1, ids, tw, I), rtol=1e-6, atol=1e-6)
