@@ -142,14 +142,16 @@ def _plain_weight(w: torch.Tensor, rows: int, cols: int, layout: str, stream, in
     storage = w.untyped_storage()
     gkey = None if group_scale is None else (group_scale.data_ptr(), group_scale._version, group_scale.dtype)
     key = (w.data_ptr(), w.numel(), w.element_size(), w.device.index, rows, cols, int4_to, gkey)
+    gstorage = None if group_scale is None else group_scale.untyped_storage()
     hit = _plain_cache.get(key)
-    if hit is not None and hit[0] == w._version and hit[2]() is storage:
+    if (hit is not None and hit[0] == w._version and hit[2]() is storage
+            and (gstorage is None or (hit[3] is not None and hit[3]() is gstorage))):
         return hit[1]
     if int4_to is None:
         plain = unshuffle_weight(w, rows, cols, stream)
     else:
         plain = unpack_int4_weight(w, rows, cols, int4_to, stream, group_scale=group_scale, rows_per_expert=rows_per_expert)
-    _plain_cache[key] = (w._version, plain, weakref.ref(storage))
+    _plain_cache[key] = (w._version, plain, weakref.ref(storage), None if gstorage is None else weakref.ref(gstorage))
     weakref.finalize(storage, _drop_plain, key, id(plain))
     return plain
 
